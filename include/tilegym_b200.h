@@ -1,0 +1,154 @@
+/*
+ * tilegym_b200 - C ABI of the B200 (sm_100a) FP8 scaled-GEMM library.
+ *
+ * Conventions (they mirror the FFI TileGym already uses for its compiled
+ * cuTile-rs kernels, src/tilegym/ops/cutile_rs/ffi_util.rs:26-35,102-122 and
+ * src/tilegym/ops/cutile_rs/matmul_kernel/ffi.rs:29-53):
+ *   - one extern "C" symbol per operator, returning an int32 status code;
+ *   - tensors cross the boundary as `const TgTensorDesc*` (device pointer,
+ *     rank, shape, strides in ELEMENTS, dtype code); the callee borrows the
+ *     memory and never frees it; the caller keeps descriptors alive for the
+ *     duration of the call only;
+ *   - the last two arguments are the CUDA device ordinal and the raw
+ *     cudaStream_t as an integer; every call enqueues work on that stream and
+ *     returns without synchronising;
+ *   - no locks are taken on the call path: call from the thread that drives
+ *     the stream.  Per-device state is created on the first call on a device.
+ *
+ * Status codes: 0 ok, -2 unsupported dtype, -3 launch failed, -4 device
+ * initialisation failed, -5 null pointer, -6 invalid arguments, -7 a bounded
+ * device-side wait expired, -8 a pointer or row pitch is not 16-byte aligned.
+ * (-1 is reserved, as in the reference FFI, for "auto".)
+ */
+#ifndef TILEGYM_B200_H_
+#define TILEGYM_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define TG_API __attribute__((visibility("default")))
+#else
+#define TG_API
+#endif
+
+#define TG_OK 0
+#define TG_ERR_DTYPE (-2)
+#define TG_ERR_LAUNCH (-3)
+#define TG_ERR_DEVICE (-4)
+#define TG_ERR_NULL (-5)
+#define TG_ERR_ARGS (-6)
+#define TG_ERR_TIMEOUT (-7)
+#define TG_ERR_ALIGN (-8)
+
+/* dtype codes of src/tilegym/ops/cutile_rs/ffi_util.rs:26-35 */
+#define TG_F32 0
+#define TG_F16 1
+#define TG_BF16 2
+#define TG_I32 3
+#define TG_I64 4
+#define TG_F8E5M2 5
+#define TG_U8 6
+#define TG_F8E4M3 7
+
+typedef struct TgTensorDesc {
+  uint64_t ptr;       /* device address */
+  int32_t ndim;       /* 1..5 */
+  int64_t shape[5];
+  int64_t strides[5]; /* in elements */
+  int32_t dtype;      /* TG_* code */
+} TgTensorDesc;
+
+/* Per-tensor-scaled FP8 GEMM with a fused epilogue:
+ *     C[M,N] = alpha * sa * sb * (A[M,K] . B[N,K]^T) + bias[N] + beta * C[M,N]
+ * A, B: e4m3, row-major, contiguous rows (K % 16 == 0, 16-byte aligned base).
+ * C: bf16 / f16 / f32, row-major, written in place (read first only if beta != 0).
+ * scale_a, scale_b: device pointers to one fp32 each, or 0 for 1.0.
+ * bias: f32 or bf16 vector of N elements, or NULL.
+ * workspace: device scratch of at least tg_fp8_gemm_workspace_bytes() bytes;
+ *   only the small-M (M <= 64) split-K path uses it; it must be zero before
+ *   the first call and is left zero by every call, and may be shared by calls
+ *   that are ordered on one stream, not by calls that overlap on the GPU.
+ * Replaces tilegym.suites.flashinfer.ops.gemm_alpha_beta for e4m3 inputs
+ * (src/tilegym/suites/flashinfer/ops.py:25-55, kernel
+ * src/tilegym/suites/flashinfer/cutile/gemm/gemm_alpha_beta.py:19-180) and
+ * the matmul a Linear patch calls (src/tilegym/ops/ops.py:715-741).
+ */
+TG_API int32_t tg_fp8_gemm_pertensor(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
+                              uint64_t scale_a, uint64_t scale_b, float alpha, const TgTensorDesc* bias,
+                              float beta, uint64_t workspace, uint64_t workspace_bytes, int32_t device_id,
+                              uint64_t stream);
+
+/* Block-scaled W8A8 GEMM (1 x block_k activation scales, block_n x block_k
+ * weight scales; only 128 x 128 is implemented, anything else is -6):
+ *     C[m,n] = sum_kb  As[m,kb] * Bs[n/128,kb] * (A[m,kb-block] . B[n,kb-block])
+ * A: (M,K) e4m3; B: (N,K) e4m3; As: (M, ceil(K/128)) f32; Bs: (ceil(N/128),
+ * ceil(K/128)) f32; C: (M,N) f32 / f16 / bf16.  Rows past M, N and columns
+ * past K read as zero.  workspace as above (used when K is split).
+ * Replaces tilegym.suites.unsloth.ops.w8a8_block_fp8_matmul
+ * (src/tilegym/suites/unsloth/ops.py:240-265; host wrapper and kernel
+ * src/tilegym/suites/unsloth/cutile/fp8.py:388-446 and :243-334).
+ */
+TG_API int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
+                                const TgTensorDesc* As, const TgTensorDesc* Bs, int32_t block_n,
+                                int32_t block_k, uint64_t workspace, uint64_t workspace_bytes,
+                                int32_t device_id, uint64_t stream);
+
+/* Bytes of scratch the two GEMM entry points may need for a problem size. */
+TG_API uint64_t tg_fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
+
+/* 1 x block activation quantiser: s = amax/448 per `block` contiguous
+ * elements (1.0 for an all-zero block), y = e4m3(x / s) with IEEE division.
+ * X: (..., K) bf16 / f16 / f32 contiguous, K % block == 0; Y same shape e4m3;
+ * S: (..., K/block) f32.  Only block == 128 is implemented.
+ * Replaces tilegym.suites.unsloth.ops.act_quant (src/tilegym/suites/unsloth/ops.py:223-237,
+ * kernel src/tilegym/suites/unsloth/cutile/fp8.py:77-120).
+ */
+TG_API int32_t tg_act_quant(const TgTensorDesc* Y, const TgTensorDesc* S, const TgTensorDesc* X, int32_t block,
+                     int32_t device_id, uint64_t stream);
+
+/* block x block weight dequantiser: y[i,j] = x[i,j] * s[i/block, j/block].
+ * X: (M,N) e4m3; S: (ceil(M/block), ceil(N/block)) f32; Y: (M,N) bf16/f16/f32.
+ * Replaces tilegym.suites.unsloth.ops.weight_dequant (src/tilegym/suites/unsloth/ops.py:199-220,
+ * kernel src/tilegym/suites/unsloth/cutile/fp8.py:36-71).
+ */
+TG_API int32_t tg_weight_dequant(const TgTensorDesc* Y, const TgTensorDesc* X, const TgTensorDesc* S, int32_t block,
+                          int32_t device_id, uint64_t stream);
+
+/* Per-tensor quantiser: scale = amax(|x|)/448 (1.0 if all zero), y =
+ * e4m3(clamp(x/scale, +-448)).  X: any shape, contiguous, bf16/f16/f32.
+ * scale_out: device pointer to one fp32.  amax_scratch: device pointer to one
+ * uint32 of scratch (cleared by the call itself with a stream-ordered memset).
+ * The reference has no such kernel; it is the quantiser the per-tensor
+ * benchmark configurations describe, placed in front of tg_fp8_gemm_pertensor
+ * the way act_quant sits in front of the block-scaled GEMM.
+ */
+TG_API int32_t tg_quant_pertensor(const TgTensorDesc* Y, uint64_t scale_out, const TgTensorDesc* X,
+                           uint64_t amax_scratch, int32_t device_id, uint64_t stream);
+
+/* 128 x 128 weight quantiser (producer of Bs): s = amax/448 per block (1.0
+ * for an all-zero block), y = e4m3(clamp(x/s, +-448)).  X: (N,K)
+ * bf16/f16/f32; Y: (N,K) e4m3; S: (ceil(N/128), ceil(K/128)) f32.
+ * Inverse of tg_weight_dequant; the reference has no GPU kernel for it.
+ */
+TG_API int32_t tg_weight_quant_block(const TgTensorDesc* Y, const TgTensorDesc* S, const TgTensorDesc* X,
+                              int32_t block, int32_t device_id, uint64_t stream);
+
+/* Reads (and clears) the device-side status word of `device_id` after
+ * synchronising the device: 0, or TG_ERR_TIMEOUT with *detail set to a code
+ * naming the wait that gave up.  detail may be NULL. */
+TG_API int32_t tg_device_status(int32_t device_id, int32_t* detail);
+
+/* Message of the last failing call made by this thread ("" if none). */
+TG_API const char* tg_last_error_string(void);
+
+/* Library version, e.g. 100 for 0.1.0. */
+TG_API int32_t tg_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TILEGYM_B200_H_ */

@@ -1,0 +1,91 @@
+"""Generate the golden fixtures in this folder from TileGym's own test references.
+
+Run once, in a container that has the TileGym source tree:
+
+    PYTHONPATH=<tilegym>/src:<tilegym> python tests/golden/make_golden.py <tilegym>
+
+It imports the `reference` static methods of TileGym's test classes
+(tests/suites/unsloth/test_fp8.py and
+tests/suites/flashinfer/test_flashinfer_gemm_alpha_beta.py), feeds them inputs
+drawn the way those tests draw them (same seeds and distributions, on the CPU)
+and stores inputs and outputs as compressed .npz files.  fp8 and bf16 tensors
+are stored as their raw bit patterns (uint8 / uint16).  The tests in
+tests/test_oracle.py load these files and check the CPU oracle against them;
+nothing reads the TileGym tree at test time.
+"""
+
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def bits(t: torch.Tensor) -> np.ndarray:
+    if t.dtype == torch.float8_e4m3fn:
+        return t.view(torch.uint8).numpy()
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.int16).numpy().view(np.uint16)
+    return t.numpy()
+
+
+def main(ref_root: str) -> None:
+    sys.path[:0] = [os.path.join(ref_root, "src"), ref_root]
+    from tests.suites.flashinfer.test_flashinfer_gemm_alpha_beta import Test_FlashInfer_Matmul_Alpha_Beta as G
+    from tests.suites.unsloth.test_fp8 import Test_Unsloth_ActQuant as Q
+    from tests.suites.unsloth.test_fp8 import Test_Unsloth_W8A8_FP8_Matmul as T
+    from tests.suites.unsloth.test_fp8 import Test_Unsloth_WeightDequant as W
+
+    # --- block-scaled GEMM: recipe of test_fp8.py:213-222 (seed 42) ---------
+    for M, N, K in [(128, 128, 128), (256, 256, 256), (7, 200, 320), (1, 128, 256)]:
+        torch.manual_seed(42)
+        bn = bk = 128
+        A = (torch.randn(M, K) * 0.1).to(torch.float8_e4m3fn)
+        B = (torch.randn(N, K) * 0.1).to(torch.float8_e4m3fn)
+        As = torch.rand(M, -(-K // bk), dtype=torch.float32) + 0.1
+        Bs = torch.rand(-(-N // bn), -(-K // bk), dtype=torch.float32) + 0.1
+        C = T.reference(A, B, As, Bs, [bn, bk], torch.float32)
+        Cb = T.reference(A, B, As, Bs, [bn, bk], torch.bfloat16)
+        np.savez_compressed(
+            os.path.join(HERE, f"w8a8_block_{M}x{N}x{K}.npz"),
+            A=bits(A), B=bits(B), As=bits(As), Bs=bits(Bs), C_f32=bits(C), C_bf16=bits(Cb),
+        )
+
+    # --- act_quant: recipe of test_fp8.py:120-127 (seed 42, bf16 randn) ------
+    for shape in [(64, 1024), (128, 384), (4, 128)]:
+        torch.manual_seed(42)
+        x = torch.randn(*shape, dtype=torch.bfloat16)
+        if shape == (4, 128):
+            x[1].zero_()  # all-zero block -> scale 1.0
+        y, s = Q.reference(x, block_size=128)
+        np.savez_compressed(
+            os.path.join(HERE, f"act_quant_{shape[0]}x{shape[1]}.npz"), x=bits(x), y=bits(y), s=bits(s)
+        )
+
+    # --- weight_dequant: recipe of test_fp8.py:62-67 (seed 42) ---------------
+    for M, N in [(256, 256), (130, 200)]:
+        torch.manual_seed(42)
+        x = torch.randn(M, N).to(torch.float8_e4m3fn)
+        s = torch.rand(-(-M // 128), -(-N // 128), dtype=torch.float32) + 0.1
+        y = W.reference(x, s, 128, torch.bfloat16)
+        np.savez_compressed(os.path.join(HERE, f"weight_dequant_{M}x{N}.npz"), x=bits(x), s=bits(s), y=bits(y))
+
+    # --- gemm_alpha_beta: recipe of test_flashinfer_gemm_alpha_beta.py:24-66 (seed 0),
+    # e4m3 -> bf16, at a size that fits a fixture -----------------------------
+    for (m, n, k), (alpha, beta) in [((256, 256, 256), (1.0, 0.0)), ((256, 256, 256), (1.5, 2.0))]:
+        torch.manual_seed(0)
+        a = torch.rand(m * k, dtype=torch.float16).to(torch.float8_e4m3fn).view(m, k)
+        b = torch.rand(k * n, dtype=torch.float16).to(torch.float8_e4m3fn).view(n, k)
+        c = torch.rand((m, n), dtype=torch.bfloat16)
+        out = G.reference(a, b, c.clone(), False, True, alpha, beta, torch.bfloat16)
+        np.savez_compressed(
+            os.path.join(HERE, f"gemm_alpha_beta_{m}_{alpha}_{beta}.npz"),
+            a=bits(a), b=bits(b), c=bits(c), out=bits(out), alpha=np.float32(alpha), beta=np.float32(beta),
+        )
+    print("golden fixtures written to", HERE)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

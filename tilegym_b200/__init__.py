@@ -1,0 +1,22 @@
+"""tilegym_b200: the FP8 scaled-GEMM path of TileGym as hand-written sm_100a kernels.
+
+Public surface (same names and signatures as the reference operators):
+    w8a8_block_fp8_matmul, act_quant, weight_dequant   (tilegym.suites.unsloth.ops)
+    gemm_alpha_beta                                    (tilegym.suites.flashinfer.ops)
+    matmul                                             (tilegym.ops)
+plus the per-tensor pieces the reference lacks (fp8_scaled_mm, quant_per_tensor,
+weight_quant_block, FP8Linear) and apply_tilegym_kernel_to_llama / _deepseek_v2.
+"""
+
+from .ops import (  # noqa: F401
+    act_quant,
+    fp8_scaled_mm,
+    gemm_alpha_beta,
+    matmul,
+    quant_per_tensor,
+    w8a8_block_fp8_matmul,
+    weight_dequant,
+    weight_quant_block,
+)
+
+__version__ = "0.1.0"

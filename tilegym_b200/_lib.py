@@ -1,0 +1,140 @@
+"""ctypes binding of libtilegym_b200.so (the C ABI declared in include/tilegym_b200.h).
+
+The library is the only implementation of every operator in this package:
+there is no fallback.  If the shared object is missing, importing the package
+works (so that build tooling can import it) but the first operator call raises.
+The binding follows the convention of the reference's own FFI loader
+(src/tilegym/backend/cutile_rs/utils.py:241-290, 366-370): tensors cross as
+descriptor structs, a non-zero return code becomes a RuntimeError.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+LIB_NAME = "libtilegym_b200.so"
+LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), LIB_NAME)
+
+TG_OK = 0
+ERR_NAMES = {
+    -2: "UNSUPPORTED_DTYPE",
+    -3: "LAUNCH_FAILED",
+    -4: "DEVICE_INIT_FAILED",
+    -5: "NULL_POINTER",
+    -6: "INVALID_ARGS",
+    -7: "TIMEOUT",
+    -8: "MISALIGNED",
+}
+
+# dtype codes of the reference FFI (src/tilegym/ops/cutile_rs/ffi_util.rs:26-35)
+DTYPE_CODES = {
+    torch.float32: 0,
+    torch.float16: 1,
+    torch.bfloat16: 2,
+    torch.int32: 3,
+    torch.int64: 4,
+    torch.float8_e5m2: 5,
+    torch.uint8: 6,
+    torch.float8_e4m3fn: 7,
+}
+
+
+class TensorDesc(ctypes.Structure):
+    _fields_ = [
+        ("ptr", ctypes.c_uint64),
+        ("ndim", ctypes.c_int32),
+        ("shape", ctypes.c_int64 * 5),
+        ("strides", ctypes.c_int64 * 5),
+        ("dtype", ctypes.c_int32),
+    ]
+
+
+class TileGymB200Error(RuntimeError):
+    def __init__(self, rc: int, msg: str):
+        super().__init__(f"tilegym_b200: {ERR_NAMES.get(rc, 'ERROR')} ({rc}): {msg}")
+        self.rc = rc
+
+
+_lib: Optional[ctypes.CDLL] = None
+
+# name -> (restype, argtypes); the list the symbol-export test walks.
+_P = ctypes.POINTER(TensorDesc)
+SIGNATURES = {
+    "tg_version": (ctypes.c_int32, []),
+    "tg_last_error_string": (ctypes.c_char_p, []),
+    "tg_fp8_gemm_workspace_bytes": (ctypes.c_uint64, [ctypes.c_int64] * 3),
+    "tg_fp8_gemm_pertensor": (
+        ctypes.c_int32,
+        [_P, _P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_float, _P, ctypes.c_float, ctypes.c_uint64,
+         ctypes.c_uint64, ctypes.c_int32, ctypes.c_uint64],
+    ),
+    "tg_fp8_gemm_blockscaled": (
+        ctypes.c_int32,
+        [_P, _P, _P, _P, _P, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int32,
+         ctypes.c_uint64],
+    ),
+    "tg_act_quant": (ctypes.c_int32, [_P, _P, _P, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64]),
+    "tg_weight_dequant": (ctypes.c_int32, [_P, _P, _P, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64]),
+    "tg_quant_pertensor": (
+        ctypes.c_int32,
+        [_P, ctypes.c_uint64, _P, ctypes.c_uint64, ctypes.c_int32, ctypes.c_uint64],
+    ),
+    "tg_weight_quant_block": (ctypes.c_int32, [_P, _P, _P, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64]),
+    "tg_device_status": (ctypes.c_int32, [ctypes.c_int32, ctypes.POINTER(ctypes.c_int32)]),
+}
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded shared library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m tilegym_b200.build` "
+                "(there is no fallback implementation)"
+            )
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = handle
+    return _lib
+
+
+def desc(t: Optional[torch.Tensor]) -> Optional[TensorDesc]:
+    """Descriptor of a tensor (None passes through as a NULL pointer)."""
+    if t is None:
+        return None
+    if t.dim() > 5:
+        raise ValueError("tensors of more than 5 dimensions are not supported")
+    code = DTYPE_CODES.get(t.dtype)
+    if code is None:
+        raise TileGymB200Error(-2, f"dtype {t.dtype} has no code in the C ABI")
+    d = TensorDesc()
+    d.ptr = t.data_ptr()
+    d.ndim = t.dim()
+    for i in range(t.dim()):
+        d.shape[i] = t.shape[i]
+        d.strides[i] = t.stride(i)
+    d.dtype = code
+    return d
+
+
+def ref(d: Optional[TensorDesc]):
+    return ctypes.byref(d) if d is not None else None
+
+
+def check_rc(rc: int) -> None:
+    if rc != TG_OK:
+        raise TileGymB200Error(rc, lib().tg_last_error_string().decode("utf-8", "replace"))
+
+
+def device_status(device_index: int) -> None:
+    """Synchronises the device and raises if a kernel's bounded wait expired."""
+    detail = ctypes.c_int32(0)
+    check_rc(lib().tg_device_status(device_index, ctypes.byref(detail)))

@@ -1,0 +1,512 @@
+// C ABI of the library: argument validation, TMA tensor maps, tile / split-K
+// selection and kernel launches.  Validation comes first in every entry point
+// and touches no CUDA state, so wrong calls are rejected the same way with or
+// without a GPU in the machine.
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "tg_internal.h"
+
+namespace tg {
+namespace {
+
+thread_local char g_err[512] = "";
+
+int32_t fail(int32_t rc, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return rc;
+}
+
+// Device status word written by a kernel whose bounded wait expired.
+__device__ int32_t g_status_word;
+
+constexpr int kMaxDevices = 64;
+struct DeviceState {
+  bool ready = false;
+  int num_sms = 0;
+  int32_t* status = nullptr;
+};
+DeviceState g_dev[kMaxDevices];
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+struct DeviceGuard {
+  int prev = -1;
+  bool changed = false;
+  cudaError_t err = cudaSuccess;
+  explicit DeviceGuard(int dev) {
+    err = cudaGetDevice(&prev);
+    if (err == cudaSuccess && prev != dev) {
+      err = cudaSetDevice(dev);
+      changed = (err == cudaSuccess);
+    }
+  }
+  ~DeviceGuard() {
+    if (changed) cudaSetDevice(prev);
+  }
+};
+
+// Called with `dev` current.
+int32_t init_device(int dev) {
+  if (dev < 0 || dev >= kMaxDevices) return fail(TG_ERR_DEVICE, "device id %d out of range", dev);
+  DeviceState& st = g_dev[dev];
+  if (st.ready) return TG_OK;
+  int major = 0, minor = 0, sms = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TG_ERR_DEVICE, "cannot query CUDA device %d (is there a GPU?)", dev);
+  }
+  if (major != 10) return fail(TG_ERR_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only", dev, major, minor);
+  if (g_encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess || fn == nullptr) {
+      cudaGetLastError();
+      return fail(TG_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from the driver");
+    }
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  void* sp = nullptr;
+  if (cudaGetSymbolAddress(&sp, g_status_word) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TG_ERR_DEVICE, "cannot resolve the status word on device %d", dev);
+  }
+  st.status = static_cast<int32_t*>(sp);
+  st.num_sms = sms;
+  st.ready = true;
+  return TG_OK;
+}
+
+int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return (v && *v) ? atoi(v) : dflt;
+}
+
+// 2-D map over a row-major e4m3 matrix [rows, K] with row pitch `pitch` bytes;
+// boxes of 128 bytes (one swizzle row) x box_rows rows; out-of-range elements read as zero.
+int32_t make_map(CUtensorMap* map, uint64_t ptr, int64_t rows, int64_t K, int64_t pitch, int box_rows) {
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch)};
+  cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, reinterpret_cast<void*>(ptr), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(TG_ERR_ARGS, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  return TG_OK;
+}
+
+bool is_out_dtype(int32_t d) { return d == TG_F32 || d == TG_F16 || d == TG_BF16; }
+int esize(int32_t d) { return d == TG_F32 ? 4 : (d == TG_F16 || d == TG_BF16) ? 2 : 1; }
+
+// A 2-D e4m3 operand with unit inner stride, 16-byte aligned base and pitch.
+int32_t check_operand(const TgTensorDesc* t, const char* name) {
+  if (t == nullptr) return fail(TG_ERR_NULL, "%s descriptor is null", name);
+  if (t->dtype != TG_F8E4M3) return fail(TG_ERR_DTYPE, "%s must be float8_e4m3fn (dtype code 7), got %d", name, t->dtype);
+  if (t->ndim != 2) return fail(TG_ERR_ARGS, "%s must be 2-D, got %d-D", name, t->ndim);
+  if (t->shape[0] < 0 || t->shape[1] <= 0) return fail(TG_ERR_ARGS, "%s has a bad shape", name);
+  if (t->strides[1] != 1 || t->strides[0] < t->shape[1]) return fail(TG_ERR_ARGS, "%s rows must be contiguous", name);
+  if (t->shape[0] > 0 && t->ptr == 0) return fail(TG_ERR_NULL, "%s data pointer is null", name);
+  if ((t->ptr & 15u) != 0 || (t->strides[0] & 15) != 0)
+    return fail(TG_ERR_ALIGN, "%s needs a 16-byte aligned base and row pitch (K %% 16 == 0) for TMA", name);
+  if (t->shape[0] > 0x7fffffff || t->shape[1] > 0x7fffffff) return fail(TG_ERR_ARGS, "%s is too large", name);
+  return TG_OK;
+}
+
+int32_t check_output(const TgTensorDesc* C, int64_t M, int64_t N) {
+  if (C == nullptr) return fail(TG_ERR_NULL, "C descriptor is null");
+  if (!is_out_dtype(C->dtype)) return fail(TG_ERR_DTYPE, "C must be f32, f16 or bf16, got dtype code %d", C->dtype);
+  if (C->ndim != 2 || C->shape[0] != M || C->shape[1] != N)
+    return fail(TG_ERR_ARGS, "C must have shape [%lld, %lld]", static_cast<long long>(M), static_cast<long long>(N));
+  if (C->strides[1] != 1 || C->strides[0] < N) return fail(TG_ERR_ARGS, "C rows must be contiguous");
+  if (M > 0 && N > 0 && C->ptr == 0) return fail(TG_ERR_NULL, "C data pointer is null");
+  if ((C->ptr & static_cast<uint64_t>(esize(C->dtype) - 1)) != 0) return fail(TG_ERR_ALIGN, "C is not element aligned");
+  return TG_OK;
+}
+
+constexpr uint64_t kWsCounterBytes = 64ull << 10;
+constexpr uint64_t kWsPartialBytes = 48ull << 20;
+
+// Split K only when the tiles alone leave most SMs idle.
+void choose_splits(int tiles, int num_kb, int num_sms, int64_t tile_floats, int target_ctas, int min_kb, int* splits,
+                   int* kbps) {
+  int s = 1;
+  if (tiles * 2 <= target_ctas && num_kb >= 2 * min_kb) {
+    s = target_ctas / tiles;
+    const int max_by_k = num_kb / min_kb;
+    if (s > max_by_k) s = max_by_k;
+    while (s > 1 && static_cast<uint64_t>(tiles) * s * tile_floats * 4 > kWsPartialBytes) --s;
+    if (s < 1) s = 1;
+  }
+  s = env_int("TILEGYM_B200_SPLITS", s);
+  if (s < 1) s = 1;
+  if (s > num_kb) s = num_kb;
+  int per = (num_kb + s - 1) / s;
+  s = (num_kb + per - 1) / per;  // every split owns at least one k-block
+  (void)num_sms;
+  *splits = s;
+  *kbps = per;
+}
+
+int choose_bn(int64_t M, int64_t N, int num_sms) {
+  // Estimated time = waves x tile width x a per-width efficiency factor
+  // (narrow tiles re-read A from shared memory more often per flop).
+  const int cand[3] = {256, 128, 64};
+  const double penalty[3] = {1.0, 1.12, 1.5};
+  int best = 256;
+  double best_cost = 1e300;
+  const int64_t tm = (M + 128 - 1) / 128;
+  for (int i = 0; i < 3; ++i) {
+    const int64_t tn = (N + cand[i] - 1) / cand[i];
+    const int64_t waves = (tm * tn + num_sms - 1) / num_sms;
+    const double cost = static_cast<double>(waves) * cand[i] * penalty[i];
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = cand[i];
+    }
+  }
+  return best;
+}
+
+}  // namespace
+}  // namespace tg
+
+using namespace tg;
+
+extern "C" {
+
+int32_t tg_version(void) { return 100; }
+
+const char* tg_last_error_string(void) { return g_err; }
+
+uint64_t tg_fp8_gemm_workspace_bytes(int64_t, int64_t, int64_t) { return kWsCounterBytes + kWsPartialBytes; }
+
+int32_t tg_fp8_gemm_pertensor(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B, uint64_t scale_a,
+                              uint64_t scale_b, float alpha, const TgTensorDesc* bias, float beta, uint64_t workspace,
+                              uint64_t workspace_bytes, int32_t device_id, uint64_t stream) {
+  int32_t rc;
+  if ((rc = check_operand(A, "A")) != TG_OK) return rc;
+  if ((rc = check_operand(B, "B")) != TG_OK) return rc;
+  const int64_t M = A->shape[0], K = A->shape[1], N = B->shape[0];
+  if (B->shape[1] != K) return fail(TG_ERR_ARGS, "A is [M,%lld] but B is [N,%lld]: K must match", (long long)K, (long long)B->shape[1]);
+  if ((rc = check_output(C, M, N)) != TG_OK) return rc;
+  if (bias != nullptr) {
+    if (bias->dtype != TG_F32 && bias->dtype != TG_BF16 && bias->dtype != TG_F16)
+      return fail(TG_ERR_DTYPE, "bias must be f32, f16 or bf16");
+    if (bias->ndim != 1 || bias->shape[0] != N || bias->strides[0] != 1)
+      return fail(TG_ERR_ARGS, "bias must be a contiguous vector of N elements");
+    if (bias->ptr == 0 && N > 0) return fail(TG_ERR_NULL, "bias data pointer is null");
+  }
+  if ((scale_a & 3u) || (scale_b & 3u)) return fail(TG_ERR_ALIGN, "scale pointers must be 4-byte aligned");
+  if (M == 0 || N == 0) return TG_OK;
+
+  DeviceGuard guard(device_id);
+  if (guard.err != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TG_ERR_DEVICE, "cannot select CUDA device %d", device_id);
+  }
+  if ((rc = init_device(device_id)) != TG_OK) return rc;
+  const DeviceState& st = g_dev[device_id];
+  cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = static_cast<int32_t>(M);
+  p.N = static_cast<int32_t>(N);
+  p.K = static_cast<int32_t>(K);
+  p.num_kb = static_cast<int32_t>((K + 127) / 128);
+  p.C = reinterpret_cast<void*>(C->ptr);
+  p.ldc = C->strides[0];
+  p.out_dtype = C->dtype;
+  p.scale_a = reinterpret_cast<const float*>(scale_a);
+  p.scale_b = reinterpret_cast<const float*>(scale_b);
+  p.alpha = alpha;
+  p.beta = beta;
+  p.bias = bias ? reinterpret_cast<const void*>(bias->ptr) : nullptr;
+  p.bias_dtype = bias ? bias->dtype : TG_F32;
+  p.status = st.status;
+  p.ws_counters = reinterpret_cast<uint32_t*>(workspace);
+  p.ws_partial = reinterpret_cast<float*>(workspace + kWsCounterBytes);
+  const bool have_ws = workspace != 0 && workspace_bytes >= kWsCounterBytes + kWsPartialBytes;
+
+  const char* force = getenv("TILEGYM_B200_FORCE_PATH");
+  bool small = M <= 64;
+  if (force && !strcmp(force, "gemm")) small = false;
+  if (force && !strcmp(force, "smallm") && M <= 64) small = true;
+
+  CUtensorMap tmA, tmB;
+  if (small) {
+    const int mp = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    p.tiles_m = 1;
+    p.tiles_n = static_cast<int32_t>((N + 127) / 128);
+    if (have_ws && p.tiles_n * 4 <= static_cast<int64_t>(kWsCounterBytes / 4))
+      choose_splits(p.tiles_n, p.num_kb, st.num_sms, static_cast<int64_t>(mp) * 128, 2 * st.num_sms, 2, &p.splits,
+                    &p.kb_per_split);
+    else {
+      p.splits = 1;
+      p.kb_per_split = p.num_kb;
+    }
+    if ((rc = make_map(&tmB, B->ptr, N, K, B->strides[0], 128)) != TG_OK) return rc;
+    if ((rc = make_map(&tmA, A->ptr, M, K, A->strides[0], mp)) != TG_OK) return rc;
+    cudaError_t e = launch_gemm_smallm(tmB, tmA, p, mp, cs);
+    if (e != cudaSuccess) return fail(TG_ERR_LAUNCH, "small-M GEMM launch failed: %s", cudaGetErrorString(e));
+    return TG_OK;
+  }
+
+  int bn = choose_bn(M, N, st.num_sms);
+  bn = env_int("TILEGYM_B200_BN", bn);
+  if (bn != 256 && bn != 128 && bn != 64) return fail(TG_ERR_ARGS, "TILEGYM_B200_BN must be 64, 128 or 256");
+  p.tiles_m = static_cast<int32_t>((M + 127) / 128);
+  p.tiles_n = static_cast<int32_t>((N + bn - 1) / bn);
+  const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+  if (tiles > 0x3fffffff) return fail(TG_ERR_ARGS, "problem has too many tiles");
+  if (have_ws && tiles * 4 <= static_cast<int64_t>(kWsCounterBytes / 4))
+    choose_splits(static_cast<int>(tiles), p.num_kb, st.num_sms, 128ll * bn, st.num_sms, 4, &p.splits, &p.kb_per_split);
+  else {
+    p.splits = 1;
+    p.kb_per_split = p.num_kb;
+  }
+  if ((rc = make_map(&tmA, A->ptr, M, K, A->strides[0], 128)) != TG_OK) return rc;
+  if ((rc = make_map(&tmB, B->ptr, N, K, B->strides[0], bn)) != TG_OK) return rc;
+  cudaError_t e = launch_gemm_pertensor(tmA, tmB, p, bn, st.num_sms, cs);
+  if (e != cudaSuccess) return fail(TG_ERR_LAUNCH, "GEMM launch failed: %s", cudaGetErrorString(e));
+  return TG_OK;
+}
+
+int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
+                                const TgTensorDesc* As, const TgTensorDesc* Bs, int32_t block_n, int32_t block_k,
+                                uint64_t workspace, uint64_t workspace_bytes, int32_t device_id, uint64_t stream) {
+  int32_t rc;
+  if ((rc = check_operand(A, "A")) != TG_OK) return rc;
+  if ((rc = check_operand(B, "B")) != TG_OK) return rc;
+  if (As == nullptr || Bs == nullptr) return fail(TG_ERR_NULL, "scale descriptor is null");
+  if (block_n != 128 || block_k != 128)
+    return fail(TG_ERR_ARGS, "only block_size [128, 128] is implemented (the tile is locked to the quantisation block), got [%d, %d]", block_n, block_k);
+  const int64_t M = A->shape[0], K = A->shape[1], N = B->shape[0];
+  if (B->shape[1] != K) return fail(TG_ERR_ARGS, "A is [M,%lld] but B is [N,%lld]: K must match", (long long)K, (long long)B->shape[1]);
+  if ((rc = check_output(C, M, N)) != TG_OK) return rc;
+  const int64_t KB = (K + 127) / 128, NB = (N + 127) / 128;
+  if (As->dtype != TG_F32 || Bs->dtype != TG_F32) return fail(TG_ERR_DTYPE, "As and Bs must be f32");
+  if (As->ndim != 2 || As->shape[0] != M || As->shape[1] != KB || As->strides[1] != 1 || As->strides[0] < KB)
+    return fail(TG_ERR_ARGS, "As must be [M, ceil(K/128)] = [%lld, %lld] with contiguous rows", (long long)M, (long long)KB);
+  if (Bs->ndim != 2 || Bs->shape[0] != NB || Bs->shape[1] != KB || Bs->strides[1] != 1 || Bs->strides[0] < KB)
+    return fail(TG_ERR_ARGS, "Bs must be [ceil(N/128), ceil(K/128)] = [%lld, %lld] with contiguous rows", (long long)NB, (long long)KB);
+  if ((M > 0 && As->ptr == 0) || (N > 0 && Bs->ptr == 0)) return fail(TG_ERR_NULL, "scale data pointer is null");
+  if ((As->ptr & 3u) || (Bs->ptr & 3u)) return fail(TG_ERR_ALIGN, "scale pointers must be 4-byte aligned");
+  if (M == 0 || N == 0) return TG_OK;
+
+  DeviceGuard guard(device_id);
+  if (guard.err != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TG_ERR_DEVICE, "cannot select CUDA device %d", device_id);
+  }
+  if ((rc = init_device(device_id)) != TG_OK) return rc;
+  const DeviceState& st = g_dev[device_id];
+  cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = static_cast<int32_t>(M);
+  p.N = static_cast<int32_t>(N);
+  p.K = static_cast<int32_t>(K);
+  p.num_kb = static_cast<int32_t>(KB);
+  p.tiles_m = static_cast<int32_t>((M + 127) / 128);
+  p.tiles_n = static_cast<int32_t>(NB);
+  p.C = reinterpret_cast<void*>(C->ptr);
+  p.ldc = C->strides[0];
+  p.out_dtype = C->dtype;
+  p.alpha = 1.0f;
+  p.beta = 0.0f;
+  p.As = reinterpret_cast<const float*>(As->ptr);
+  p.Bs = reinterpret_cast<const float*>(Bs->ptr);
+  p.ldas = As->strides[0];
+  p.ldbs = Bs->strides[0];
+  p.status = st.status;
+  p.ws_counters = reinterpret_cast<uint32_t*>(workspace);
+  p.ws_partial = reinterpret_cast<float*>(workspace + kWsCounterBytes);
+  const bool have_ws = workspace != 0 && workspace_bytes >= kWsCounterBytes + kWsPartialBytes;
+  const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+  if (tiles > 0x3fffffff) return fail(TG_ERR_ARGS, "problem has too many tiles");
+  if (have_ws && tiles * 8 <= static_cast<int64_t>(kWsCounterBytes / 4))
+    choose_splits(static_cast<int>(tiles), p.num_kb, st.num_sms, 128ll * 128, st.num_sms, 4, &p.splits, &p.kb_per_split);
+  else {
+    p.splits = 1;
+    p.kb_per_split = p.num_kb;
+  }
+  CUtensorMap tmA, tmB;
+  if ((rc = make_map(&tmA, A->ptr, M, K, A->strides[0], 128)) != TG_OK) return rc;
+  if ((rc = make_map(&tmB, B->ptr, N, K, B->strides[0], 128)) != TG_OK) return rc;
+  cudaError_t e = launch_gemm_blockscaled(tmA, tmB, p, st.num_sms, cs);
+  if (e != cudaSuccess) return fail(TG_ERR_LAUNCH, "block-scaled GEMM launch failed: %s", cudaGetErrorString(e));
+  return TG_OK;
+}
+
+static int32_t check_dense(const TgTensorDesc* t, const char* name) {
+  if (t == nullptr) return fail(TG_ERR_NULL, "%s descriptor is null", name);
+  if (t->ndim < 1 || t->ndim > 5) return fail(TG_ERR_ARGS, "%s must have 1 to 5 dimensions", name);
+  int64_t expect = 1;
+  for (int d = t->ndim - 1; d >= 0; --d) {
+    if (t->shape[d] < 0) return fail(TG_ERR_ARGS, "%s has a negative extent", name);
+    if (t->shape[d] != 1 && t->strides[d] != expect) return fail(TG_ERR_ARGS, "%s must be contiguous", name);
+    expect *= t->shape[d];
+  }
+  return TG_OK;
+}
+static int64_t numel(const TgTensorDesc* t) {
+  int64_t n = 1;
+  for (int d = 0; d < t->ndim; ++d) n *= t->shape[d];
+  return n;
+}
+static bool is_in_dtype(int32_t d) { return d == TG_F32 || d == TG_F16 || d == TG_BF16; }
+
+int32_t tg_act_quant(const TgTensorDesc* Y, const TgTensorDesc* S, const TgTensorDesc* X, int32_t block,
+                     int32_t device_id, uint64_t stream) {
+  int32_t rc;
+  if ((rc = check_dense(X, "X")) != TG_OK) return rc;
+  if ((rc = check_dense(Y, "Y")) != TG_OK) return rc;
+  if ((rc = check_dense(S, "S")) != TG_OK) return rc;
+  if (!is_in_dtype(X->dtype)) return fail(TG_ERR_DTYPE, "X must be f32, f16 or bf16");
+  if (Y->dtype != TG_F8E4M3) return fail(TG_ERR_DTYPE, "Y must be float8_e4m3fn");
+  if (S->dtype != TG_F32) return fail(TG_ERR_DTYPE, "S must be f32");
+  if (block != 128) return fail(TG_ERR_ARGS, "only block_size 128 is implemented, got %d", block);
+  const int64_t n = numel(X);
+  const int64_t K = X->shape[X->ndim - 1];
+  if (K % block != 0) return fail(TG_ERR_ARGS, "last dimension %lld is not a multiple of block_size %d", (long long)K, block);
+  if (numel(Y) != n || numel(S) != n / block) return fail(TG_ERR_ARGS, "Y / S sizes do not match X");
+  if (n == 0) return TG_OK;
+  if (X->ptr == 0 || Y->ptr == 0 || S->ptr == 0) return fail(TG_ERR_NULL, "data pointer is null");
+  if ((X->ptr & 15u) || (Y->ptr & 3u) || (S->ptr & 3u)) return fail(TG_ERR_ALIGN, "X must be 16-byte, Y and S 4-byte aligned");
+  DeviceGuard guard(device_id);
+  if (guard.err != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TG_ERR_DEVICE, "cannot select CUDA device %d", device_id);
+  }
+  if ((rc = init_device(device_id)) != TG_OK) return rc;
+  cudaError_t e = launch_act_quant(reinterpret_cast<void*>(Y->ptr), reinterpret_cast<float*>(S->ptr),
+                                   reinterpret_cast<const void*>(X->ptr), X->dtype, n / block,
+                                   reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(TG_ERR_LAUNCH, "act_quant launch failed: %s", cudaGetErrorString(e));
+  return TG_OK;
+}
+
+int32_t tg_weight_dequant(const TgTensorDesc* Y, const TgTensorDesc* X, const TgTensorDesc* S, int32_t block,
+                          int32_t device_id, uint64_t stream) {
+  int32_t rc;
+  if ((rc = check_dense(X, "X")) != TG_OK) return rc;
+  if ((rc = check_dense(Y, "Y")) != TG_OK) return rc;
+  if ((rc = check_dense(S, "S")) != TG_OK) return rc;
+  if (X->dtype != TG_F8E4M3) return fail(TG_ERR_DTYPE, "X must be float8_e4m3fn");
+  if (!is_out_dtype(Y->dtype)) return fail(TG_ERR_DTYPE, "Y must be f32, f16 or bf16");
+  if (S->dtype != TG_F32) return fail(TG_ERR_DTYPE, "S must be f32");
+  if (block != 128) return fail(TG_ERR_ARGS, "only block_size 128 is implemented, got %d", block);
+  if (X->ndim != 2 || Y->ndim != 2 || S->ndim != 2) return fail(TG_ERR_ARGS, "X, Y and S must be 2-D");
+  const int64_t M = X->shape[0], N = X->shape[1];
+  if (Y->shape[0] != M || Y->shape[1] != N) return fail(TG_ERR_ARGS, "Y must have X's shape");
+  if (S->shape[0] != (M + 127) / 128 || S->shape[1] != (N + 127) / 128)
+    return fail(TG_ERR_ARGS, "S must be [ceil(M/128), ceil(N/128)]");
+  if (M == 0 || N == 0) return TG_OK;
+  if (X->ptr == 0 || Y->ptr == 0 || S->ptr == 0) return fail(TG_ERR_NULL, "data pointer is null");
+  DeviceGuard guard(device_id);
+  if (guard.err != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TG_ERR_DEVICE, "cannot select CUDA device %d", device_id);
+  }
+  if ((rc = init_device(device_id)) != TG_OK) return rc;
+  cudaError_t e = launch_weight_dequant(reinterpret_cast<void*>(Y->ptr), Y->dtype, reinterpret_cast<const uint8_t*>(X->ptr),
+                                        reinterpret_cast<const float*>(S->ptr), M, N, S->shape[1],
+                                        reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(TG_ERR_LAUNCH, "weight_dequant launch failed: %s", cudaGetErrorString(e));
+  return TG_OK;
+}
+
+int32_t tg_quant_pertensor(const TgTensorDesc* Y, uint64_t scale_out, const TgTensorDesc* X, uint64_t amax_scratch,
+                           int32_t device_id, uint64_t stream) {
+  int32_t rc;
+  if ((rc = check_dense(X, "X")) != TG_OK) return rc;
+  if ((rc = check_dense(Y, "Y")) != TG_OK) return rc;
+  if (!is_in_dtype(X->dtype)) return fail(TG_ERR_DTYPE, "X must be f32, f16 or bf16");
+  if (Y->dtype != TG_F8E4M3) return fail(TG_ERR_DTYPE, "Y must be float8_e4m3fn");
+  if (scale_out == 0 || amax_scratch == 0) return fail(TG_ERR_NULL, "scale_out / amax_scratch pointer is null");
+  if ((scale_out & 3u) || (amax_scratch & 3u)) return fail(TG_ERR_ALIGN, "scale_out / amax_scratch must be 4-byte aligned");
+  const int64_t n = numel(X);
+  if (numel(Y) != n) return fail(TG_ERR_ARGS, "Y must have as many elements as X");
+  if (n > 0 && (X->ptr == 0 || Y->ptr == 0)) return fail(TG_ERR_NULL, "data pointer is null");
+  if ((X->ptr & 15u) || (Y->ptr & 3u)) return fail(TG_ERR_ALIGN, "X must be 16-byte and Y 4-byte aligned");
+  DeviceGuard guard(device_id);
+  if (guard.err != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TG_ERR_DEVICE, "cannot select CUDA device %d", device_id);
+  }
+  if ((rc = init_device(device_id)) != TG_OK) return rc;
+  cudaError_t e = launch_quant_pertensor(reinterpret_cast<uint8_t*>(Y->ptr), reinterpret_cast<float*>(scale_out),
+                                         reinterpret_cast<const void*>(X->ptr), X->dtype, n,
+                                         reinterpret_cast<uint32_t*>(amax_scratch), g_dev[device_id].num_sms,
+                                         reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(TG_ERR_LAUNCH, "quant_pertensor launch failed: %s", cudaGetErrorString(e));
+  return TG_OK;
+}
+
+int32_t tg_weight_quant_block(const TgTensorDesc* Y, const TgTensorDesc* S, const TgTensorDesc* X, int32_t block,
+                              int32_t device_id, uint64_t stream) {
+  int32_t rc;
+  if ((rc = check_dense(X, "X")) != TG_OK) return rc;
+  if ((rc = check_dense(Y, "Y")) != TG_OK) return rc;
+  if ((rc = check_dense(S, "S")) != TG_OK) return rc;
+  if (!is_in_dtype(X->dtype)) return fail(TG_ERR_DTYPE, "X must be f32, f16 or bf16");
+  if (Y->dtype != TG_F8E4M3) return fail(TG_ERR_DTYPE, "Y must be float8_e4m3fn");
+  if (S->dtype != TG_F32) return fail(TG_ERR_DTYPE, "S must be f32");
+  if (block != 128) return fail(TG_ERR_ARGS, "only block_size 128 is implemented, got %d", block);
+  if (X->ndim != 2 || Y->ndim != 2 || S->ndim != 2) return fail(TG_ERR_ARGS, "X, Y and S must be 2-D");
+  const int64_t N = X->shape[0], K = X->shape[1];
+  if (Y->shape[0] != N || Y->shape[1] != K) return fail(TG_ERR_ARGS, "Y must have X's shape");
+  if (S->shape[0] != (N + 127) / 128 || S->shape[1] != (K + 127) / 128)
+    return fail(TG_ERR_ARGS, "S must be [ceil(N/128), ceil(K/128)]");
+  if (N == 0 || K == 0) return TG_OK;
+  if (X->ptr == 0 || Y->ptr == 0 || S->ptr == 0) return fail(TG_ERR_NULL, "data pointer is null");
+  DeviceGuard guard(device_id);
+  if (guard.err != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TG_ERR_DEVICE, "cannot select CUDA device %d", device_id);
+  }
+  if ((rc = init_device(device_id)) != TG_OK) return rc;
+  cudaError_t e = launch_weight_quant_block(reinterpret_cast<uint8_t*>(Y->ptr), reinterpret_cast<float*>(S->ptr),
+                                            reinterpret_cast<const void*>(X->ptr), X->dtype, N, K, S->shape[1],
+                                            reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(TG_ERR_LAUNCH, "weight_quant_block launch failed: %s", cudaGetErrorString(e));
+  return TG_OK;
+}
+
+int32_t tg_device_status(int32_t device_id, int32_t* detail) {
+  if (detail) *detail = 0;
+  DeviceGuard guard(device_id);
+  if (guard.err != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TG_ERR_DEVICE, "cannot select CUDA device %d", device_id);
+  }
+  int32_t rc;
+  if ((rc = init_device(device_id)) != TG_OK) return rc;
+  int32_t word = 0;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpy(&word, g_dev[device_id].status, sizeof(word), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return fail(TG_ERR_LAUNCH, "device %d reports: %s", device_id, cudaGetErrorString(e));
+  if (word != 0) {
+    int32_t zero = 0;
+    cudaMemcpy(g_dev[device_id].status, &zero, sizeof(zero), cudaMemcpyHostToDevice);
+    if (detail) *detail = word;
+    return fail(TG_ERR_TIMEOUT, "a bounded device-side wait expired (role %d, site %d)", word / 1000, word % 1000);
+  }
+  return TG_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,311 @@
+// e4m3 quantisers and the block dequantiser that sit either side of the FP8
+// GEMMs.  All of them are single-pass streaming kernels bound by HBM
+// bandwidth: 16-byte accesses, one warp per 128-element quantisation block
+// where a block reduction is needed.  Division is IEEE (div.rn): an
+// approximate reciprocal moves values across e4m3 rounding boundaries.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+#include "tg_internal.h"
+
+namespace tg {
+
+namespace {
+
+constexpr float kE4M3Max = 448.0f;
+
+__device__ __forceinline__ uint8_t to_e4m3(float v) {
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+__device__ __forceinline__ float from_e4m3(uint8_t b) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(b), __NV_E4M3);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// Loads 4 consecutive elements as fp32 (8- or 16-byte access).
+template <typename T>
+__device__ __forceinline__ void load4(const T* src, float (&v)[4]) {
+  if constexpr (sizeof(T) == 4) {
+    float4 t = *reinterpret_cast<const float4*>(src);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else {
+    uint2 t = *reinterpret_cast<const uint2*>(src);
+    const T* e = reinterpret_cast<const T*>(&t);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = to_f32<T>(e[j]);
+  }
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ---------------------------------------------------------------- act_quant
+// One warp per block of 128 contiguous elements: lane l owns elements 4l..4l+3.
+// Follows src/tilegym/suites/unsloth/cutile/fp8.py:77-120 (amax/448, 1.0 for a
+// zero block, IEEE division, cast to e4m3).
+template <typename T>
+__global__ void __launch_bounds__(256) tg_act_quant_kernel(uint8_t* __restrict__ y, float* __restrict__ s,
+                                                           const T* __restrict__ x, int64_t n_blocks) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps_total = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (int64_t b = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); b < n_blocks;
+       b += warps_total) {
+    float v[4];
+    load4<T>(x + b * 128 + lane * 4, v);
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    amax = warp_max(amax);
+    float scale = __fdiv_rn(amax, kE4M3Max);
+    if (scale == 0.f) scale = 1.0f;
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) packed |= static_cast<uint32_t>(to_e4m3(__fdiv_rn(v[j], scale))) << (8 * j);
+    *reinterpret_cast<uint32_t*>(y + b * 128 + lane * 4) = packed;
+    if (lane == 0) s[b] = scale;
+  }
+}
+
+// ----------------------------------------------------------- weight_dequant
+// y[i,j] = x[i,j] * s[i/128, j/128]; each thread converts 16 consecutive
+// columns (one 16-byte load) when N % 16 == 0, else one element.
+// Follows src/tilegym/suites/unsloth/cutile/fp8.py:36-71.
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(256) tg_weight_dequant_kernel(T* __restrict__ y, const uint8_t* __restrict__ x,
+                                                                const float* __restrict__ s, int64_t M, int64_t N,
+                                                                int64_t lds, bool vec) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  if (vec) {
+    const int64_t groups_per_row = N / 16;
+    const int64_t total = M * groups_per_row;
+    for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < total; g += stride) {
+      const int64_t i = g / groups_per_row;
+      const int64_t j = (g - i * groups_per_row) * 16;
+      const float sc = __ldg(s + (i >> 7) * lds + (j >> 7));
+      const uint4 raw = *reinterpret_cast<const uint4*>(x + i * N + j);
+      const uint8_t* b = reinterpret_cast<const uint8_t*>(&raw);
+      alignas(16) T out[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) out[k] = from_f32<T>(from_e4m3(b[k]) * sc);
+      uint4* dst = reinterpret_cast<uint4*>(y + i * N + j);
+      const uint4* src = reinterpret_cast<const uint4*>(out);
+#pragma unroll
+      for (int k = 0; k < static_cast<int>(sizeof(T)); ++k) dst[k] = src[k];
+    }
+  } else {
+    const int64_t total = M * N;
+    for (int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride) {
+      const int64_t i = e / N, j = e - i * N;
+      y[e] = from_f32<T>(from_e4m3(x[e]) * __ldg(s + (i >> 7) * lds + (j >> 7)));
+    }
+  }
+}
+
+// ----------------------------------------------------------- per-tensor quant
+// Pass 1: amax of |x| via an atomic max on the fp32 bit pattern (monotone for
+// non-negative floats).  Pass 2: scale = amax/448 (1.0 if zero), quantise.
+template <typename T>
+__global__ void __launch_bounds__(256) tg_amax_kernel(const T* __restrict__ x, int64_t numel, uint32_t* amax_bits) {
+  float m = 0.f;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t n4 = numel / 4;
+  for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < n4; g += stride) {
+    float v[4];
+    load4<T>(x + g * 4, v);
+    m = fmaxf(m, fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))));
+  }
+  for (int64_t e = n4 * 4 + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < numel; e += stride)
+    m = fmaxf(m, fabsf(to_f32<T>(x[e])));
+  m = warp_max(m);
+  __shared__ float wm[8];
+  if ((threadIdx.x & 31) == 0) wm[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? wm[threadIdx.x] : 0.f;
+    t = warp_max(t);
+    if (threadIdx.x == 0) atomicMax(amax_bits, __float_as_uint(t));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) tg_quant_pertensor_kernel(uint8_t* __restrict__ y, float* scale_out,
+                                                                 const T* __restrict__ x, int64_t numel,
+                                                                 const uint32_t* amax_bits) {
+  float scale = __fdiv_rn(__uint_as_float(*amax_bits), kE4M3Max);
+  if (scale == 0.f) scale = 1.0f;
+  if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t n4 = numel / 4;
+  for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < n4; g += stride) {
+    float v[4];
+    load4<T>(x + g * 4, v);
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float qv = fminf(fmaxf(__fdiv_rn(v[j], scale), -kE4M3Max), kE4M3Max);
+      packed |= static_cast<uint32_t>(to_e4m3(qv)) << (8 * j);
+    }
+    *reinterpret_cast<uint32_t*>(y + g * 4) = packed;
+  }
+  for (int64_t e = n4 * 4 + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < numel; e += stride) {
+    float qv = fminf(fmaxf(__fdiv_rn(to_f32<T>(x[e]), scale), -kE4M3Max), kE4M3Max);
+    y[e] = to_e4m3(qv);
+  }
+}
+
+// ------------------------------------------------------- 128x128 weight quant
+// One CTA per 128 x 128 block; thread t owns columns 4*(t%32) .. +3 of rows
+// t/32, t/32+8, ... (16 rows), keeps them in registers across the block-wide
+// amax reduction, then quantises.  Edge blocks treat missing elements as zero.
+template <typename T>
+__global__ void __launch_bounds__(256) tg_weight_quant_block_kernel(uint8_t* __restrict__ y, float* __restrict__ s,
+                                                                    const T* __restrict__ x, int64_t N, int64_t K,
+                                                                    int64_t lds, bool vec) {
+  const int bi = blockIdx.y, bj = blockIdx.x;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int64_t col = static_cast<int64_t>(bj) * 128 + lane * 4;
+  float v[16][4];
+  float amax = 0.f;
+#pragma unroll
+  for (int r = 0; r < 16; ++r) {
+    const int64_t row = static_cast<int64_t>(bi) * 128 + w + 8 * r;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[r][j] = 0.f;
+    if (row < N) {
+      if (vec && col + 4 <= K) {
+        load4<T>(x + row * K + col, v[r]);
+      } else {
+        for (int j = 0; j < 4; ++j)
+          if (col + j < K) v[r][j] = to_f32<T>(x[row * K + col + j]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) amax = fmaxf(amax, fabsf(v[r][j]));
+  }
+  amax = warp_max(amax);
+  __shared__ float wm[8];
+  if (lane == 0) wm[w] = amax;
+  __syncthreads();
+  amax = wm[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) amax = fmaxf(amax, wm[i]);
+  float scale = __fdiv_rn(amax, kE4M3Max);
+  if (scale == 0.f) scale = 1.0f;
+  if (threadIdx.x == 0) s[static_cast<int64_t>(bi) * lds + bj] = scale;
+#pragma unroll
+  for (int r = 0; r < 16; ++r) {
+    const int64_t row = static_cast<int64_t>(bi) * 128 + w + 8 * r;
+    if (row >= N) continue;
+    uint8_t qb[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float qv = fminf(fmaxf(__fdiv_rn(v[r][j], scale), -kE4M3Max), kE4M3Max);
+      qb[j] = to_e4m3(qv);
+    }
+    if (vec && col + 4 <= K) {
+      *reinterpret_cast<uint32_t*>(y + row * K + col) =
+          static_cast<uint32_t>(qb[0]) | (static_cast<uint32_t>(qb[1]) << 8) | (static_cast<uint32_t>(qb[2]) << 16) |
+          (static_cast<uint32_t>(qb[3]) << 24);
+    } else {
+      for (int j = 0; j < 4; ++j)
+        if (col + j < K) y[row * K + col + j] = qb[j];
+    }
+  }
+}
+
+int grid_for(int64_t work_items, int threads, int cap) {
+  int64_t g = (work_items + threads - 1) / threads;
+  if (g < 1) g = 1;
+  if (g > cap) g = cap;
+  return static_cast<int>(g);
+}
+
+}  // namespace
+
+cudaError_t launch_act_quant(void* y, float* s, const void* x, int x_dtype, int64_t n_blocks, cudaStream_t stream) {
+  if (n_blocks == 0) return cudaSuccess;
+  const int grid = grid_for(n_blocks, 8, 148 * 32);
+  uint8_t* yy = static_cast<uint8_t*>(y);
+  if (x_dtype == TG_BF16)
+    tg_act_quant_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(yy, s, static_cast<const __nv_bfloat16*>(x), n_blocks);
+  else if (x_dtype == TG_F16)
+    tg_act_quant_kernel<__half><<<grid, 256, 0, stream>>>(yy, s, static_cast<const __half*>(x), n_blocks);
+  else
+    tg_act_quant_kernel<float><<<grid, 256, 0, stream>>>(yy, s, static_cast<const float*>(x), n_blocks);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_weight_dequant(void* y, int y_dtype, const uint8_t* x, const float* s, int64_t M, int64_t N,
+                                  int64_t lds, cudaStream_t stream) {
+  if (M == 0 || N == 0) return cudaSuccess;
+  const int esz = (y_dtype == TG_F32) ? 4 : 2;
+  const bool vec = (N % 16 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(y) & 15u) == 0) && ((N * esz) % 16 == 0);
+  const int64_t items = vec ? M * (N / 16) : M * N;
+  const int grid = grid_for(items, 256, 148 * 16);
+  if (y_dtype == TG_BF16)
+    tg_weight_dequant_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(y), x, s, M, N, lds, vec);
+  else if (y_dtype == TG_F16)
+    tg_weight_dequant_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<__half*>(y), x, s, M, N, lds, vec);
+  else
+    tg_weight_dequant_kernel<float><<<grid, 256, 0, stream>>>(static_cast<float*>(y), x, s, M, N, lds, vec);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_quant_pertensor(uint8_t* y, float* scale_out, const void* x, int x_dtype, int64_t numel,
+                                   uint32_t* amax_scratch, int num_sms, cudaStream_t stream) {
+  cudaError_t e = cudaMemsetAsync(amax_scratch, 0, sizeof(uint32_t), stream);
+  if (e != cudaSuccess) return e;
+  const int grid = grid_for((numel + 3) / 4, 256, num_sms * 8);
+  if (x_dtype == TG_BF16) {
+    const auto* xx = static_cast<const __nv_bfloat16*>(x);
+    tg_amax_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(xx, numel, amax_scratch);
+    tg_quant_pertensor_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(y, scale_out, xx, numel, amax_scratch);
+  } else if (x_dtype == TG_F16) {
+    const auto* xx = static_cast<const __half*>(x);
+    tg_amax_kernel<__half><<<grid, 256, 0, stream>>>(xx, numel, amax_scratch);
+    tg_quant_pertensor_kernel<__half><<<grid, 256, 0, stream>>>(y, scale_out, xx, numel, amax_scratch);
+  } else {
+    const auto* xx = static_cast<const float*>(x);
+    tg_amax_kernel<float><<<grid, 256, 0, stream>>>(xx, numel, amax_scratch);
+    tg_quant_pertensor_kernel<float><<<grid, 256, 0, stream>>>(y, scale_out, xx, numel, amax_scratch);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_weight_quant_block(uint8_t* y, float* s, const void* x, int x_dtype, int64_t N, int64_t K,
+                                      int64_t lds, cudaStream_t stream) {
+  if (N == 0 || K == 0) return cudaSuccess;
+  dim3 grid(static_cast<unsigned>((K + 127) / 128), static_cast<unsigned>((N + 127) / 128));
+  const bool vec = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(y) & 3u) == 0);
+  if (x_dtype == TG_BF16)
+    tg_weight_quant_block_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(y, s, static_cast<const __nv_bfloat16*>(x), N, K, lds, vec);
+  else if (x_dtype == TG_F16)
+    tg_weight_quant_block_kernel<__half><<<grid, 256, 0, stream>>>(y, s, static_cast<const __half*>(x), N, K, lds, vec);
+  else
+    tg_weight_quant_block_kernel<float><<<grid, 256, 0, stream>>>(y, s, static_cast<const float*>(x), N, K, lds, vec);
+  return cudaGetLastError();
+}
+
+}  // namespace tg

@@ -1,0 +1,60 @@
+// Internal declarations shared by the kernel translation units and the C ABI.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/tilegym_b200.h"
+
+namespace tg {
+
+// Codes written to the device status word by a wait that gave up
+// (status = role * 1000 + site), reported through tg_device_status().
+enum WaitRole : int { kRoleProducer = 1, kRoleMma = 2, kRoleEpilogue = 3 };
+
+struct GemmParams {
+  // problem
+  int32_t M, N, K;
+  int32_t num_kb;            // ceil(K / 128)
+  int32_t tiles_m, tiles_n;  // output tiles
+  // output
+  void* C;
+  int64_t ldc;        // elements
+  int32_t out_dtype;  // TG_F32 / TG_F16 / TG_BF16
+  // per-tensor epilogue
+  const float* scale_a;  // device scalar or nullptr
+  const float* scale_b;
+  float alpha, beta;
+  const void* bias;  // nullptr, f32 or bf16 [N]
+  int32_t bias_dtype;
+  // block-scaled epilogue
+  const float* As;  // [M, ldas]
+  const float* Bs;  // [ceil(N/128), ldbs]
+  int64_t ldas, ldbs;
+  // split-K (small-M and thin problems)
+  int32_t splits;         // K splits (1 = none)
+  int32_t kb_per_split;   // k-blocks per split
+  float* ws_partial;      // [splits, tiles..., 128*BN] fp32 partial tiles
+  uint32_t* ws_counters;  // one per output tile, zero on entry and on exit
+  // diagnostics
+  int32_t* status;  // device status word
+};
+
+// Launchers (each sets its kernel's shared-memory attribute once per device).
+cudaError_t launch_gemm_pertensor(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int bn,
+                                  int num_sms, cudaStream_t stream);
+cudaError_t launch_gemm_blockscaled(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
+                                    int num_sms, cudaStream_t stream);
+// Swap-AB split-K kernel for M <= 64: tmW boxes 128 weight rows, tmX boxes `mp` activation rows.
+cudaError_t launch_gemm_smallm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int mp,
+                               cudaStream_t stream);
+
+cudaError_t launch_act_quant(void* y, float* s, const void* x, int x_dtype, int64_t n_blocks, cudaStream_t stream);
+cudaError_t launch_weight_dequant(void* y, int y_dtype, const uint8_t* x, const float* s, int64_t M, int64_t N,
+                                  int64_t lds, cudaStream_t stream);
+cudaError_t launch_quant_pertensor(uint8_t* y, float* scale_out, const void* x, int x_dtype, int64_t numel,
+                                   uint32_t* amax_scratch, int num_sms, cudaStream_t stream);
+cudaError_t launch_weight_quant_block(uint8_t* y, float* s, const void* x, int x_dtype, int64_t N, int64_t K,
+                                      int64_t lds, cudaStream_t stream);
+
+}  // namespace tg

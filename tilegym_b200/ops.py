@@ -1,0 +1,338 @@
+"""Operator entry points: same names, arguments and error behaviour as the
+reference's operator stubs, routed to the sm_100a kernels through the C ABI.
+
+There is no dispatch table and no fallback: every function needs CUDA tensors
+and the built shared library, and raises otherwise.  All work is enqueued on
+`torch.cuda.current_stream()` without synchronising, like the reference
+(src/tilegym/suites/unsloth/cutile/fp8.py:424).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from . import _lib
+
+_OUT_DTYPES = (torch.float32, torch.float16, torch.bfloat16)
+_IN_DTYPES = (torch.float32, torch.float16, torch.bfloat16)
+_FP8 = torch.float8_e4m3fn
+
+# One zero-initialised scratch buffer per (device, stream): the split-K paths
+# keep partial sums and arrival counters there and leave the counters zero.
+_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+_amax_scratch: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def _need_cuda(*tensors: Optional[torch.Tensor]) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError(
+                "tilegym_b200 operators run on CUDA tensors only (there is no CPU implementation in this package)"
+            )
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f"tensors are on different devices: {dev} and {t.device}")
+    assert dev is not None
+    return dev
+
+
+def _stream(dev: torch.device) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def _workspace(dev: torch.device) -> torch.Tensor:
+    key = (dev.index, _stream(dev))
+    ws = _workspaces.get(key)
+    if ws is None:
+        nbytes = int(_lib.lib().tg_fp8_gemm_workspace_bytes(0, 0, 0))
+        ws = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+        _workspaces[key] = ws
+    return ws
+
+
+# ----------------------------------------------------------------------------
+# Block-scaled GEMM and its quantisers (reference: tilegym.suites.unsloth.ops)
+# ----------------------------------------------------------------------------
+def w8a8_block_fp8_matmul(
+    A: torch.Tensor,
+    B: torch.Tensor,
+    As: torch.Tensor,
+    Bs: torch.Tensor,
+    block_size: Optional[List[int]] = None,
+    output_dtype: torch.dtype = torch.float32,
+) -> torch.Tensor:
+    """Block-wise FP8 matrix multiplication (W8A8): C = dequant(A) @ dequant(B).T.
+
+    Signature and preconditions of src/tilegym/suites/unsloth/ops.py:240-265 and
+    src/tilegym/suites/unsloth/cutile/fp8.py:388-414: A (..., K) e4m3 contiguous,
+    B (N, K) e4m3 contiguous, As (..., ceil(K/block_k)) f32, Bs (ceil(N/block_n),
+    ceil(K/block_k)) f32; returns a new (..., N) tensor of `output_dtype`.
+    Differences: only block_size [128, 128] is implemented, and an output dtype
+    outside {f32, f16, bf16} is rejected (the reference silently computes f32).
+    """
+    if block_size is None:
+        block_n, block_k = 128, 128
+    else:
+        assert len(block_size) == 2
+        block_n, block_k = int(block_size[0]), int(block_size[1])
+    dev = _need_cuda(A, B, As, Bs)
+    assert B.ndim == 2 and B.is_contiguous() and Bs.ndim == 2
+    N, K = B.shape
+    assert A.shape[-1] == B.shape[-1]
+    assert A.shape[:-1] == As.shape[:-1] and A.is_contiguous()
+    assert math.ceil(A.shape[-1] / block_k) == As.shape[-1]
+    assert math.ceil(N / block_n) == Bs.shape[0]
+    assert math.ceil(K / block_k) == Bs.shape[1]
+    if output_dtype not in _OUT_DTYPES:
+        raise _lib.TileGymB200Error(-6, f"output_dtype {output_dtype} is not one of f32, f16, bf16")
+
+    M = A.numel() // K
+    C = A.new_empty(A.shape[:-1] + (N,), dtype=output_dtype)
+    ws = _workspace(dev)
+    a2, as2, c2 = A.view(M, K), As.contiguous().view(M, -1), C.view(M, N)
+    bs2 = Bs.contiguous()
+    rc = _lib.lib().tg_fp8_gemm_blockscaled(
+        _lib.ref(_lib.desc(c2)), _lib.ref(_lib.desc(a2)), _lib.ref(_lib.desc(B)), _lib.ref(_lib.desc(as2)),
+        _lib.ref(_lib.desc(bs2)), block_n, block_k, ws.data_ptr(), ws.numel(), dev.index, _stream(dev),
+    )
+    _lib.check_rc(rc)
+    return C
+
+
+def act_quant(x: torch.Tensor, block_size: int = 128) -> Tuple[torch.Tensor, torch.Tensor]:
+    """FP8 block-wise activation quantisation: (y e4m3, s f32 per block).
+
+    Signature of src/tilegym/suites/unsloth/ops.py:223-237; host behaviour of
+    src/tilegym/suites/unsloth/cutile/fp8.py:369-385 (x made contiguous, last
+    dimension divisible by block_size).
+    """
+    dev = _need_cuda(x)
+    if not x.is_contiguous():
+        x = x.contiguous()
+    assert x.shape[-1] % block_size == 0
+    y = torch.empty_like(x, dtype=_FP8)
+    s = x.new_empty(*x.size()[:-1], x.size(-1) // block_size, dtype=torch.float32)
+    rc = _lib.lib().tg_act_quant(
+        _lib.ref(_lib.desc(y.view(-1))), _lib.ref(_lib.desc(s.view(-1))), _lib.ref(_lib.desc(x.view(-1))),
+        int(block_size), dev.index, _stream(dev),
+    )
+    _lib.check_rc(rc)
+    return y, s
+
+
+def weight_dequant(
+    x: torch.Tensor, s: torch.Tensor, block_size: int = 128, dtype: torch.dtype = torch.bfloat16
+) -> torch.Tensor:
+    """FP8 block-wise weight dequantisation, y = x * s[i//block, j//block].
+
+    Signature of src/tilegym/suites/unsloth/ops.py:199-220; host behaviour of
+    src/tilegym/suites/unsloth/cutile/fp8.py:348-367.
+    """
+    dev = _need_cuda(x, s)
+    if not x.is_contiguous():
+        x = x.contiguous()
+    if not s.is_contiguous():
+        s = s.contiguous()
+    assert x.dim() == 2 and s.dim() == 2
+    y = torch.empty_like(x, dtype=dtype)
+    rc = _lib.lib().tg_weight_dequant(
+        _lib.ref(_lib.desc(y)), _lib.ref(_lib.desc(x)), _lib.ref(_lib.desc(s)), int(block_size), dev.index,
+        _stream(dev),
+    )
+    _lib.check_rc(rc)
+    return y
+
+
+def weight_quant_block(w: torch.Tensor, block_size: int = 128) -> Tuple[torch.Tensor, torch.Tensor]:
+    """128 x 128 block quantisation of a weight (N, K): (q e4m3, s f32 [ceil(N/128), ceil(K/128)]).
+    The producer of `Bs`; inverse of `weight_dequant`."""
+    dev = _need_cuda(w)
+    if not w.is_contiguous():
+        w = w.contiguous()
+    assert w.dim() == 2
+    N, K = w.shape
+    q = torch.empty_like(w, dtype=_FP8)
+    s = w.new_empty(math.ceil(N / block_size), math.ceil(K / block_size), dtype=torch.float32)
+    rc = _lib.lib().tg_weight_quant_block(
+        _lib.ref(_lib.desc(q)), _lib.ref(_lib.desc(s)), _lib.ref(_lib.desc(w)), int(block_size), dev.index,
+        _stream(dev),
+    )
+    _lib.check_rc(rc)
+    return q, s
+
+
+# ----------------------------------------------------------------------------
+# Per-tensor-scaled GEMM (reference: tilegym.suites.flashinfer.ops.gemm_alpha_beta)
+# ----------------------------------------------------------------------------
+def _pertensor(
+    c2: torch.Tensor,
+    a2: torch.Tensor,
+    b2: torch.Tensor,
+    scale_a: Optional[torch.Tensor],
+    scale_b: Optional[torch.Tensor],
+    alpha: float,
+    bias: Optional[torch.Tensor],
+    beta: float,
+    dev: torch.device,
+) -> None:
+    ws = _workspace(dev)
+    rc = _lib.lib().tg_fp8_gemm_pertensor(
+        _lib.ref(_lib.desc(c2)), _lib.ref(_lib.desc(a2)), _lib.ref(_lib.desc(b2)),
+        scale_a.data_ptr() if scale_a is not None else 0, scale_b.data_ptr() if scale_b is not None else 0,
+        float(alpha), _lib.ref(_lib.desc(bias)), float(beta), ws.data_ptr(), ws.numel(), dev.index, _stream(dev),
+    )
+    _lib.check_rc(rc)
+
+
+def _scalar_f32(s: Optional[torch.Tensor], dev: torch.device, name: str) -> Optional[torch.Tensor]:
+    if s is None:
+        return None
+    if not torch.is_tensor(s):
+        return torch.tensor([float(s)], dtype=torch.float32, device=dev)
+    if s.numel() != 1:
+        raise _lib.TileGymB200Error(-6, f"{name} must hold exactly one element (per-tensor scale)")
+    if s.dtype != torch.float32 or s.device != dev:
+        s = s.to(device=dev, dtype=torch.float32)
+    return s.reshape(1)
+
+
+def fp8_scaled_mm(
+    A: torch.Tensor,
+    B: torch.Tensor,
+    scale_a: Optional[torch.Tensor] = None,
+    scale_b: Optional[torch.Tensor] = None,
+    bias: Optional[torch.Tensor] = None,
+    out_dtype: torch.dtype = torch.bfloat16,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """C = (scale_a * A) @ (scale_b * B).T + bias, fp32 accumulation, `out_dtype` result.
+
+    A (..., K) e4m3, B (N, K) e4m3 (the layout of nn.Linear.weight), scales are
+    one-element fp32 tensors kept on the device (no host synchronisation).
+    The reference has no per-tensor-scaled GEMM with a bias vector; this is the
+    operator its gemm_alpha_beta (alpha = scale_a * scale_b) approximates.
+    """
+    dev = _need_cuda(A, B)
+    assert A.dtype == _FP8 and B.dtype == _FP8, "A and B must be float8_e4m3fn"
+    assert B.ndim == 2 and A.shape[-1] == B.shape[-1]
+    if not A.is_contiguous():
+        A = A.contiguous()
+    if not B.is_contiguous():
+        B = B.contiguous()
+    N, K = B.shape
+    M = A.numel() // K
+    if out is None:
+        out = A.new_empty(A.shape[:-1] + (N,), dtype=out_dtype)
+    else:
+        assert out.shape == A.shape[:-1] + (N,) and out.is_contiguous()
+    if bias is not None and not bias.is_contiguous():
+        bias = bias.contiguous()
+    _pertensor(out.view(M, N), A.view(M, K), B, _scalar_f32(scale_a, dev, "scale_a"),
+               _scalar_f32(scale_b, dev, "scale_b"), 1.0, bias, 0.0, dev)
+    return out
+
+
+def gemm_alpha_beta(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    c: torch.Tensor,
+    trans_a: bool = False,
+    trans_b: bool = True,
+    alpha: float = 1.0,
+    beta: float = 0.0,
+    num_sms: Optional[int] = None,
+    **kwargs,
+) -> torch.Tensor:
+    """C = alpha * A @ B.T + beta * C, in place, returns `c`.
+
+    Signature of src/tilegym/suites/flashinfer/ops.py:25-55 and
+    src/tilegym/suites/flashinfer/cutile/gemm/gemm_alpha_beta.py:336-381 (the
+    same contiguity asserts).  Only the FP8 path is implemented here: a and b
+    float8_e4m3fn, trans_a=False, trans_b=True (b is [N, K]).  `num_sms` and
+    tuning kwargs (`use_autotune`, `backend`, ...) are accepted and ignored:
+    the kernel always uses every SM.  Unlike the reference kernel, `c` is not
+    read when beta == 0, so an uninitialised `c` cannot inject NaNs.
+    """
+    dev = _need_cuda(a, b, c)
+    if a.dtype != _FP8 or b.dtype != _FP8:
+        raise NotImplementedError("tilegym_b200.gemm_alpha_beta implements the float8_e4m3fn path only")
+    if trans_a or not trans_b:
+        raise NotImplementedError("tilegym_b200.gemm_alpha_beta needs trans_a=False, trans_b=True (A [M,K], B [N,K])")
+    M, K = a.shape
+    N, KB = b.shape
+    assert K == KB, "incompatible dimensions"
+    assert c.shape == (M, N), "C must have shape [M, N]"
+    assert a.is_contiguous(), "A matrix must be contiguous"
+    assert b.is_contiguous(), "B matrix must be contiguous"
+    assert c.is_contiguous(), "C matrix must be contiguous"
+    _pertensor(c, a, b, None, None, alpha, None, beta, dev)
+    return c
+
+
+def matmul(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    trans_a: Optional[bool] = None,
+    trans_b: Optional[bool] = None,
+    static_persistent: bool = True,
+    use_tma: Optional[bool] = None,
+    **kwargs,
+) -> torch.Tensor:
+    """Unscaled FP8 matmul with the reference's signature (src/tilegym/ops/ops.py:715-741).
+
+    e4m3 inputs only.  With trans_b=True, b is [N, K] and is used as is; otherwise
+    b is [K, N] and is transposed into the K-major layout the kernel reads (one
+    copy).  The result keeps the input dtype like the reference
+    (src/tilegym/ops/cutile/matmul.py:446): fp32 accumulation, clamp to +-448,
+    cast to e4m3.  Pass out_dtype=torch.bfloat16 to skip the narrowing cast.
+    Tuning kwargs and `backend=` are accepted and ignored.
+    """
+    dev = _need_cuda(a, b)
+    if a.dtype != _FP8 or b.dtype != _FP8:
+        raise NotImplementedError("tilegym_b200.matmul implements the float8_e4m3fn path only")
+    if trans_a:
+        a = a.t()
+    if not a.is_contiguous():
+        a = a.contiguous()
+    bt = b if trans_b else b.t()
+    if not bt.is_contiguous():
+        bt = bt.contiguous()
+    M, K = a.shape
+    N = bt.shape[0]
+    assert bt.shape[1] == K, "incompatible dimensions"
+    out_dtype = kwargs.pop("out_dtype", None)
+    c = torch.empty((M, N), dtype=torch.float32 if out_dtype is None else out_dtype, device=dev)
+    _pertensor(c, a, bt, None, None, 1.0, None, 0.0, dev)
+    if out_dtype is None:
+        return c.clamp_(-448.0, 448.0).to(_FP8)
+    return c
+
+
+def quant_per_tensor(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-tensor e4m3 quantisation: (q, scale) with scale = amax/448 as a
+    one-element fp32 device tensor (1.0 for an all-zero input)."""
+    dev = _need_cuda(x)
+    if x.dtype not in _IN_DTYPES:
+        raise _lib.TileGymB200Error(-2, f"quant_per_tensor takes f32, f16 or bf16, got {x.dtype}")
+    if not x.is_contiguous():
+        x = x.contiguous()
+    q = torch.empty_like(x, dtype=_FP8)
+    scale = torch.empty(1, dtype=torch.float32, device=dev)
+    key = (dev.index, _stream(dev))
+    scratch = _amax_scratch.get(key)
+    if scratch is None:
+        scratch = torch.zeros(1, dtype=torch.int32, device=dev)
+        _amax_scratch[key] = scratch
+    rc = _lib.lib().tg_quant_pertensor(
+        _lib.ref(_lib.desc(q.view(-1))), scale.data_ptr(), _lib.ref(_lib.desc(x.view(-1))), scratch.data_ptr(),
+        dev.index, _stream(dev),
+    )
+    _lib.check_rc(rc)
+    return q, scale
