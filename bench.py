@@ -1,0 +1,403 @@
+#!/usr/bin/env python
+"""Benchmark of the FP8 scaled-GEMM hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N = 1 : one step = the four Llama-3.1-8B prefill linears at M = 4096 tokens
+        (qkv, o_proj, gate_up, down), per-tensor e4m3 scales, bf16 out.
+N > 1 : one step = the Llama-3.1-70B-shape gate_up GEMM (M=8192, N=57344,
+        K=8192), weight rows sharded over the N ranks, NCCL all-gather of the
+        bf16 output slabs (launched under torchrun, one rank per GPU).
+Prints ONE JSON line on rank 0.  `--impl reference` times the reference's own
+torch CPU path (dequantise -> fp32 matmul -> bf16; the oracle) on a bounded
+row sample of the same workload, on the host cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+LLAMA8B = [("qkv", 6144, 4096), ("o_proj", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336)]
+M_PREFILL = 4096
+L70B = dict(M=8192, N=57344, K=8192)
+NOMINAL_FP8_TFLOPS = 4500.0
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return d, "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while a timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period_s
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop_evt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def stop(self):
+        self._stop_evt.set()
+        if self.is_alive():
+            self.join(timeout=2)
+        if not self.samples:
+            return None
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# --------------------------------------------------------------------------- inputs
+def make_case(M, N, K, dev, seed):
+    """Seeded synthetic operands with the stated distributions, quantised on the GPU:
+    activations N(0,1) with 0.1 % of the K channels x20, weights N(0, 0.02)."""
+    import tilegym_b200 as tg
+
+    g = torch.Generator(device=dev).manual_seed(seed)
+    x = torch.randn(M, K, generator=g, device=dev, dtype=torch.bfloat16)
+    n_out = max(1, round(0.001 * K))
+    cols = torch.randperm(K, generator=g, device=dev)[:n_out]
+    x[:, cols] *= 20.0
+    a8, sa = tg.quant_per_tensor(x)
+    del x
+    w = torch.randn(N, K, generator=g, device=dev, dtype=torch.bfloat16) * 0.02
+    b8, sb = tg.quant_per_tensor(w)
+    del w
+    return a8, b8, sa, sb
+
+
+def cpu_step_sample(shapes, rows, seed=0):
+    """One bounded CPU sample: the oracle GEMM on `rows` activation rows of every shape.
+    Returns (flops, callable)."""
+    from oracle import torch_ref as R
+
+    cases = []
+    flops = 0
+    for i, (M, N, K) in enumerate(shapes):
+        m = min(rows, M)
+        g = torch.Generator().manual_seed(seed + i)
+        a8 = (torch.randn(m, K, generator=g)).clamp_(-448, 448).to(torch.float8_e4m3fn)
+        b8 = (torch.randn(N, K, generator=g)).clamp_(-448, 448).to(torch.float8_e4m3fn)
+        cases.append((a8, b8, torch.tensor([0.03]), torch.tensor([0.0002])))
+        flops += 2 * m * N * K
+
+    def step():
+        for a8, b8, sa, sb in cases:
+            R.ref_fp8_scaled_mm(a8, b8, sa, sb)
+
+    return flops, step
+
+
+# --------------------------------------------------------------------------- reference arm
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    if args.gpus == 1:
+        shapes = [(M_PREFILL, N, K) for _, N, K in LLAMA8B]
+        rows, workload = 256, "llama31_8b_prefill_m4096"
+    else:
+        shapes = [(L70B["M"], L70B["N"], L70B["K"])]
+        rows, workload = 256, "llama31_70b_gate_up_nshard"
+    flops, step = cpu_step_sample(shapes, rows)
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    tflops = flops * args.steps / dt / 1e12
+    threads = torch.get_num_threads()
+    sample = f"{rows} of the M activation rows of every GEMM of the step (all N, K), torch CPU dequantise->fp32 matmul->bf16"
+    line = {
+        "impl": "reference", "metric": "fp8_gemm_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "e4m3_f32acc",
+        "data": "synthetic", "config": {"workload": workload, "sample_rows": rows},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "host": {"cpu_count": os.cpu_count(), "torch_threads": threads, "torch": torch.__version__},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- our arm
+def timed(fn, steps, warmup, dev, dist=None):
+    """W warm-up steps, then exactly `steps` steps between CUDA events on the current
+    stream, barrier + synchronize on both sides; returns seconds (max over ranks)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize(dev)
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+    sec = e0.elapsed_time(e1) / 1e3
+    if dist is not None:
+        t = torch.tensor([sec], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sec = float(t.item())
+    return sec
+
+
+def run_ours_single(args):
+    import tilegym_b200 as tg
+    from tilegym_b200 import _lib
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    peaks, peak_src = measured_peaks()
+    cases = []
+    for i, (name, N, K) in enumerate(LLAMA8B):
+        a8, b8, sa, sb = make_case(M_PREFILL, N, K, dev, 2000 + i)
+        out = torch.empty(M_PREFILL, N, dtype=torch.bfloat16, device=dev)
+        cases.append((name, a8, b8, sa, sb, out))
+    flops_step = sum(2 * M_PREFILL * N * K for _, N, K in LLAMA8B)
+    bytes_resident = sum(c[1].numel() + c[2].numel() + c[5].numel() * 2 for c in cases)
+
+    def step():
+        for _, a8, b8, sa, sb, out in cases:
+            tg.fp8_scaled_mm(a8, b8, sa, sb, None, torch.bfloat16, out=out)
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    sec = timed(step, args.steps, args.warmup, dev)
+    clocks = sampler.stop()
+    _lib.device_status(0)
+    tflops = flops_step * args.steps / sec / 1e12
+
+    # per-shape device time (outside the headline region), each GEMM back to back
+    per_shape = {}
+    for name, a8, b8, sa, sb, out in cases:
+        s = timed(lambda: tg.fp8_scaled_mm(a8, b8, sa, sb, None, torch.bfloat16, out=out), 20, 3, dev)
+        N, K = b8.shape
+        per_shape[name] = {"us": s / 20 * 1e6, "tflops": 2 * M_PREFILL * N * K * 20 / s / 1e12}
+
+    # end to end through the public API with HOST buffers: pinned activations in, pinned result out
+    host_in = [c[1].cpu().pin_memory() for c in cases]
+    host_out = [torch.empty(c[5].shape, dtype=torch.bfloat16).pin_memory() for c in cases]
+    h2d = sum(t.numel() * t.element_size() for t in host_in)
+    d2h = sum(t.numel() * t.element_size() for t in host_out)
+
+    def step_e2e():
+        for (name, a8, b8, sa, sb, out), hin, hout in zip(cases, host_in, host_out):
+            a8.copy_(hin, non_blocking=True)
+            tg.fp8_scaled_mm(a8, b8, sa, sb, None, torch.bfloat16, out=out)
+            hout.copy_(out, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 20))
+    sec_e2e = timed(step_e2e, e2e_steps, 3, dev)
+    e2e_tflops = flops_step * e2e_steps / sec_e2e / 1e12
+
+    # CPU baseline: the oracle on a bounded sample of the same step
+    cpu = None
+    if not args.no_cpu_baseline:
+        rows = 512
+        cflops, cstep = cpu_step_sample([(M_PREFILL, N, K) for _, N, K in LLAMA8B], rows)
+        cstep()
+        t0 = time.perf_counter()
+        reps = 3
+        for _ in range(reps):
+            cstep()
+        dt = (time.perf_counter() - t0) / reps
+        cpu = {"value": cflops / dt / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+               "sample": f"{rows} of the 4096 activation rows of each of the 4 GEMMs, {reps} passes, torch CPU oracle"}
+
+    launches = 4 * args.steps
+    peak = 2.0 * peaks["bf16_tflops_sustained"]
+    roofline = {
+        "bound": "tensor", "kernel": "tg_fp8_gemm_pertensor_kernel<256>", "achieved": tflops, "peak": peak,
+        "unit": "TFLOP/s", "frac": tflops / peak,
+        "peak_source": f"2 x bf16_tflops_sustained of {peak_src} (fp8 issues at twice the bf16 rate); nominal dense fp8 {NOMINAL_FP8_TFLOPS}",
+        "frac_of_nominal": tflops / NOMINAL_FP8_TFLOPS,
+        "avg_launch_us": sec / launches * 1e6, "flops_per_launch": flops_step / 4,
+        "traffic": TRAFFIC_BYTES_PER_LAUNCH,
+    }
+    line = {
+        "metric": "fp8_gemm_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "e4m3_f32acc", "data": "synthetic",
+        "config": {"workload": "llama31_8b_prefill_m4096", "gemms": [f"{n}:{M_PREFILL}x{N}x{K}" for n, N, K in LLAMA8B],
+                   "scaling_mode": "per-tensor e4m3, bf16 out",
+                   "l2": f"no flush: {bytes_resident / 1e6:.0f} MB touched per step > 126 MB L2"},
+        "roofline": roofline, "cpu_baseline": cpu,
+        "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": sec_e2e / e2e_steps * 1e3, "steps": e2e_steps},
+        "gpu_launches": launches, "clocks": clocks, "per_shape": per_shape,
+    }
+    if args.extra:
+        import bench_extra
+
+        line["extra"] = bench_extra.run(dev, peaks)
+    print(json.dumps(line), flush=True)
+
+
+# ncu: dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, averaged over the
+# four shapes of the step (see profiles/); None until a capture has been taken.
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def run_ours_multi(args, rank, world, local_rank):
+    import torch.distributed as dist
+
+    import tilegym_b200 as tg
+    from tilegym_b200 import _lib, sharded
+
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    peaks, peak_src = measured_peaks()
+    M, N, K = L70B["M"], L70B["N"], L70B["K"]
+    lo, hi = sharded.shard_bounds(N, world, rank)
+    # every rank draws the same activations; the weight shard is drawn per rank from a rank-independent
+    # stream position so that the union over ranks is one fixed weight matrix
+    g = torch.Generator(device=dev).manual_seed(5000)
+    x = torch.randn(M, K, generator=g, device=dev, dtype=torch.bfloat16)
+    cols = torch.randperm(K, generator=g, device=dev)[: max(1, round(0.001 * K))]
+    x[:, cols] *= 20.0
+    a8, sa = tg.quant_per_tensor(x)
+    del x
+    gw = torch.Generator(device=dev).manual_seed(6000 + rank)
+    w = torch.randn(hi - lo, K, generator=gw, device=dev, dtype=torch.bfloat16) * 0.02
+    # global per-tensor weight scale: amax over all shards
+    amax = w.abs().max().float().reshape(1)
+    dist.all_reduce(amax, op=dist.ReduceOp.MAX)
+    sb = (amax / 448.0).to(torch.float32)
+    b8 = (w.float() / sb).clamp_(-448, 448).to(torch.float8_e4m3fn)
+    del w
+    gemm = sharded.ColumnParallelFP8Gemm(b8, sb, M)
+
+    def step():
+        gemm.forward(a8, sa, gather=True)
+
+    def step_nogather():
+        gemm.forward(a8, sa, gather=False)
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    sec = timed(step, args.steps, args.warmup, dev, dist)
+    clocks = sampler.stop()
+    sec_gemm = timed(step_nogather, args.steps, args.warmup, dev, dist)
+    _lib.device_status(local_rank)
+    flops = 2.0 * M * N * K
+    tflops = flops * args.steps / sec / 1e12
+
+    # end to end: pinned activations in, this rank's gathered output out
+    hin = a8.cpu().pin_memory()
+    hout = torch.empty(gemm.out_slabs.shape, dtype=torch.bfloat16).pin_memory()
+
+    def step_e2e():
+        a8.copy_(hin, non_blocking=True)
+        gemm.forward(a8, sa, gather=True)
+        hout.copy_(gemm.out_slabs, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    sec_e2e = timed(step_e2e, e2e_steps, 2, dev, dist)
+    if rank == 0:
+        peak = 2.0 * peaks["bf16_tflops_sustained"] * world
+        line = {
+            "metric": "fp8_gemm_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": sec / args.steps * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "e4m3_f32acc", "data": "synthetic",
+            "config": {"workload": "llama31_70b_gate_up_nshard", "M": M, "N": N, "K": K,
+                       "parallelism": f"column-parallel x{world}, NCCL all-gather of bf16 slabs",
+                       "l2": "no flush: operands and output exceed 126 MB L2"},
+            "roofline": {"bound": "tensor", "kernel": "tg_fp8_gemm_pertensor_kernel<256>",
+                         "achieved": flops * args.steps / sec_gemm / 1e12, "peak": peak, "unit": "TFLOP/s",
+                         "frac": flops * args.steps / sec_gemm / 1e12 / peak,
+                         "peak_source": f"{world} x 2 x bf16_tflops_sustained of {peak_src}; GEMM phase only (no gather)",
+                         "traffic": None},
+            "cpu_baseline": None,
+            "e2e": {"value": flops * e2e_steps / sec_e2e / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": hin.numel(),
+                    "d2h_bytes_per_step": hout.numel() * 2, "ms_per_step": sec_e2e / e2e_steps * 1e3},
+            "gpu_launches": args.steps, "clocks": clocks,
+            "phases": {"gemm_only_ms": sec_gemm / args.steps * 1e3, "gemm_plus_allgather_ms": sec / args.steps * 1e3},
+        }
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--extra", action="store_true", help="also run the decode (HBM-bound) and block-scaled shape sweeps")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world == 1 and args.gpus == 1:
+        run_ours_single(args)
+    elif world == 1 and args.gpus > 1:
+        raise SystemExit("launch with torchrun: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N")
+    else:
+        run_ours_multi(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

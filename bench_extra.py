@@ -1,0 +1,97 @@
+"""Shape sweeps that accompany the headline number of bench.py (`--extra`):
+the decode (M <= 64, HBM-bound) GEMMs of the Llama-3.1-8B linears and the
+DeepSeek-V2-style block-scaled GEMMs.
+
+Timing method for the small kernels: R launches are captured into one CUDA
+graph, each reading a different copy of the weight (the copies together are
+several times the 126 MB L2, so every launch streams its weight from HBM),
+the graph is replayed a few times between CUDA events and the time is divided
+by the number of launches.  Host launch overhead is therefore excluded and
+the L2 is cold for the weights; the few-KB activations stay L2-resident as
+they would in a decode loop.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+LLAMA8B = [("qkv", 6144, 4096), ("o_proj", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336)]
+DEEPSEEK = [(24576, 1536), (5120, 12288), (3072, 5120)]
+L2_BYTES = 126e6
+
+
+def graph_time_us(launch, n_variants: int, replays: int = 5) -> float:
+    """`launch(i)` enqueues variant i on the current stream.  Returns microseconds per launch."""
+    for i in range(min(n_variants, 2)):
+        launch(i)  # warm-up outside capture: module load, attributes, workspace
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(n_variants):
+            launch(i)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (replays * n_variants)
+
+
+def decode_sweep(dev, hbm_peak_gbs: float):
+    import tilegym_b200 as tg
+
+    rows = []
+    for name, N, K in LLAMA8B:
+        copies = max(4, math.ceil(4 * L2_BYTES / (N * K)))
+        w = [torch.randn(N, K, device=dev, dtype=torch.bfloat16).mul_(0.02).to(torch.float8_e4m3fn) for _ in range(copies)]
+        sb = torch.full((1,), 2e-4, device=dev)
+        sa = torch.full((1,), 3e-2, device=dev)
+        for M in (1, 8, 16, 64):
+            a = torch.randn(M, K, device=dev).to(torch.float8_e4m3fn)
+            outs = [torch.empty(M, N, dtype=torch.bfloat16, device=dev) for _ in range(copies)]
+            us = graph_time_us(lambda i: tg.fp8_scaled_mm(a, w[i], sa, sb, None, torch.bfloat16, out=outs[i]), copies)
+            nbytes = N * K + M * K + 2 * M * N + 8
+            gbs = nbytes / us / 1e3
+            rows.append({"shape": name, "M": M, "N": N, "K": K, "us": round(us, 2), "gbs": round(gbs, 1),
+                         "frac_of_measured_hbm": round(gbs / hbm_peak_gbs, 3), "weight_copies": copies})
+        del w
+    return rows
+
+
+def block_scaled_sweep(dev, fp8_peak_tflops: float, hbm_peak_gbs: float):
+    import tilegym_b200 as tg
+
+    rows = []
+    for N, K in DEEPSEEK:
+        for M in (128, 4096):
+            copies = max(2, math.ceil(3 * L2_BYTES / (N * K))) if M == 128 else 2
+            b = [torch.randn(N, K, device=dev, dtype=torch.bfloat16).mul_(0.02).to(torch.float8_e4m3fn) for _ in range(copies)]
+            a = torch.randn(M, K, device=dev).to(torch.float8_e4m3fn)
+            As = torch.rand(M, K // 128, device=dev) + 0.5
+            Bs = torch.rand(N // 128, K // 128, device=dev) + 0.5
+            us = graph_time_us(lambda i: tg.w8a8_block_fp8_matmul(a, b[i], As, Bs, [128, 128], torch.bfloat16), copies,
+                               replays=5 if M == 128 else 10)
+            flops = 2.0 * M * N * K
+            nbytes = M * K + N * K + 2 * M * N + 4 * (As.numel() + Bs.numel())
+            rows.append({"M": M, "N": N, "K": K, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1),
+                         "gbs": round(nbytes / us / 1e3, 1),
+                         "bound": "hbm" if M == 128 else "tensor",
+                         "frac": round((nbytes / us / 1e3) / hbm_peak_gbs if M == 128 else (flops / us / 1e6) / fp8_peak_tflops, 3)})
+            del b
+    return rows
+
+
+def run(dev, peaks):
+    hbm = float(peaks["hbm_gbs"])
+    fp8 = 2.0 * float(peaks["bf16_tflops"])  # kernels timed alone: burst figure
+    return {
+        "method": "CUDA-graph replay over rotating weight copies (> 3x L2), time per launch; fractions are of the "
+                  "measured HBM copy bandwidth / of 2 x measured bf16 burst",
+        "decode_per_tensor": decode_sweep(dev, hbm),
+        "block_scaled": block_scaled_sweep(dev, fp8, hbm),
+    }

@@ -1,0 +1,114 @@
+"""The C-ABI library without a GPU: it loads, exports every symbol the public
+header declares, and rejects wrong calls with the documented codes before it
+touches CUDA.  No compute call is made here."""
+
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from conftest import ROOT
+from tilegym_b200 import _lib, ops
+
+HEADER = os.path.join(ROOT, "include", "tilegym_b200.h")
+
+
+def declared_symbols():
+    src = open(HEADER).read()
+    return re.findall(r"TG_API\s+[\w\s\*]+?\b(tg_\w+)\s*\(", src)
+
+
+def test_library_is_built_and_loads():
+    assert os.path.exists(_lib.LIB_PATH), "run `python -m tilegym_b200.build`"
+    assert _lib.lib().tg_version() >= 100
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    names = declared_symbols()
+    assert len(names) >= 10
+    handle = ctypes.CDLL(_lib.LIB_PATH)
+    for n in names:
+        assert hasattr(handle, n), f"{n} is declared in the header but not exported"
+        assert n in _lib.SIGNATURES or n.endswith("_static"), f"{n} has no ctypes signature"
+
+
+def _d(t):
+    return _lib.ref(_lib.desc(t))
+
+
+def test_workspace_size_is_stated():
+    assert _lib.lib().tg_fp8_gemm_workspace_bytes(16, 4096, 4096) == (64 << 10) + (48 << 20)
+
+
+def test_pertensor_argument_checks():
+    L = _lib.lib()
+    a = torch.zeros(128, 128, dtype=torch.float8_e4m3fn)
+    c = torch.zeros(128, 128, dtype=torch.bfloat16)
+
+    def call(C, A, B, bias=None):
+        return L.tg_fp8_gemm_pertensor(_d(C), _d(A), _d(B), 0, 0, 1.0, _d(bias), 0.0, 0, 0, 0, 0)
+
+    assert call(c, a, None) == -5 and b"null" in L.tg_last_error_string()
+    assert call(c, a.view(torch.uint8), a) == -2
+    assert call(c.to(torch.int32), a, a) == -2
+    assert call(c, a, torch.zeros(128, 64, dtype=torch.float8_e4m3fn)) == -6  # K mismatch
+    assert call(torch.zeros(64, 128, dtype=torch.bfloat16), a, a) == -6  # C shape
+    assert call(c, torch.zeros(128, 136, dtype=torch.float8_e4m3fn), torch.zeros(128, 136, dtype=torch.float8_e4m3fn)) == -8  # K % 16
+    assert call(c, a, a, torch.zeros(64)) == -6  # bias length
+    # empty problems are accepted without a device
+    e = torch.zeros(0, 128, dtype=torch.float8_e4m3fn)
+    assert call(torch.zeros(0, 128, dtype=torch.bfloat16), e, a) == 0
+
+
+def test_blockscaled_argument_checks():
+    L = _lib.lib()
+    a = torch.zeros(128, 256, dtype=torch.float8_e4m3fn)
+    c = torch.zeros(128, 128, dtype=torch.float32)
+    b = torch.zeros(128, 256, dtype=torch.float8_e4m3fn)
+    As, Bs = torch.ones(128, 2), torch.ones(1, 2)
+
+    def call(As_, Bs_, bn=128, bk=128):
+        return L.tg_fp8_gemm_blockscaled(_d(c), _d(a), _d(b), _d(As_), _d(Bs_), bn, bk, 0, 0, 0, 0)
+
+    assert call(As, Bs, 64, 128) == -6 and b"128" in L.tg_last_error_string()
+    assert call(torch.ones(128, 3), Bs) == -6
+    assert call(As, torch.ones(2, 2)) == -6
+    assert call(As.half(), Bs) == -2
+
+
+def test_quantiser_argument_checks():
+    L = _lib.lib()
+    x = torch.zeros(4, 256, dtype=torch.bfloat16)
+    y = torch.zeros(4, 256, dtype=torch.float8_e4m3fn)
+    s = torch.zeros(4, 2)
+    assert L.tg_act_quant(_d(y), _d(s), _d(x), 64, 0, 0) == -6
+    assert L.tg_act_quant(_d(y), _d(s), _d(x.to(torch.int32)), 128, 0, 0) == -2
+    assert L.tg_act_quant(_d(y), _d(torch.zeros(4, 3)), _d(x), 128, 0, 0) == -6
+    assert L.tg_weight_dequant(_d(x), _d(y), _d(torch.zeros(1, 1)), 128, 0, 0) == -6  # S shape
+    assert L.tg_quant_pertensor(_d(y), 0, _d(x), 0, 0, 0) == -5
+
+
+def test_ops_refuse_cpu_tensors_instead_of_falling_back():
+    a = torch.zeros(16, 128, dtype=torch.float8_e4m3fn)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        ops.fp8_scaled_mm(a, a)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        ops.w8a8_block_fp8_matmul(a, a, torch.ones(16, 1), torch.ones(1, 1))
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        ops.act_quant(torch.zeros(4, 128, dtype=torch.bfloat16))
+
+
+def test_signatures_match_the_reference_entry_points():
+    import inspect
+
+    sig = inspect.signature(ops.w8a8_block_fp8_matmul)
+    assert list(sig.parameters) == ["A", "B", "As", "Bs", "block_size", "output_dtype"]
+    assert sig.parameters["output_dtype"].default is torch.float32
+    sig = inspect.signature(ops.gemm_alpha_beta)
+    assert list(sig.parameters)[:8] == ["a", "b", "c", "trans_a", "trans_b", "alpha", "beta", "num_sms"]
+    assert sig.parameters["trans_b"].default is True
+    assert list(inspect.signature(ops.act_quant).parameters) == ["x", "block_size"]
+    assert list(inspect.signature(ops.weight_dequant).parameters) == ["x", "s", "block_size", "dtype"]
+    assert list(inspect.signature(ops.matmul).parameters)[:6] == ["a", "b", "trans_a", "trans_b", "static_persistent", "use_tma"]

@@ -1,0 +1,255 @@
+"""Parity of the CUDA FP8 GEMM paths (through the C ABI) with the CPU oracle.
+
+Tolerance (stated by the task): max relative error <= 1e-2 and max absolute
+error <= 2 bf16 ulps of the reference output's magnitude; `check_tolerance`
+implements it (relative error is taken over elements above 2^-10 of the
+output's magnitude, the rest are held to 2 ulps of that floor).
+"""
+
+import os
+
+import pytest
+import torch
+
+from conftest import load_golden
+from oracle import torch_ref as R
+
+pytestmark = pytest.mark.gpu
+
+import tilegym_b200 as tg  # noqa: E402
+from tilegym_b200 import _lib  # noqa: E402
+
+KNOBS = ("TILEGYM_B200_BN", "TILEGYM_B200_SPLITS", "TILEGYM_B200_FORCE_PATH")
+
+
+@pytest.fixture(autouse=True)
+def clean_env_and_status(dev):
+    for k in KNOBS:
+        os.environ.pop(k, None)
+    yield
+    for k in KNOBS:
+        os.environ.pop(k, None)
+    _lib.device_status(0)  # raises if any bounded device-side wait expired
+
+
+def run_pt(dev, M, N, K, seed, bias=False, out_dtype=torch.bfloat16, outliers=True):
+    a8, b8, sa, sb = R.gen_per_tensor_case(M, N, K, seed, outliers)
+    bvec = torch.randn(N, generator=torch.Generator().manual_seed(seed + 7)) if bias else None
+    ref = R.ref_fp8_scaled_mm(a8, b8, sa, sb, bvec, out_dtype)
+    out = tg.fp8_scaled_mm(a8.to(dev), b8.to(dev), sa.to(dev), sb.to(dev), bvec.to(dev) if bias else None, out_dtype)
+    assert out.dtype == out_dtype and out.shape == (M, N)
+    res = R.check_tolerance(out, ref)
+    assert res["ok"], res
+    return out
+
+
+# ------------------------------------------------------------ per-tensor path
+def test_config1_1024_cube(dev):
+    """BASELINE config 1: M=N=K=1024, N(0,1) operands, per-tensor scales."""
+    a8, sa = R.ref_quant_per_tensor(R.gen_activations(1024, 1024, 100, outliers=False))
+    b8, sb = R.ref_quant_per_tensor(R.gen_weights(1024, 1024, 101, std=1.0))
+    ref = R.ref_fp8_scaled_mm(a8, b8, sa, sb)
+    out = tg.fp8_scaled_mm(a8.to(dev), b8.to(dev), sa.to(dev), sb.to(dev))
+    assert R.check_tolerance(out, ref)["ok"]
+
+
+@pytest.mark.parametrize("N,K", [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)])
+def test_llama8b_prefill_shapes(dev, N, K):
+    """BASELINE config 2 at full size: M=4096, outlier channels, N(0,0.02) weights."""
+    run_pt(dev, 4096, N, K, seed=2000 + N + K)
+
+
+@pytest.mark.parametrize("M", [1, 8, 16, 64])
+@pytest.mark.parametrize("N,K", [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)])
+def test_llama8b_decode_shapes(dev, M, N, K):
+    """BASELINE config 3 at full size (swap-AB split-K path)."""
+    run_pt(dev, M, N, K, seed=3000 + M + N + K)
+
+
+@pytest.mark.parametrize("bn", ["256", "128", "64"])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (300, 520, 1040), (1, 16, 16), (129, 257 * 8, 144)])
+def test_tile_widths_and_tails(dev, bn, M, N, K):
+    os.environ["TILEGYM_B200_BN"] = bn
+    os.environ["TILEGYM_B200_FORCE_PATH"] = "gemm"
+    run_pt(dev, M, N, K, seed=11, bias=True)
+
+
+@pytest.mark.parametrize("M", [1, 2, 7, 16, 17, 31, 32, 33, 63, 64, 65, 127, 128, 129])
+def test_m_sweep_across_both_paths(dev, M):
+    run_pt(dev, M, 384, 2048, seed=40 + M, bias=(M % 2 == 0))
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M", [5, 200])
+def test_output_dtypes_and_unaligned_n(dev, out_dtype, M):
+    # N = 100 is not a multiple of 8: rows of C are not 16-byte aligned, scalar stores
+    run_pt(dev, M, 100, 512, seed=77, bias=True, out_dtype=out_dtype)
+
+
+@pytest.mark.parametrize("splits", ["1", "2", "5"])
+@pytest.mark.parametrize("M", [16, 256])
+def test_split_k_matches_unsplit(dev, splits, M):
+    os.environ["TILEGYM_B200_SPLITS"] = splits
+    run_pt(dev, M, 512, 4096, seed=5)
+
+
+def test_split_k_is_bit_stable(dev):
+    """The split-K reduction adds partial sums in split order, so repeated
+    runs give identical bits (the reference checks determinism over repeated
+    runs the same way, tests/common.py:374-504)."""
+    a8, b8, sa, sb = R.gen_per_tensor_case(16, 4096, 4096, 8)
+    a, b, sa, sb = a8.to(dev), b8.to(dev), sa.to(dev), sb.to(dev)
+    first = tg.fp8_scaled_mm(a, b, sa, sb).clone()
+    for _ in range(20):
+        again = tg.fp8_scaled_mm(a, b, sa, sb)
+        assert torch.equal(first, again)
+
+
+def test_workspace_counters_are_left_zero(dev):
+    from tilegym_b200 import ops
+
+    run_pt(dev, 16, 4096, 4096, seed=8)
+    ws = ops._workspace(dev)
+    assert int(ws[: 64 << 10].view(torch.int32).abs().max()) == 0
+
+
+def test_leading_dims_are_flattened(dev):
+    a8, b8, sa, sb = R.gen_per_tensor_case(6 * 50, 256, 512, 21)
+    ref = R.ref_fp8_scaled_mm(a8, b8, sa, sb).view(6, 50, 256)
+    out = tg.fp8_scaled_mm(a8.view(6, 50, 512).to(dev), b8.to(dev), sa.to(dev), sb.to(dev))
+    assert out.shape == (6, 50, 256) and R.check_tolerance(out, ref)["ok"]
+
+
+def test_empty_inputs(dev):
+    b8 = torch.zeros(256, 128, dtype=torch.float8_e4m3fn, device=dev)
+    out = tg.fp8_scaled_mm(torch.zeros(0, 128, dtype=torch.float8_e4m3fn, device=dev), b8)
+    assert out.shape == (0, 256)
+
+
+def test_linearity_in_the_scales_at_full_size(dev):
+    """Size-independent property: doubling scale_a doubles every output
+    exactly (a power-of-two factor commutes with all roundings)."""
+    M, N, K = 4096, 4096, 4096
+    a = torch.randn(M, K, device=dev).to(torch.float8_e4m3fn)
+    b = (torch.randn(N, K, device=dev) * 0.02).to(torch.float8_e4m3fn)
+    s1 = torch.tensor([0.031], device=dev)
+    c1 = tg.fp8_scaled_mm(a, b, s1, s1)
+    c2 = tg.fp8_scaled_mm(a, b, s1 * 2, s1)
+    assert torch.equal(c1.float() * 2, c2.float())
+
+
+# -------------------------------------------------------- gemm_alpha_beta API
+@pytest.mark.parametrize("name", ["gemm_alpha_beta_256_1.0_0.0.npz", "gemm_alpha_beta_256_1.5_2.0.npz"])
+def test_gemm_alpha_beta_against_reference_fixture(dev, name):
+    """Same comparison and tolerance as the reference's own test
+    (tests/suites/flashinfer/test_flashinfer_gemm_alpha_beta.py:68-75)."""
+    g = load_golden(name)
+    c = g["c"].to(dev)
+    out = tg.gemm_alpha_beta(g["a"].to(dev), g["b"].to(dev), c, False, True, g["alpha"], g["beta"])
+    assert out.data_ptr() == c.data_ptr()  # in place
+    torch.testing.assert_close(out.float().cpu(), g["out"].float(), rtol=1e-2, atol=1e-2)
+    tight = R.ref_gemm_alpha_beta(g["a"], g["b"], g["c"], g["alpha"], g["beta"])
+    assert R.check_tolerance(out, tight)["ok"]
+
+
+def test_gemm_alpha_beta_reference_recipe_4096(dev):
+    """The reference test's recipe at one of its own sizes: rand() operands, seed 0."""
+    torch.manual_seed(0)
+    m = n = k = 4096
+    a = torch.rand(m * k, dtype=torch.float16).to(torch.float8_e4m3fn).view(m, k)
+    b = torch.rand(k * n, dtype=torch.float16).to(torch.float8_e4m3fn).view(n, k)
+    c = torch.rand((m, n), dtype=torch.bfloat16)
+    ref = R.ref_gemm_alpha_beta(a, b, c, 1.5, 2.0)
+    out = tg.gemm_alpha_beta(a.to(dev), b.to(dev), c.to(dev), False, True, 1.5, 2.0)
+    assert R.check_tolerance(out, ref)["ok"]
+
+
+def test_gemm_alpha_beta_beta_zero_ignores_c_contents(dev):
+    g = load_golden("gemm_alpha_beta_256_1.0_0.0.npz")
+    c = torch.full((256, 256), float("nan"), dtype=torch.bfloat16, device=dev)
+    out = tg.gemm_alpha_beta(g["a"].to(dev), g["b"].to(dev), c, alpha=1.0, beta=0.0)
+    assert bool(torch.isfinite(out).all())
+
+
+def test_matmul_keeps_input_dtype(dev):
+    a = (torch.randn(64, 256) * 0.3).to(torch.float8_e4m3fn)
+    b = (torch.randn(256, 128) * 0.3).to(torch.float8_e4m3fn)
+    out = tg.matmul(a.to(dev), b.to(dev))
+    assert out.dtype == torch.float8_e4m3fn and out.shape == (64, 128)
+    ref = R.ref_matmul(a, b)
+    # the reference's own tolerance for fp8 outputs is atol = rtol = 1 (tests/ops/test_matmul.py:231-236)
+    torch.testing.assert_close(out.float().cpu(), ref.float(), rtol=0.13, atol=0.5)
+    out2 = tg.matmul(a.to(dev), b.t().contiguous().to(dev), trans_b=True, out_dtype=torch.bfloat16)
+    assert R.check_tolerance(out2, (a.float() @ b.float()).to(torch.bfloat16))["ok"]
+
+
+# ---------------------------------------------------------- block-scaled path
+@pytest.mark.parametrize(
+    "name", ["w8a8_block_128x128x128.npz", "w8a8_block_256x256x256.npz", "w8a8_block_7x200x320.npz", "w8a8_block_1x128x256.npz"]
+)
+def test_block_scaled_against_reference_fixtures(dev, name):
+    g = load_golden(name)
+    args = [g[k].to(dev) for k in ("A", "B", "As", "Bs")]
+    out = tg.w8a8_block_fp8_matmul(*args, [128, 128])  # default output dtype: float32, as in the reference
+    assert out.dtype == torch.float32
+    # the reference test's tolerance (tests/suites/unsloth/test_fp8.py:224-231) ...
+    torch.testing.assert_close(out.cpu(), g["C_f32"], rtol=5e-2, atol=5e-2)
+    # ... and fp32-accumulation-order tightness
+    torch.testing.assert_close(out.cpu(), g["C_f32"], rtol=1e-4, atol=1e-4)
+    out_bf = tg.w8a8_block_fp8_matmul(*args, None, torch.bfloat16)
+    assert R.check_tolerance(out_bf, g["C_bf16"])["ok"]
+
+
+@pytest.mark.parametrize("M", [128, 4096])
+@pytest.mark.parametrize("N,K", [(24576, 1536), (5120, 12288), (3072, 5120)])
+def test_deepseek_block_scaled_shapes(dev, M, N, K):
+    """BASELINE config 4 at full size."""
+    a8, b8, As, Bs = R.gen_block_scaled_case(M, N, K, seed=4000 + M + N)
+    ref = R.ref_w8a8_block_fp8_matmul(a8, b8, As, Bs, [128, 128], torch.bfloat16)
+    out = tg.w8a8_block_fp8_matmul(a8.to(dev), b8.to(dev), As.to(dev), Bs.to(dev), [128, 128], torch.bfloat16)
+    res = R.check_tolerance(out, ref)
+    assert res["ok"], res
+
+
+@pytest.mark.parametrize("shape", [(512, 1024, 512), (1024, 2048, 1024)])
+def test_block_scaled_reference_test_shapes(dev, shape):
+    """The larger shapes of the reference test, its recipe and seed (test_fp8.py:193-222)."""
+    M, N, K = shape
+    torch.manual_seed(42)
+    A = (torch.randn(M, K) * 0.1).to(torch.float8_e4m3fn)
+    B = (torch.randn(N, K) * 0.1).to(torch.float8_e4m3fn)
+    As = torch.rand(M, K // 128) + 0.1
+    Bs = torch.rand(N // 128, K // 128) + 0.1
+    ref = R.ref_w8a8_block_fp8_matmul(A, B, As, Bs, [128, 128])
+    out = tg.w8a8_block_fp8_matmul(A.to(dev), B.to(dev), As.to(dev), Bs.to(dev), [128, 128])
+    torch.testing.assert_close(out.cpu(), ref, rtol=1e-4, atol=1e-4)
+
+
+def test_block_scaled_split_k_and_leading_dims(dev):
+    os.environ["TILEGYM_B200_SPLITS"] = "3"
+    a8, b8, As, Bs = R.gen_block_scaled_case(2 * 70, 256, 2048, seed=9)
+    ref = R.ref_w8a8_block_fp8_matmul(a8, b8, As, Bs, None, torch.bfloat16).view(2, 70, 256)
+    out = tg.w8a8_block_fp8_matmul(a8.view(2, 70, 2048).to(dev), b8.to(dev), As.view(2, 70, 16).to(dev), Bs.to(dev),
+                                   None, torch.bfloat16)
+    assert out.shape == (2, 70, 256) and R.check_tolerance(out, ref)["ok"]
+
+
+def test_block_scaled_rejects_other_blocks_and_dtypes(dev):
+    a = torch.zeros(128, 128, dtype=torch.float8_e4m3fn, device=dev)
+    with pytest.raises(RuntimeError, match="INVALID_ARGS"):
+        tg.w8a8_block_fp8_matmul(a, a, torch.ones(128, 2, device=dev), torch.ones(2, 2, device=dev), [64, 64])
+    with pytest.raises(RuntimeError, match="INVALID_ARGS"):
+        tg.w8a8_block_fp8_matmul(a, a, torch.ones(128, 1, device=dev), torch.ones(1, 1, device=dev), None, torch.int32)
+
+
+def test_act_quant_feeds_block_scaled_gemm(dev):
+    """Quantise on the GPU, multiply on the GPU, compare with the oracle chain."""
+    x = torch.randn(256, 1024, dtype=torch.bfloat16)
+    w = R.gen_weights(384, 1024, 3)
+    yq, ys = R.ref_act_quant(x)
+    wq, ws = R.ref_weight_quant_block(w)
+    ref = R.ref_w8a8_block_fp8_matmul(yq, wq, ys, ws, None, torch.bfloat16)
+    gy, gs = tg.act_quant(x.to(dev))
+    gw, gws = tg.weight_quant_block(w.to(dev))
+    out = tg.w8a8_block_fp8_matmul(gy, gw, gs, gws, None, torch.bfloat16)
+    assert R.check_tolerance(out, ref)["ok"]

@@ -1,0 +1,104 @@
+"""The CPU oracle against the golden fixtures made from TileGym's own test
+references (tests/golden/make_golden.py), plus self-checks of its helpers."""
+
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN, load_golden
+from oracle import torch_ref as R
+
+
+def test_e4m3_table_matches_torch_cast():
+    tab = torch.from_numpy(R.e4m3_table())
+    via_torch = torch.arange(256, dtype=torch.int32).to(torch.uint8).view(torch.float8_e4m3fn).float()
+    nan = torch.isnan(tab)
+    assert nan.sum() == 2 and bool((torch.isnan(via_torch) == nan).all())
+    assert bool((tab[~nan] == via_torch[~nan]).all())
+    assert float(tab[~nan].abs().max()) == R.E4M3_MAX
+
+
+@pytest.mark.parametrize("name", sorted(os.path.basename(p) for p in glob.glob(os.path.join(GOLDEN, "w8a8_block_*.npz"))))
+def test_block_scaled_gemm_matches_reference_fixture(name):
+    g = load_golden(name)
+    out = R.ref_w8a8_block_fp8_matmul(g["A"], g["B"], g["As"], g["Bs"], [128, 128], torch.float32)
+    # same dequantised operands, same fp32 matmul: equal up to summation order inside torch.matmul
+    torch.testing.assert_close(out, g["C_f32"], rtol=1e-5, atol=1e-5)
+    out_bf16 = R.ref_w8a8_block_fp8_matmul(g["A"], g["B"], g["As"], g["Bs"], None, torch.bfloat16)
+    res = R.check_tolerance(out_bf16, g["C_bf16"], ulps=1.0)
+    assert res["ok"], res
+
+
+@pytest.mark.parametrize("name", ["act_quant_64x1024.npz", "act_quant_128x384.npz", "act_quant_4x128.npz"])
+def test_act_quant_matches_reference_fixture(name):
+    g = load_golden(name)
+    y, s = R.ref_act_quant(g["x"], 128)
+    assert bool((y.view(torch.uint8) == g["y"].view(torch.uint8)).all())
+    assert bool((s == g["s"]).all())
+    if name == "act_quant_4x128.npz":
+        assert float(s[1, 0]) == 1.0  # all-zero block
+
+
+@pytest.mark.parametrize("name", ["weight_dequant_256x256.npz", "weight_dequant_130x200.npz"])
+def test_weight_dequant_matches_reference_fixture(name):
+    g = load_golden(name)
+    y = R.ref_weight_dequant(g["x"], g["s"], 128, torch.bfloat16)
+    assert bool((y.view(torch.int16) == g["y"].view(torch.int16)).all())
+
+
+@pytest.mark.parametrize("name", ["gemm_alpha_beta_256_1.0_0.0.npz", "gemm_alpha_beta_256_1.5_2.0.npz"])
+def test_gemm_alpha_beta_matches_reference_fixture(name):
+    g = load_golden(name)
+    # the reference test's own (bf16) form reproduces its stored output
+    bf = R.ref_gemm_alpha_beta_bf16(g["a"], g["b"], g["c"], g["alpha"], g["beta"])
+    torch.testing.assert_close(bf.float(), g["out"].float(), rtol=1e-2, atol=1e-2)
+    # the fp32-accumulate form the kernels follow agrees within the reference test's tolerance
+    f32 = R.ref_gemm_alpha_beta(g["a"], g["b"], g["c"], g["alpha"], g["beta"])
+    torch.testing.assert_close(f32.float(), g["out"].float(), rtol=1e-2, atol=1e-2)
+
+
+def test_per_tensor_forms_agree():
+    a8, b8, sa, sb = R.gen_per_tensor_case(64, 96, 256, seed=5)
+    x = R.ref_fp8_scaled_mm(a8, b8, sa, sb)
+    c = torch.zeros(64, 96, dtype=torch.bfloat16)
+    y = R.ref_gemm_alpha_beta(a8, b8, c, alpha=float(sa) * float(sb), beta=0.0)
+    assert R.check_tolerance(x, y, ulps=1.0)["ok"]
+
+
+def test_quant_per_tensor_roundtrip_and_zero():
+    x = R.gen_activations(32, 4096, seed=9)
+    q, s = R.ref_quant_per_tensor(x)
+    assert float(s) == pytest.approx(float(x.abs().max()) / 448.0)
+    assert float(q.float().abs().max()) == 448.0
+    q0, s0 = R.ref_quant_per_tensor(torch.zeros(4, 16))
+    assert float(s0) == 1.0 and float(q0.float().abs().max()) == 0.0
+
+
+def test_weight_quant_block_inverts_dequant():
+    w = R.gen_weights(200, 300, seed=4)
+    q, s = R.ref_weight_quant_block(w)
+    assert s.shape == (2, 3)
+    back = R.ref_weight_dequant(q, s, 128, torch.float32)
+    # e4m3 has 3 mantissa bits: relative error <= 2^-4 of the block maximum
+    assert float((back - w).abs().max()) <= float(w.abs().max()) * 2.0 ** -4
+
+
+def test_generators_are_seeded_and_have_outliers():
+    a = R.gen_activations(16, 4096, seed=1)
+    b = R.gen_activations(16, 4096, seed=1)
+    assert bool((a == b).all())
+    col_rms = a.pow(2).mean(0).sqrt()
+    assert int((col_rms > 8).sum()) == 4  # 0.1 % of 4096 channels scaled x20
+
+
+def test_tolerance_checker_accepts_one_ulp_and_rejects_more():
+    ref = torch.full((4, 4), 3.0)
+    ok = ref.clone(); ok[0, 0] += R.ulp_bf16(3.0)
+    bad = ref.clone(); bad[0, 0] += 4 * R.ulp_bf16(3.0)
+    assert R.check_tolerance(ok, ref)["ok"]
+    assert not R.check_tolerance(bad, ref)["ok"]
+    assert not R.check_tolerance(torch.full((4, 4), float("nan")), ref)["ok"]
+    assert R.ulp_bf16(1.0) == 2.0 ** -7

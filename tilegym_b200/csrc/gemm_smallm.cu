@@ -191,12 +191,19 @@ __global__ void __launch_bounds__(kThreads, 2)
           if (m < mv) part[m * kBM] = acc[m];
         if (splitk_arrive_is_last(p.ws_counters + tn * 4 + q, p.splits)) {
           const float* tile_part = p.ws_partial + static_cast<int64_t>(tn) * p.splits * (MP * kBM) + n_local;
+#pragma unroll
+          for (int m = 0; m < MP; ++m) acc[m] = 0.f;
 #pragma unroll 1
-          for (int m = 0; m < mv; ++m) {
-            float sum = 0.f;
-            for (int s2 = 0; s2 < p.splits; ++s2)  // fixed order: bit-stable result
-              sum += __ldcg(tile_part + static_cast<int64_t>(s2) * (MP * kBM) + m * kBM);
-            if (n_ok) smallm_store(p, m, n, fmaf(sum, scale, bias));
+          for (int s2 = 0; s2 < p.splits; ++s2) {  // fixed order: bit-stable result
+            const float* src = tile_part + static_cast<int64_t>(s2) * (MP * kBM);
+#pragma unroll
+            for (int m = 0; m < MP; ++m)  // MP independent loads in flight
+              if (m < mv) acc[m] += __ldcg(src + m * kBM);
+          }
+          if (n_ok) {
+#pragma unroll
+            for (int m = 0; m < MP; ++m)
+              if (m < mv) smallm_store(p, m, n, fmaf(acc[m], scale, bias));
           }
         }
       }

@@ -48,10 +48,23 @@ def _stream(dev: torch.device) -> int:
 
 
 def _workspace(dev: torch.device) -> torch.Tensor:
+    """Scratch of the current stream.  While a CUDA graph is being captured a
+    dedicated per-device buffer is used instead (allocated beforehand, outside
+    any capture), so that no allocation or zero-fill is recorded into the graph;
+    graphs replayed concurrently on one device would share it and race."""
+    nbytes = None
+    cap_key = (dev.index, -1)
+    if cap_key not in _workspaces:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("call a tilegym_b200 GEMM once on this device before capturing it into a CUDA graph")
+        nbytes = int(_lib.lib().tg_fp8_gemm_workspace_bytes(0, 0, 0))
+        _workspaces[cap_key] = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+    if torch.cuda.is_current_stream_capturing():
+        return _workspaces[cap_key]
     key = (dev.index, _stream(dev))
     ws = _workspaces.get(key)
     if ws is None:
-        nbytes = int(_lib.lib().tg_fp8_gemm_workspace_bytes(0, 0, 0))
+        nbytes = nbytes or int(_lib.lib().tg_fp8_gemm_workspace_bytes(0, 0, 0))
         ws = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
         _workspaces[key] = ws
     return ws

@@ -1,0 +1,82 @@
+"""Column-parallel (N-sharded) FP8 GEMM across the GPUs of one node.
+
+The reference is single-GPU; this layer is new.  Rank g of G holds the weight
+rows [g*N/G, (g+1)*N/G) (quantised BEFORE sharding, so the per-tensor scale is
+the global one and results match the 1-GPU GEMM bit for bit), activations are
+replicated, every rank computes C_g = A . B_g^T with the same kernels as the
+1-GPU path, and one all-gather of the bf16 slabs over NCCL / NVLink completes
+the output.  One process per GPU; `torch.distributed` carries the collective.
+The index arithmetic is plain Python so it can be tested on CPU ranks (gloo).
+"""
+
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(N: int, world: int, rank: int, align: int = 128) -> Tuple[int, int]:
+    """Rows [lo, hi) of the weight that `rank` owns.  Shards are equal and a
+    multiple of `align` rows (the weight-scale block), so block scales shard
+    with the rows; N must divide accordingly."""
+    if world < 1 or not (0 <= rank < world):
+        raise ValueError(f"bad rank {rank} of {world}")
+    if N % (world * align) != 0:
+        raise ValueError(f"N={N} does not split into {world} shards of a multiple of {align} rows")
+    per = N // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_weight(B: torch.Tensor, world: int, rank: int, Bs: Optional[torch.Tensor] = None, block: int = 128):
+    """This rank's slab of an already-quantised weight (and of its 128x128 block scales)."""
+    lo, hi = shard_bounds(B.shape[0], world, rank, block)
+    b = B[lo:hi].contiguous()
+    if Bs is None:
+        return b
+    return b, Bs[lo // block : hi // block].contiguous()
+
+
+def gathered_view(slabs: torch.Tensor) -> torch.Tensor:
+    """[G, M, N/G] gathered slabs -> [M, G, N/G] strided view (no copy):
+    view[m, g, j] is C[m, g * N/G + j]."""
+    return slabs.permute(1, 0, 2)
+
+
+def assemble(slabs: torch.Tensor) -> torch.Tensor:
+    """[G, M, N/G] -> contiguous [M, N] (one extra pass over the output)."""
+    G, M, n = slabs.shape
+    return slabs.permute(1, 0, 2).reshape(M, G * n)
+
+
+class ColumnParallelFP8Gemm:
+    """C = (sa*A) . (sb*B)^T with B row-sharded over the ranks of `group`.
+
+    `out_slabs` ([G, M, N/G], bf16) is allocated once; `forward` launches the
+    local GEMM straight into this rank's slab, then all-gathers in place.
+    """
+
+    def __init__(self, B_shard: torch.Tensor, scale_b: torch.Tensor, M: int, group=None,
+                 bias_shard: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16):
+        from . import ops  # the CUDA path; imported here so the index helpers above stay importable on CPU
+
+        self._ops = ops
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.B, self.scale_b, self.bias = B_shard, scale_b, bias_shard
+        n = B_shard.shape[0]
+        self.out_slabs = torch.empty(self.world, M, n, dtype=out_dtype, device=B_shard.device)
+
+    def forward(self, A: torch.Tensor, scale_a: torch.Tensor, gather: bool = True) -> torch.Tensor:
+        mine = self.out_slabs[self.rank]
+        self._ops.fp8_scaled_mm(A, self.B, scale_a, self.scale_b, self.bias, mine.dtype, out=mine)
+        if gather and self.world > 1:
+            dist.all_gather_into_tensor(self.out_slabs.view(-1), mine.view(-1), group=self.group)
+        return self.out_slabs
+
+
+def reference_gather(shards: List[torch.Tensor]) -> torch.Tensor:
+    """What the sharded path must equal: the column-wise concatenation."""
+    return torch.cat(shards, dim=-1)
