@@ -375,15 +375,43 @@ def run_ours_multi(args, rank, world, local_rank):
     dist.destroy_process_group()
 
 
+def run_one(args):
+    """A single kernel on a single problem, for `ncu` captures of a small case."""
+    import tilegym_b200 as tg
+
+    kind, dims = args.one.split(":")
+    M, N, K = (int(v) for v in dims.split(","))
+    dev = torch.device("cuda:0")
+    a8, b8, sa, sb = make_case(M, N, K, dev, 1)
+    if kind == "pertensor":
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        fn = lambda: tg.fp8_scaled_mm(a8, b8, sa, sb, None, torch.bfloat16, out=out)  # noqa: E731
+    elif kind == "blockscaled":
+        As = torch.rand(M, (K + 127) // 128, device=dev) + 0.5
+        Bs = torch.rand((N + 127) // 128, (K + 127) // 128, device=dev) + 0.5
+        fn = lambda: tg.w8a8_block_fp8_matmul(a8, b8, As, Bs, [128, 128], torch.bfloat16)  # noqa: E731
+    else:
+        raise SystemExit("--one KIND must be pertensor or blockscaled")
+    sec = timed(fn, args.steps, args.warmup, dev)
+    print(json.dumps({"one": args.one, "us_per_launch": sec / args.steps * 1e6,
+                      "tflops": 2.0 * M * N * K * args.steps / sec / 1e12,
+                      "gbs": (M * K + N * K + 2 * M * N) * args.steps / sec / 1e9}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--extra", action="store_true", help="also run the decode (HBM-bound) and block-scaled shape sweeps")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--one", default=None, metavar="KIND:M,N,K",
+                    help="profiling aid: run one GEMM (pertensor or blockscaled) of the given size steps+warmup times")
     args = ap.parse_args()
+    if args.one:
+        run_one(args)
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
