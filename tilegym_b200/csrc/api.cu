@@ -264,6 +264,26 @@ int32_t tg_fp8_gemm_pertensor(const TgTensorDesc* C, const TgTensorDesc* A, cons
     return TG_OK;
   }
 
+  // Large problems: CTA-pair kernel (256 x 256 tiles, half the L2 traffic per SM).
+  if (M >= 256 && N >= 256 && env_int("TILEGYM_B200_2CTA", 1) != 0 && getenv("TILEGYM_B200_BN") == nullptr &&
+      getenv("TILEGYM_B200_SPLITS") == nullptr) {
+    p.tiles_m = static_cast<int32_t>((M + 255) / 256);
+    p.tiles_n = static_cast<int32_t>((N + 255) / 256);
+    p.splits = 1;
+    p.kb_per_split = p.num_kb;
+    // tile-rows per raster group: keep the group's A panels (group_m x 256 x K bytes) within ~24 MB of L2
+    int group_m = static_cast<int>((24ll << 20) / (256ll * K));
+    if (group_m < 2) group_m = 2;
+    if (group_m > p.tiles_m) group_m = p.tiles_m;
+    group_m = env_int("TILEGYM_B200_GROUP_M", group_m);
+    if (group_m < 1) group_m = 1;
+    if ((rc = make_map(&tmA, A->ptr, M, K, A->strides[0], 128)) != TG_OK) return rc;
+    if ((rc = make_map(&tmB, B->ptr, N, K, B->strides[0], 128)) != TG_OK) return rc;
+    cudaError_t e2 = launch_gemm_pertensor_2cta(tmA, tmB, p, group_m, st.num_sms, cs);
+    if (e2 != cudaSuccess) return fail(TG_ERR_LAUNCH, "GEMM (CTA pair) launch failed: %s", cudaGetErrorString(e2));
+    return TG_OK;
+  }
+
   int bn = choose_bn(M, N, st.num_sms);
   bn = env_int("TILEGYM_B200_BN", bn);
   if (bn != 256 && bn != 128 && bn != 64) return fail(TG_ERR_ARGS, "TILEGYM_B200_BN must be 64, 128 or 256");

@@ -1,0 +1,293 @@
+// Per-tensor-scaled FP8 GEMM for sm_100a, CTA-pair version (tcgen05 cta_group::2):
+//   C[M,N] = alpha*sa*sb * (A[M,K] . B[N,K]^T) + bias + beta*C
+// Two CTAs of a cluster (two SMs) work on one 256 x 256 output tile.  Each CTA
+// TMA-loads only its own half of the operands (128 rows of A, 128 rows of B) and
+// keeps its own 128 x 256 half of the accumulator in its TMEM; the leader CTA
+// issues tcgen05.mma with M = 256, which reads A and B from both CTAs' shared
+// memory.  Compared with one CTA per 128 x 256 tile this halves the B bytes
+// each SM pulls from L2 per flop (32 KB instead of 48 KB per 128-deep k-block),
+// which is what bounds the single-CTA kernel.  No multicast copy is used: each
+// CTA fetches exactly the bytes it owns.
+// Roles per CTA: warp 0 TMA producer, warp 1 MMA issuer (leader only) and TMEM
+// owner, warps 2..5 epilogue.  Two TMEM accumulator buffers overlap the
+// epilogue of tile i with the main loop of tile i+1.
+#include "tg_gemm_common.cuh"
+
+namespace tg {
+
+namespace {
+
+constexpr int kThreads = 192;
+constexpr int kBN = 256;              // tile width (both CTAs)
+constexpr int kBNHalf = 128;          // B rows each CTA loads
+constexpr int kStages = 6;
+constexpr int kABytes = kBM * kBK;    // 16 KB
+constexpr int kBBytes = kBNHalf * kBK;  // 16 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kTmemCols = 2 * kBN;    // 512: two accumulator buffers
+constexpr int kCtrlBytes = 256;
+constexpr int kSmemBytes = kStages * kStageBytes + kCtrlBytes + 1024;
+static_assert((2 * kStages + 4) * 8 + 8 <= kCtrlBytes, "control block");
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load whose completion bytes are counted on an mbarrier that may live in the peer CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void mma_f8f6f4_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive (count 1) on the barrier at `bar_cluster_addr` once all tcgen05 operations issued so far by
+// this thread, for the CTA pair, have completed.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
+               : "memory");
+}
+
+// Pair-tile order: groups of `group_m` tile-rows (256 rows each), column by column inside a group.
+__device__ __forceinline__ void pair_tile_coords(int t, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+  const int per_group = group_m * tiles_n;
+  const int g = t / per_group;
+  const int first_m = g * group_m;
+  const int gsize = min(tiles_m - first_m, group_m);
+  const int r = t - g * per_group;
+  tm = first_m + r % gsize;
+  tn = r / gsize;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+    tg_fp8_gemm_pertensor_2cta_kernel(const __grid_constant__ CUtensorMap tmA,
+                                      const __grid_constant__ CUtensorMap tmB, const GemmParams p, int group_m) {
+  constexpr int S = kStages;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+  const uint32_t a_base = base;
+  const uint32_t b_base = base + S * kABytes;
+  uint8_t* ctrl = smem + S * kStageBytes;
+  const uint32_t bar_full = smem_u32(ctrl);      // S barriers; only the leader's are used
+  const uint32_t bar_empty = bar_full + 8 * S;   // S barriers, one set per CTA
+  const uint32_t bar_tfull = bar_empty + 8 * S;  // 2 barriers, one set per CTA
+  const uint32_t bar_tempty = bar_tfull + 16;    // 2 barriers; only the leader's are used
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + (2 * S + 4) * 8);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const bool leader = (rank == 0);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) {
+      mbar_init(bar_full + 8 * i, 1);   // one arrive.expect_tx by the leader's producer
+      mbar_init(bar_empty + 8 * i, 1);  // one commit by the leader's MMA thread
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_tfull + 8 * i, 1);   // one commit by the leader's MMA thread
+      mbar_init(bar_tempty + 8 * i, 8);  // four epilogue warps of each CTA
+    }
+    *abort_flag = 0u;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised before anyone signals across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;  // pair tiles (256 x 256)
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer (both CTAs)
+    if (lane == 0) {
+      prefetch_tmap(&tmA);
+      prefetch_tmap(&tmB);
+      const uint32_t leader_full = map_to_cta(bar_full, 0);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+        int tm, tn;
+        pair_tile_coords(t, p.tiles_m, p.tiles_n, group_m, tm, tn);
+        const int a_row = tm * 256 + static_cast<int>(rank) * kBM;
+        const int b_row = tn * kBN + static_cast<int>(rank) * kBNHalf;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag)) {
+            report_timeout(p.status, kRoleProducer * 1000 + 31);
+            ok = false;
+            break;
+          }
+          if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, 2 * kStageBytes);  // both CTAs' bytes
+          tma_load_2d_pair(a_base + s * kABytes, &tmA, leader_full + 8 * s, kb * kBK, a_row);
+          tma_load_2d_pair(b_base + s * kBBytes, &tmB, leader_full + 8 * s, kb * kBK, b_row);
+          if (++s == S) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer (leader CTA only)
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc_e4m3_f32(256, kBN);
+      const uint32_t peer_empty = map_to_cta(bar_empty, 1);
+      const uint32_t peer_tfull = map_to_cta(bar_tfull, 1);
+      int s = 0;
+      uint32_t ph = 0;
+      int buf = 0;
+      uint32_t aph = 0;
+      bool ok = true;
+      for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+        if (!mbar_wait(bar_tempty + 8 * buf, aph ^ 1u, abort_flag)) {
+          report_timeout(p.status, kRoleMma * 1000 + 31);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * kBN);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag)) {
+            report_timeout(p.status, kRoleMma * 1000 + 32);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t adesc = make_kmajor_sw128_desc(a_base + s * kABytes);
+          const uint64_t bdesc = make_kmajor_sw128_desc(b_base + s * kBBytes);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            mma_f8f6f4_pair(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit_pair(bar_empty + 8 * s);   // this CTA's stage is free again ...
+          tc_commit_pair(peer_empty + 8 * s);  // ... and so is the peer's
+          if (++s == S) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+        if (!ok) break;
+        tc_commit_pair(bar_tfull + 8 * buf);
+        tc_commit_pair(peer_tfull + 8 * buf);
+        buf ^= 1;
+        if (buf == 0) aph ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs)
+    const int q = warp & 3;
+    float scale = p.alpha;
+    if (p.scale_a != nullptr) scale *= __ldg(p.scale_a);
+    if (p.scale_b != nullptr) scale *= __ldg(p.scale_b);
+    const bool vec_ok = c_rows_aligned(p);
+    const uint32_t leader_tempty = map_to_cta(bar_tempty, 0);
+    int buf = 0;
+    uint32_t aph = 0;
+    for (int t = pair_id; t < num_tiles; t += num_pairs) {
+      int tm, tn;
+      pair_tile_coords(t, p.tiles_m, p.tiles_n, group_m, tm, tn);
+      bool w = mbar_wait(bar_tfull + 8 * buf, aph, abort_flag);
+      w = __all_sync(0xffffffffu, w);
+      if (!w) {
+        report_timeout(p.status, kRoleEpilogue * 1000 + 31);
+        break;
+      }
+      tc_fence_after();
+      const int64_t row = static_cast<int64_t>(tm) * 256 + static_cast<int>(rank) * kBM + q * 32 + lane;
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * kBN);
+#pragma unroll 1
+      for (int c = 0; c < kBN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_addr + c * 32, r);
+        tmem_ld_wait();
+        if (c == kBN / 32 - 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(leader_tempty + 8 * buf);
+        }
+        if (row < p.M) epilogue_store32(p, row, tn * kBN + c * 32, reinterpret_cast<const float*>(r), scale, vec_ok);
+      }
+      buf ^= 1;
+      if (buf == 0) aph ^= 1u;
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  // Neither CTA may leave while the other can still read its shared memory
+  // (pair MMAs) or signal its barriers, so both meet at a cluster barrier first.
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_gemm_pertensor_2cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
+                                       int group_m, int num_sms, cudaStream_t stream) {
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(tg_fp8_gemm_pertensor_2cta_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  int pairs = num_sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  tg_fp8_gemm_pertensor_2cta_kernel<<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmA, tmB, p, group_m);
+  return cudaGetLastError();
+}
+
+}  // namespace tg

@@ -43,6 +43,9 @@ struct GemmParams {
 // Launchers (each sets its kernel's shared-memory attribute once per device).
 cudaError_t launch_gemm_pertensor(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int bn,
                                   int num_sms, cudaStream_t stream);
+// CTA-pair (cta_group::2) kernel: 256 x 256 tiles; tmA and tmB both box 128 rows; p.tiles_* count 256-wide tiles.
+cudaError_t launch_gemm_pertensor_2cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
+                                       int group_m, int num_sms, cudaStream_t stream);
 cudaError_t launch_gemm_blockscaled(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
                                     int num_sms, cudaStream_t stream);
 // Swap-AB split-K kernel for M <= 64: tmW boxes 128 weight rows, tmX boxes `mp` activation rows.
