@@ -97,6 +97,24 @@ TG_API int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc
                                 int32_t block_k, uint64_t workspace, uint64_t workspace_bytes,
                                 int32_t device_id, uint64_t stream);
 
+/* The small-M (M <= 64) path of tg_fp8_gemm_pertensor for callers that cannot
+ * allocate device memory - a server whose pool already owns the GPU, or a
+ * decode loop that must never reach cudaMalloc / cudaFree because they
+ * synchronise the device.  It has no counterpart in the reference.
+ * Same arithmetic and arguments as tg_fp8_gemm_pertensor minus the workspace:
+ * the split-K scratch is a fixed 8 MiB + 16 KiB __device__ array inside the
+ * library (held on every GPU that loads the library until the process
+ * exits).  Limits: M <= 64 and N <= 131072, otherwise -6 with a message.
+ * All calls on a device share that array: calls that overlap on the GPU race;
+ * calls ordered on one stream are fine (each call clears the counters it
+ * uses).  The first call on a device resolves the array's address and
+ * configures the kernel; make it before any stream capture.  Calls no
+ * cudaMalloc, cudaFree or other allocating routine. */
+TG_API int32_t tg_fp8_gemm_pertensor_smallm_static(const TgTensorDesc* C, const TgTensorDesc* A,
+                                                   const TgTensorDesc* B, uint64_t scale_a, uint64_t scale_b,
+                                                   float alpha, const TgTensorDesc* bias, float beta,
+                                                   int32_t device_id, uint64_t stream);
+
 /* Bytes of scratch the two GEMM entry points may need for a problem size. */
 TG_API uint64_t tg_fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
 

@@ -180,6 +180,21 @@ int choose_bn(int64_t M, int64_t N, int num_sms) {
 }
 
 }  // namespace
+
+// Thin exports of the helpers above for entry points that live in other files.
+int32_t api_fail(int32_t rc, const char* msg) { return fail(rc, "%s", msg); }
+int32_t api_check_operand(const TgTensorDesc* t, const char* name) { return check_operand(t, name); }
+int32_t api_check_output(const TgTensorDesc* C, int64_t M, int64_t N) { return check_output(C, M, N); }
+int32_t api_make_map(CUtensorMap* map, uint64_t ptr, int64_t rows, int64_t K, int64_t pitch, int box_rows) {
+  return make_map(map, ptr, rows, K, pitch, box_rows);
+}
+int32_t api_init_device(int dev, int* num_sms, int32_t** status) {
+  int32_t rc = init_device(dev);
+  if (rc != TG_OK) return rc;
+  *num_sms = g_dev[dev].num_sms;
+  *status = g_dev[dev].status;
+  return TG_OK;
+}
 }  // namespace tg
 
 using namespace tg;

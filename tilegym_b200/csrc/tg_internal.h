@@ -52,6 +52,13 @@ cudaError_t launch_gemm_blockscaled(const CUtensorMap& tmA, const CUtensorMap& t
 cudaError_t launch_gemm_smallm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int mp,
                                cudaStream_t stream);
 
+// Helpers of the main entry-point file, for entry points defined elsewhere.
+int32_t api_fail(int32_t rc, const char* msg);
+int32_t api_check_operand(const TgTensorDesc* t, const char* name);
+int32_t api_check_output(const TgTensorDesc* C, int64_t M, int64_t N);
+int32_t api_make_map(CUtensorMap* map, uint64_t ptr, int64_t rows, int64_t K, int64_t pitch, int box_rows);
+int32_t api_init_device(int dev, int* num_sms, int32_t** status);  // call with `dev` current
+
 cudaError_t launch_act_quant(void* y, float* s, const void* x, int x_dtype, int64_t n_blocks, cudaStream_t stream);
 cudaError_t launch_weight_dequant(void* y, int y_dtype, const uint8_t* x, const float* s, int64_t M, int64_t N,
                                   int64_t lds, cudaStream_t stream);

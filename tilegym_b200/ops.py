@@ -252,6 +252,32 @@ def fp8_scaled_mm(
     return out
 
 
+def fp8_scaled_mm_no_alloc(
+    A: torch.Tensor,
+    B: torch.Tensor,
+    scale_a: Optional[torch.Tensor],
+    scale_b: Optional[torch.Tensor],
+    out: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """`fp8_scaled_mm` for decode-sized inputs (at most 64 rows) without any
+    device allocation, for callers whose memory pool owns the GPU or whose
+    loop must not reach the allocator.  Everything is supplied by the caller
+    (contiguous e4m3 operands, one-element fp32 device scales or None, the
+    output tensor); the split-K scratch is a fixed array inside the library,
+    shared by all calls on the device, so do not overlap calls on different
+    streams.  Make the first call on a device before capturing any stream."""
+    dev = _need_cuda(A, B, out)
+    M, K = A.shape
+    rc = _lib.lib().tg_fp8_gemm_pertensor_smallm_static(
+        _lib.ref(_lib.desc(out)), _lib.ref(_lib.desc(A)), _lib.ref(_lib.desc(B)),
+        scale_a.data_ptr() if scale_a is not None else 0, scale_b.data_ptr() if scale_b is not None else 0,
+        1.0, _lib.ref(_lib.desc(bias)), 0.0, dev.index, _stream(dev),
+    )
+    _lib.check_rc(rc)
+    return out
+
+
 def gemm_alpha_beta(
     a: torch.Tensor,
     b: torch.Tensor,
