@@ -30,7 +30,13 @@ def test_fp8linear_matches_oracle_chain(dev, mode, bias):
     mod = FP8Linear.from_linear(lin.to(dev), mode)
     out = mod(x.to(dev))
     assert out.shape == (4, 33, 384) and out.dtype == torch.bfloat16
-    assert R.check_tolerance(out.view(-1, 384), ref, ulps=3.0 if bias and mode == "block" else 2.0)["ok"]
+    if bias and mode == "block":
+        # the bias is added after the bf16 rounding here: near-cancelling elements keep the rounding
+        # error of the pre-bias magnitude, so only the absolute bound applies
+        err = float((out.view(-1, 384).float().cpu() - ref.float()).abs().max())
+        assert err <= 3.0 * R.ulp_bf16(float(ref.float().abs().max()))
+    else:
+        assert R.check_tolerance(out.view(-1, 384), ref)["ok"]
 
 
 def test_linear_helper_caches_quantised_module(dev):
