@@ -19,7 +19,8 @@ pytestmark = pytest.mark.gpu
 import tilegym_b200 as tg  # noqa: E402
 from tilegym_b200 import _lib  # noqa: E402
 
-KNOBS = ("TILEGYM_B200_BN", "TILEGYM_B200_SPLITS", "TILEGYM_B200_FORCE_PATH")
+KNOBS = ("TILEGYM_B200_BN", "TILEGYM_B200_SPLITS", "TILEGYM_B200_FORCE_PATH", "TILEGYM_B200_SMALLM_WS",
+         "TILEGYM_B200_2CTA", "TILEGYM_B200_GROUP_M")
 
 
 @pytest.fixture(autouse=True)
@@ -91,6 +92,35 @@ def test_output_dtypes_and_unaligned_n(dev, out_dtype, M):
 def test_split_k_matches_unsplit(dev, splits, M):
     os.environ["TILEGYM_B200_SPLITS"] = splits
     run_pt(dev, M, 512, 4096, seed=5)
+
+
+@pytest.mark.parametrize("M", [1, 16, 40, 64])
+@pytest.mark.parametrize("ws", ["0", "1"])
+def test_small_m_cluster_and_workspace_reductions_agree(dev, M, ws):
+    """The K splits are reduced either through distributed shared memory (cluster, default) or through
+    the global workspace; both add the partial sums in split order, so the bits are identical."""
+    a8, b8, sa, sb = (t.to(dev) for t in R.gen_per_tensor_case(M, 1024, 8192, 60 + M))
+    os.environ["TILEGYM_B200_SPLITS"] = "4"  # same split count on both paths
+    os.environ["TILEGYM_B200_SMALLM_WS"] = ws
+    out = tg.fp8_scaled_mm(a8, b8, sa, sb)
+    os.environ["TILEGYM_B200_SMALLM_WS"] = "1" if ws == "0" else "0"
+    other = tg.fp8_scaled_mm(a8, b8, sa, sb)
+    assert R.check_tolerance(out, R.ref_fp8_scaled_mm(a8.cpu(), b8.cpu(), sa.cpu(), sb.cpu()))["ok"]
+    assert torch.equal(out, other)
+
+
+@pytest.mark.parametrize("group_m", ["1", "3", "64"])
+def test_cta_pair_kernel_raster_groups(dev, group_m):
+    os.environ["TILEGYM_B200_GROUP_M"] = group_m
+    run_pt(dev, 1280, 1536, 512, seed=12, bias=True)
+
+
+def test_cta_pair_and_single_cta_kernels_agree(dev):
+    a8, b8, sa, sb = (t.to(dev) for t in R.gen_per_tensor_case(1024, 768, 2048, 13))
+    pair = tg.fp8_scaled_mm(a8, b8, sa, sb)
+    os.environ["TILEGYM_B200_2CTA"] = "0"
+    single = tg.fp8_scaled_mm(a8, b8, sa, sb)
+    assert torch.equal(pair, single)  # same fp32 accumulation order inside the tensor core, same epilogue
 
 
 def test_split_k_is_bit_stable(dev):

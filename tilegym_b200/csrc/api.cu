@@ -159,6 +159,35 @@ void choose_splits(int tiles, int num_kb, int num_sms, int64_t tile_floats, int 
   *kbps = per;
 }
 
+// Small-M decomposition: 128 weight rows per tile and the largest power-of-two number of K splits
+// (the cluster size, at most 8) that still fits all CTAs on the GPU at two per SM with at least two
+// k-blocks each.  Measured on B200: this beats both fewer splits (too few bytes in flight) and
+// narrower tiles.  TILEGYM_B200_SPLITS / TILEGYM_B200_TILE_ROWS override it.
+void choose_smallm_config(int64_t N, int num_kb, int num_sms, int mp, int32_t* tile_rows, int32_t* splits,
+                          int32_t* kbps) {
+  (void)mp;
+  const int best_tr = 128;
+  const int64_t tiles = (N + best_tr - 1) / best_tr;
+  int best_s = 1;
+  for (int s = 2; s <= 8; s *= 2) {
+    if (tiles * s > 2ll * num_sms || num_kb / s < 2) break;
+    best_s = s;
+  }
+  int s = env_int("TILEGYM_B200_SPLITS", best_s);
+  if (s < 1) s = 1;
+  if (s > 8) s = 8;
+  if (s > num_kb) s = num_kb;
+  int per = (num_kb + s - 1) / s;
+  s = (num_kb + per - 1) / per;
+  int tr = env_int("TILEGYM_B200_TILE_ROWS", best_tr);
+  tr = (tr / 8) * 8;
+  if (tr < 16) tr = 16;
+  if (tr > 128) tr = 128;
+  *tile_rows = tr;
+  *splits = s;
+  *kbps = per;
+}
+
 int choose_bn(int64_t M, int64_t N, int num_sms) {
   // Estimated time = waves x tile width x a per-width efficiency factor
   // (narrow tiles re-read A from shared memory more often per flop).
@@ -265,16 +294,22 @@ int32_t tg_fp8_gemm_pertensor(const TgTensorDesc* C, const TgTensorDesc* A, cons
     const int mp = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     p.tiles_m = 1;
     p.tiles_n = static_cast<int32_t>((N + 127) / 128);
-    if (have_ws && p.tiles_n * 4 <= static_cast<int64_t>(kWsCounterBytes / 4))
-      choose_splits(p.tiles_n, p.num_kb, st.num_sms, static_cast<int64_t>(mp) * 128, 2 * st.num_sms, 2, &p.splits,
-                    &p.kb_per_split);
-    else {
+    // Default: the K splits of a tile form a thread-block cluster (1, 2, 4 or 8 CTAs) and reduce through
+    // distributed shared memory; TILEGYM_B200_SMALLM_WS=1 selects the global-workspace reduction.
+    const bool use_ws = env_int("TILEGYM_B200_SMALLM_WS", 0) != 0;
+    const bool ws_ok = have_ws;
+    choose_smallm_config(N, p.num_kb, st.num_sms, mp, &p.tile_rows, &p.splits, &p.kb_per_split);
+    if (use_ws && !ws_ok) {
       p.splits = 1;
       p.kb_per_split = p.num_kb;
     }
-    if ((rc = make_map(&tmB, B->ptr, N, K, B->strides[0], 128)) != TG_OK) return rc;
+    p.tiles_n = static_cast<int32_t>((N + p.tile_rows - 1) / p.tile_rows);
+    if (use_ws && p.tiles_n * 4 > static_cast<int64_t>(kWsCounterBytes / 4))
+      return fail(TG_ERR_ARGS, "N is too large for the workspace reduction");
+    if ((rc = make_map(&tmB, B->ptr, N, K, B->strides[0], p.tile_rows)) != TG_OK) return rc;
     if ((rc = make_map(&tmA, A->ptr, M, K, A->strides[0], mp)) != TG_OK) return rc;
-    cudaError_t e = launch_gemm_smallm(tmB, tmA, p, mp, cs);
+    cudaError_t e = (use_ws || p.splits == 1) ? launch_gemm_smallm(tmB, tmA, p, mp, cs)
+                                              : launch_gemm_smallm_cluster(tmB, tmA, p, mp, cs);
     if (e != cudaSuccess) return fail(TG_ERR_LAUNCH, "small-M GEMM launch failed: %s", cudaGetErrorString(e));
     return TG_OK;
   }

@@ -1,15 +1,20 @@
 // Small-M (decode, M <= 64) per-tensor-scaled FP8 GEMM for sm_100a.
-// The problem is a weight-streaming one (N*K bytes of e4m3 against a few
-// rows of activations), bound by HBM bandwidth, so the kernel is built
-// around bytes in flight rather than tensor-pipe occupancy:
-//   * swap-AB: 128 weight rows ride the MMA's M axis (TMEM lanes), the M
-//     activation rows (padded to MP = 16/32/64 by TMA zero fill) are the MMA's
-//     N, so no tensor-core work is wasted on padding rows of a 128-row tile;
-//   * split-K: the grid is (weight-row tiles) x (K splits), about two CTAs per
-//     SM, each streaming its slab through a deep TMA ring;
-//   * partial sums go to an fp32 workspace; the warp that arrives last for a
-//     (tile, lane-quadrant) adds them in split order and runs the epilogue, so
-//     nobody waits and the result does not depend on arrival order.
+// The problem is a weight-streaming one (N*K bytes of e4m3 against a few rows
+// of activations), bound by HBM bandwidth, so the kernel is built around bytes
+// in flight and a short tail rather than tensor-pipe occupancy:
+//   * swap-AB: up to 128 weight rows ride the MMA's M axis (TMEM lanes), the M
+//     activation rows (padded to MP = 16/32/64 by TMA zero fill) are the MMA's N;
+//   * the grid is (weight-row tiles) x (K splits), about two CTAs per SM; the
+//     host picks the rows per tile (a multiple of 16, at most 128) so that the
+//     CTAs spread evenly over the SMs;
+//   * the first ring of TMA loads is issued before the CTA's set-up barrier;
+//   * split-K, cluster variant: the CTAs that share a weight tile form one
+//     thread-block cluster; every CTA PUSHES its fp32 partial rows into the
+//     shared memory of the CTA that owns them (output row m belongs to rank
+//     m % splits), one cluster barrier later each owner adds its rows in split
+//     order and stores them.  No global scratch, atomics or fences;
+//   * split-K, workspace variant: partial tiles go to a global fp32 workspace
+//     and the last-arriving warp per (tile, quadrant) reduces them.
 // Same contract as the large-M kernel: C = alpha*sa*sb * A.B^T + bias + beta*C.
 #include "tg_gemm_common.cuh"
 
@@ -19,16 +24,34 @@ namespace {
 
 constexpr int kThreads = 192;  // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
 
+// Debug aid (compile with -DTG_TRACE): per-CTA %globaltimer stamps of the kernel's phases, written to the
+// partial-sum area of the workspace (unused by the cluster variant) as [cta][16] uint64.
+#ifdef TG_TRACE
+#define TG_STAMP(slot)                                                                                   \
+  do {                                                                                                   \
+    if (p.ws_partial != nullptr)                                                                         \
+      reinterpret_cast<unsigned long long*>(p.ws_partial)[blockIdx.x * 16 + (slot)] = globaltimer_ns(); \
+  } while (0)
+#else
+#define TG_STAMP(slot) \
+  do {                 \
+  } while (0)
+#endif
+
 template <int MP>
 struct SmCfg {
-  static constexpr int kWBytes = kBM * kBK;  // 128 weight rows x 128 B
+  static constexpr int kWBytes = kBM * kBK;  // room for 128 weight rows x 128 B per stage
   static constexpr int kXBytes = MP * kBK;
   static constexpr int kStageBytes = kWBytes + kXBytes;
-  static constexpr int kStages = (MP == 16) ? 6 : (MP == 32 ? 5 : 4);
+  static constexpr int kStages = (MP == 16) ? 5 : (MP == 32 ? 4 : 3);
   static constexpr int kTmemCols = MP < 32 ? 32 : MP;
+  // cluster reduction inbox: splits * ceil(M / splits) <= MP + 7 partial rows of 128 floats
+  static constexpr int kInboxRows = MP + 8;
+  static constexpr int kInboxBytes = kInboxRows * kBM * 4;
   static constexpr int kCtrlBytes = 128;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kCtrlBytes + 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kInboxBytes + kCtrlBytes + 1024;
   static_assert((2 * kStages + 1) * 8 + 8 <= kCtrlBytes, "control block");
+  static_assert(2 * kSmemBytes <= 227 * 1024, "two CTAs per SM");
 };
 
 __device__ __forceinline__ void smallm_store(const GemmParams& p, int m, int64_t n, float v) {
@@ -48,7 +71,30 @@ __device__ __forceinline__ void smallm_store(const GemmParams& p, int m, int64_t
   }
 }
 
-template <int MP>
+__device__ __forceinline__ uint32_t sm_cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t sm_map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void sm_st_cluster_f32(uint32_t cluster_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void sm_cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void sm_cluster_arrive_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void sm_cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <int MP, bool CLUSTER>
 __global__ void __launch_bounds__(kThreads, 2)
     tg_fp8_gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                               const GemmParams p) {
@@ -60,7 +106,8 @@ __global__ void __launch_bounds__(kThreads, 2)
   uint8_t* smem = smem_raw + (base - raw);
   const uint32_t w_base = base;
   const uint32_t x_base = base + S * Cfg::kWBytes;
-  uint8_t* ctrl = smem + S * Cfg::kStageBytes;
+  float* inbox = reinterpret_cast<float*>(smem + S * Cfg::kStageBytes);
+  uint8_t* ctrl = smem + S * Cfg::kStageBytes + Cfg::kInboxBytes;
   const uint32_t bar_full = smem_u32(ctrl);
   const uint32_t bar_empty = bar_full + 8 * S;
   const uint32_t bar_tfull = bar_empty + 8 * S;
@@ -69,6 +116,17 @@ __global__ void __launch_bounds__(kThreads, 2)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) TG_STAMP(0);
+
+  // one work unit per CTA: weight-row tile tn (p.tile_rows rows), K split sp
+  const int u = blockIdx.x;
+  const int tn = u / p.splits, sp = u - tn * p.splits;
+  const int kb0 = sp * p.kb_per_split;
+  const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
+  const uint32_t stage_tx = static_cast<uint32_t>(p.tile_rows * kBK + Cfg::kXBytes);
+  const int row0 = tn * p.tile_rows;
+  uint64_t pol_w = 0, pol_x = 0;
+  int pre = 0;  // k-blocks whose loads were issued before the set-up barrier
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) {
@@ -78,37 +136,43 @@ __global__ void __launch_bounds__(kThreads, 2)
     mbar_init(bar_tfull, 1);
     *abort_flag = 0u;
     fence_mbar_init();
+    // The ring is empty and only this thread touches the full barriers until the barrier below:
+    // start the weight stream right away, TMEM allocation and the other warps catch up meanwhile.
+    pol_w = policy_evict_first();  // weights are read once
+    pol_x = policy_evict_last();   // activations are re-read by every CTA
+    pre = min(S, kb1 - kb0);
+    for (int i = 0; i < pre; ++i) {
+      mbar_arrive_expect_tx(bar_full + 8 * i, stage_tx);
+      tma_load_2d_hint(w_base + i * Cfg::kWBytes, &tmW, bar_full + 8 * i, (kb0 + i) * kBK, row0, pol_w);
+      tma_load_2d_hint(x_base + i * Cfg::kXBytes, &tmX, bar_full + 8 * i, (kb0 + i) * kBK, 0, pol_x);
+    }
+    TG_STAMP(2);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
     tmem_relinquish();
   }
+  if constexpr (CLUSTER) {
+    __syncwarp();
+    sm_cluster_arrive_relaxed();  // "this CTA runs" (nothing to publish): matched by the wait before the pushes
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-
-  // one work unit per CTA: weight-row tile tn, K split sp
-  const int u = blockIdx.x;
-  const int tn = u / p.splits, sp = u - tn * p.splits;
-  const int kb0 = sp * p.kb_per_split;
-  const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
+  if (threadIdx.x == 0) TG_STAMP(1);
 
   if (warp == 0) {
     if (lane == 0) {
-      prefetch_tmap(&tmW);
-      prefetch_tmap(&tmX);
-      const uint64_t pol_w = policy_evict_first();  // weights are read once
-      const uint64_t pol_x = policy_evict_last();   // activations are re-read by every CTA
-      int s = 0;
-      uint32_t ph = 0;
-      for (int kb = kb0; kb < kb1; ++kb) {
+      int s = pre % S;
+      uint32_t ph = (pre == S) ? 1u : 0u;
+      for (int kb = kb0 + pre; kb < kb1; ++kb) {
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag)) {
           report_timeout(p.status, kRoleProducer * 1000 + 21);
           break;
         }
-        mbar_arrive_expect_tx(bar_full + 8 * s, Cfg::kStageBytes);
-        tma_load_2d_hint(w_base + s * Cfg::kWBytes, &tmW, bar_full + 8 * s, kb * kBK, tn * kBM, pol_w);
+        mbar_arrive_expect_tx(bar_full + 8 * s, stage_tx);
+        tma_load_2d_hint(w_base + s * Cfg::kWBytes, &tmW, bar_full + 8 * s, kb * kBK, row0, pol_w);
         tma_load_2d_hint(x_base + s * Cfg::kXBytes, &tmX, bar_full + 8 * s, kb * kBK, 0, pol_x);
         if (++s == S) {
           s = 0;
@@ -129,10 +193,12 @@ __global__ void __launch_bounds__(kThreads, 2)
           break;
         }
         tc_fence_after();
+        if (kb == kb0) TG_STAMP(3);
         const uint64_t wdesc = make_kmajor_sw128_desc(w_base + s * Cfg::kWBytes);
         const uint64_t xdesc = make_kmajor_sw128_desc(x_base + s * Cfg::kXBytes);
 #pragma unroll
         for (int k = 0; k < kBK / kUmmaK; ++k) {
+          // the MMA always spans 128 lanes; lanes >= tile_rows see stale shared memory and are never stored
           mma_f8f6f4(tmem_base, wdesc + 2u * k, xdesc + 2u * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
         }
         tc_commit(bar_empty + 8 * s);
@@ -142,26 +208,31 @@ __global__ void __launch_bounds__(kThreads, 2)
         }
       }
       if (ok) tc_commit(bar_tfull);
+      TG_STAMP(4);
     }
-  } else {
-    const int q = warp & 3;
-    const int n_local = q * 32 + lane;
-    const int64_t n = static_cast<int64_t>(tn) * kBM + n_local;
-    const bool n_ok = n < p.N;
-    float scale = p.alpha;
+  }
+
+  // ---------------------------------------------------------------- epilogue
+  const int q = warp & 3;
+  const int n_local = q * 32 + lane;
+  const int64_t n = static_cast<int64_t>(row0) + n_local;
+  const bool n_ok = (warp >= 2) && n_local < p.tile_rows && n < p.N;
+  const int mv = p.M < MP ? p.M : MP;
+  float scale = p.alpha, bias = 0.f;
+  float acc[MP];
+  bool have_acc = false;
+  if (warp >= 2) {
     if (p.scale_a != nullptr) scale *= __ldg(p.scale_a);
     if (p.scale_b != nullptr) scale *= __ldg(p.scale_b);
-    const float bias = (p.bias != nullptr && n_ok) ? load_bias(p.bias, p.bias_dtype, static_cast<int>(n)) : 0.f;
-    const int mv = p.M < MP ? p.M : MP;
-
+    if (p.bias != nullptr && n_ok) bias = load_bias(p.bias, p.bias_dtype, static_cast<int>(n));
     bool w = mbar_wait(bar_tfull, 0u, abort_flag);
     w = __all_sync(0xffffffffu, w);
     if (!w) {
       report_timeout(p.status, kRoleEpilogue * 1000 + 21);
     } else {
       tc_fence_after();
+      if (threadIdx.x == 64) TG_STAMP(5);
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-      float acc[MP];
       if constexpr (MP == 16) {
         uint32_t r[16];
         tmem_ld_32x16(t_addr, r);
@@ -178,33 +249,79 @@ __global__ void __launch_bounds__(kThreads, 2)
           for (int j = 0; j < 32; ++j) acc[c * 32 + j] = __uint_as_float(r[j]);
         }
       }
-      if (p.splits == 1) {
+      have_acc = true;
+    }
+  }
+
+  if (p.splits == 1) {
+    if (have_acc && n_ok) {
+#pragma unroll
+      for (int m = 0; m < MP; ++m)
+        if (m < mv) smallm_store(p, m, n, fmaf(acc[m], scale, bias));
+    }
+  } else if constexpr (CLUSTER) {
+    // Output row m is finished by the CTA of rank m % splits; partial row m of split sp goes to slot
+    // [sp][m / splits] of that CTA's inbox.  rows_per_rank = ceil(mv / splits).
+    const int rpr = (mv + p.splits - 1) / p.splits;
+    __syncwarp();
+    sm_cluster_wait();  // every CTA of the cluster has started: its shared memory may be written
+    if (have_acc && n_local < p.tile_rows) {
+      const uint32_t inbox_addr = smem_u32(inbox) + static_cast<uint32_t>((sp * rpr) * kBM + n_local) * 4u;
+      uint32_t peer[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) peer[r] = sm_map_to_cta(inbox_addr, r < p.splits ? r : 0);
+      int r = 0, j = 0;  // m = j * splits + r
+#pragma unroll
+      for (int m = 0; m < MP; ++m) {
+        if (m < mv) {
+          uint32_t dst = peer[0];
+#pragma unroll
+          for (int t = 1; t < 8; ++t) dst = (r == t) ? peer[t] : dst;
+          sm_st_cluster_f32(dst + static_cast<uint32_t>(j) * (kBM * 4u), acc[m]);
+          if (++r == p.splits) {
+            r = 0;
+            ++j;
+          }
+        }
+      }
+    }
+    if (threadIdx.x == 64) TG_STAMP(6);
+    __syncwarp();
+    sm_cluster_arrive();  // release: this CTA's pushes are done
+    sm_cluster_wait();    // acquire: every peer's pushes into this CTA's inbox are visible
+    if (threadIdx.x == 64) TG_STAMP(7);
+    if (n_ok) {
+      const int rank = static_cast<int>(sm_cluster_ctarank());
+      for (int j = 0; j * p.splits + rank < mv; ++j) {
+        const float* src = inbox + j * kBM + n_local;
+        float sum = src[0];
+        for (int s2 = 1; s2 < p.splits; ++s2) sum += src[s2 * rpr * kBM];  // split order: bit-stable
+        smallm_store(p, j * p.splits + rank, n, fmaf(sum, scale, bias));
+      }
+    }
+    if (threadIdx.x == 64) TG_STAMP(8);
+    // no peer touches this CTA's shared memory after the barrier above: it may exit on its own
+  } else {
+    if (have_acc) {
+      float* part = p.ws_partial + static_cast<int64_t>(u) * (MP * kBM) + n_local;
+#pragma unroll
+      for (int m = 0; m < MP; ++m)
+        if (m < mv) part[m * kBM] = acc[m];
+      if (splitk_arrive_is_last(p.ws_counters + tn * 4 + q, p.splits)) {
+        const float* tile_part = p.ws_partial + static_cast<int64_t>(tn) * p.splits * (MP * kBM) + n_local;
+#pragma unroll
+        for (int m = 0; m < MP; ++m) acc[m] = 0.f;
+#pragma unroll 1
+        for (int s2 = 0; s2 < p.splits; ++s2) {  // fixed order: bit-stable result
+          const float* src = tile_part + static_cast<int64_t>(s2) * (MP * kBM);
+#pragma unroll
+          for (int m = 0; m < MP; ++m)  // MP independent loads in flight
+            if (m < mv) acc[m] += __ldcg(src + m * kBM);
+        }
         if (n_ok) {
 #pragma unroll
           for (int m = 0; m < MP; ++m)
             if (m < mv) smallm_store(p, m, n, fmaf(acc[m], scale, bias));
-        }
-      } else {
-        float* part = p.ws_partial + static_cast<int64_t>(u) * (MP * kBM) + n_local;
-#pragma unroll
-        for (int m = 0; m < MP; ++m)
-          if (m < mv) part[m * kBM] = acc[m];
-        if (splitk_arrive_is_last(p.ws_counters + tn * 4 + q, p.splits)) {
-          const float* tile_part = p.ws_partial + static_cast<int64_t>(tn) * p.splits * (MP * kBM) + n_local;
-#pragma unroll
-          for (int m = 0; m < MP; ++m) acc[m] = 0.f;
-#pragma unroll 1
-          for (int s2 = 0; s2 < p.splits; ++s2) {  // fixed order: bit-stable result
-            const float* src = tile_part + static_cast<int64_t>(s2) * (MP * kBM);
-#pragma unroll
-            for (int m = 0; m < MP; ++m)  // MP independent loads in flight
-              if (m < mv) acc[m] += __ldcg(src + m * kBM);
-          }
-          if (n_ok) {
-#pragma unroll
-            for (int m = 0; m < MP; ++m)
-              if (m < mv) smallm_store(p, m, n, fmaf(acc[m], scale, bias));
-          }
         }
       }
     }
@@ -217,29 +334,73 @@ __global__ void __launch_bounds__(kThreads, 2)
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
+  if (threadIdx.x == 0) TG_STAMP(9);
 }
 
-template <int MP>
-cudaError_t launch_mp(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, cudaStream_t stream) {
-  using Cfg = SmCfg<MP>;
+template <int MP, bool CLUSTER>
+cudaError_t configure_once() {
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(tg_fp8_gemm_smallm_kernel<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(tg_fp8_gemm_smallm_kernel<MP, CLUSTER>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SmCfg<MP>::kSmemBytes);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
+  return cudaSuccess;
+}
+
+template <int MP>
+cudaError_t launch_mp_cluster(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p,
+                              cudaStream_t stream) {
+  cudaError_t e = configure_once<MP, true>();
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(p.tiles_n * p.splits), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = SmCfg<MP>::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(p.splits);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, tg_fp8_gemm_smallm_kernel<MP, true>, tmW, tmX, p);
+}
+
+template <int MP>
+cudaError_t launch_mp(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, cudaStream_t stream) {
+  cudaError_t e = configure_once<MP, false>();
+  if (e != cudaSuccess) return e;
   const int grid = p.tiles_n * p.splits;
-  tg_fp8_gemm_smallm_kernel<MP><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tmW, tmX, p);
+  tg_fp8_gemm_smallm_kernel<MP, false><<<grid, kThreads, SmCfg<MP>::kSmemBytes, stream>>>(tmW, tmX, p);
   return cudaGetLastError();
 }
 
 }  // namespace
 
+cudaError_t launch_gemm_smallm_cluster(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int mp,
+                                       cudaStream_t stream) {
+  if (p.splits < 1 || p.splits > 8) return cudaErrorInvalidValue;  // portable cluster size
+  if (p.tile_rows < 16 || p.tile_rows > 128) return cudaErrorInvalidValue;
+  switch (mp) {
+    case 16:
+      return launch_mp_cluster<16>(tmW, tmX, p, stream);
+    case 32:
+      return launch_mp_cluster<32>(tmW, tmX, p, stream);
+    case 64:
+      return launch_mp_cluster<64>(tmW, tmX, p, stream);
+    default:
+      return cudaErrorInvalidValue;
+  }
+}
+
 cudaError_t launch_gemm_smallm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int mp,
                                cudaStream_t stream) {
+  if (p.tile_rows < 16 || p.tile_rows > 128) return cudaErrorInvalidValue;
   switch (mp) {
     case 16:
       return launch_mp<16>(tmW, tmX, p, stream);

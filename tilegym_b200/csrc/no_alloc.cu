@@ -122,6 +122,7 @@ extern "C" TG_API int32_t tg_fp8_gemm_pertensor_smallm_static(const TgTensorDesc
   p.K = static_cast<int32_t>(K);
   p.num_kb = static_cast<int32_t>((K + 127) / 128);
   p.tiles_m = 1;
+  p.tile_rows = 128;
   p.tiles_n = static_cast<int32_t>((N + 127) / 128);
   p.C = reinterpret_cast<void*>(C->ptr);
   p.ldc = C->strides[0];

@@ -17,6 +17,7 @@ struct GemmParams {
   int32_t M, N, K;
   int32_t num_kb;            // ceil(K / 128)
   int32_t tiles_m, tiles_n;  // output tiles
+  int32_t tile_rows;         // small-M kernel: weight rows per tile (<= 128)
   // output
   void* C;
   int64_t ldc;        // elements
@@ -51,6 +52,11 @@ cudaError_t launch_gemm_blockscaled(const CUtensorMap& tmA, const CUtensorMap& t
 // Swap-AB split-K kernel for M <= 64: tmW boxes 128 weight rows, tmX boxes `mp` activation rows.
 cudaError_t launch_gemm_smallm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int mp,
                                cudaStream_t stream);
+
+// Same kernel with the K splits of a tile launched as one thread-block cluster (1 <= splits <= 8) and the
+// partial sums reduced through distributed shared memory: needs no workspace.
+cudaError_t launch_gemm_smallm_cluster(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int mp,
+                                       cudaStream_t stream);
 
 // Helpers of the main entry-point file, for entry points defined elsewhere.
 int32_t api_fail(int32_t rc, const char* msg);
