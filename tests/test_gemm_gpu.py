@@ -20,7 +20,7 @@ import tilegym_b200 as tg  # noqa: E402
 from tilegym_b200 import _lib  # noqa: E402
 
 KNOBS = ("TILEGYM_B200_BN", "TILEGYM_B200_SPLITS", "TILEGYM_B200_FORCE_PATH", "TILEGYM_B200_SMALLM_WS",
-         "TILEGYM_B200_2CTA", "TILEGYM_B200_GROUP_M")
+         "TILEGYM_B200_2CTA", "TILEGYM_B200_GROUP_M", "TILEGYM_B200_BS_PAIR", "TILEGYM_B200_TILE_ROWS")
 
 
 @pytest.fixture(autouse=True)
@@ -253,6 +253,24 @@ def test_block_scaled_reference_test_shapes(dev, shape):
     ref = R.ref_w8a8_block_fp8_matmul(A, B, As, Bs, [128, 128])
     out = tg.w8a8_block_fp8_matmul(A.to(dev), B.to(dev), As.to(dev), Bs.to(dev), [128, 128])
     torch.testing.assert_close(out.cpu(), ref, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("M,N,K", [(300, 520, 1040), (256, 256, 128), (1000, 1100, 400)])
+def test_block_scaled_cta_pair_kernel_tails_and_agreement(dev, M, N, K):
+    """Ragged M / N / K through the 256 x 256 CTA-pair kernel, against the oracle and the 128 x 128 kernel."""
+    g = torch.Generator().manual_seed(M + N + K)
+    A = (torch.randn(M, K, generator=g) * 0.1).to(torch.float8_e4m3fn)
+    B = (torch.randn(N, K, generator=g) * 0.1).to(torch.float8_e4m3fn)
+    As = torch.rand(M, -(-K // 128), generator=g) + 0.1
+    Bs = torch.rand(-(-N // 128), -(-K // 128), generator=g) + 0.1
+    ref = R.ref_w8a8_block_fp8_matmul(A, B, As, Bs, [128, 128])
+    args = [t.to(dev) for t in (A, B, As, Bs)]
+    os.environ["TILEGYM_B200_BS_PAIR"] = "1"  # the CTA-pair kernel is opt-in
+    pair = tg.w8a8_block_fp8_matmul(*args, [128, 128])
+    torch.testing.assert_close(pair.cpu(), ref, rtol=1e-4, atol=1e-4)
+    os.environ["TILEGYM_B200_BS_PAIR"] = "0"
+    single = tg.w8a8_block_fp8_matmul(*args, [128, 128])
+    torch.testing.assert_close(single, pair, rtol=1e-5, atol=1e-5)  # the 128 x 128 kernel may split K here
 
 
 def test_block_scaled_split_k_and_leading_dims(dev):

@@ -408,7 +408,7 @@ int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, co
   const bool have_ws = workspace != 0 && workspace_bytes >= kWsCounterBytes + kWsPartialBytes;
   const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
   if (tiles > 0x3fffffff) return fail(TG_ERR_ARGS, "problem has too many tiles");
-  if (have_ws && tiles * 8 <= static_cast<int64_t>(kWsCounterBytes / 4))
+  if (have_ws && tiles * 16 <= static_cast<int64_t>(kWsCounterBytes / 4))
     choose_splits(static_cast<int>(tiles), p.num_kb, st.num_sms, 128ll * 128, st.num_sms, 4, &p.splits, &p.kb_per_split);
   else {
     p.splits = 1;
@@ -417,6 +417,25 @@ int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, co
   CUtensorMap tmA, tmB;
   if ((rc = make_map(&tmA, A->ptr, M, K, A->strides[0], 128)) != TG_OK) return rc;
   if ((rc = make_map(&tmB, B->ptr, N, K, B->strides[0], 128)) != TG_OK) return rc;
+  // Experimental, opt-in (TILEGYM_B200_BS_PAIR=1): CTA-pair kernel (256 x 192 tiles, each CTA loads 96 rows
+  // of B).  It halves the L2 traffic per flop but its two-buffer promotion chain currently runs slower than
+  // the 128 x 128 kernel with four TMEM buffers, which stays the default.
+  if (M >= 256 && N >= 256 && env_int("TILEGYM_B200_BS_PAIR", 0) != 0 && getenv("TILEGYM_B200_SPLITS") == nullptr) {
+    if ((rc = make_map(&tmB, B->ptr, N, K, B->strides[0], 96)) != TG_OK) return rc;
+    p.tiles_m = static_cast<int32_t>((M + 255) / 256);
+    p.tiles_n = static_cast<int32_t>((N + 191) / 192);
+    p.splits = 1;
+    p.kb_per_split = p.num_kb;
+    int group_m = static_cast<int>((24ll << 20) / (256ll * K));
+    if (group_m < 2) group_m = 2;
+    if (group_m > p.tiles_m) group_m = p.tiles_m;
+    group_m = env_int("TILEGYM_B200_GROUP_M", group_m);
+    if (group_m < 1) group_m = 1;
+    cudaError_t e2 = launch_gemm_blockscaled_2cta(tmA, tmB, p, group_m, st.num_sms, cs);
+    if (e2 != cudaSuccess)
+      return fail(TG_ERR_LAUNCH, "block-scaled GEMM (CTA pair) launch failed: %s", cudaGetErrorString(e2));
+    return TG_OK;
+  }
   cudaError_t e = launch_gemm_blockscaled(tmA, tmB, p, st.num_sms, cs);
   if (e != cudaSuccess) return fail(TG_ERR_LAUNCH, "block-scaled GEMM launch failed: %s", cudaGetErrorString(e));
   return TG_OK;
