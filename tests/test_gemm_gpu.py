@@ -20,7 +20,7 @@ import tilegym_b200 as tg  # noqa: E402
 from tilegym_b200 import _lib  # noqa: E402
 
 KNOBS = ("TILEGYM_B200_BN", "TILEGYM_B200_SPLITS", "TILEGYM_B200_FORCE_PATH", "TILEGYM_B200_SMALLM_WS",
-         "TILEGYM_B200_2CTA", "TILEGYM_B200_GROUP_M", "TILEGYM_B200_BS_PAIR", "TILEGYM_B200_TILE_ROWS")
+         "TILEGYM_B200_2CTA", "TILEGYM_B200_GROUP_M", "TILEGYM_B200_BS_PAIR", "TILEGYM_B200_TILE_ROWS", "TILEGYM_B200_TAIL_DIV")
 
 
 @pytest.fixture(autouse=True)
@@ -113,6 +113,18 @@ def test_small_m_cluster_and_workspace_reductions_agree(dev, M, ws):
 def test_cta_pair_kernel_raster_groups(dev, group_m):
     os.environ["TILEGYM_B200_GROUP_M"] = group_m
     run_pt(dev, 1280, 1536, 512, seed=12, bias=True)
+
+
+@pytest.mark.parametrize("tail_div", ["1", "2", "4"])
+@pytest.mark.parametrize("M,N,K", [(512, 768, 1024), (1000, 1100, 400), (4096, 6144, 512)])
+def test_cta_pair_kernel_tail_slices(dev, tail_div, M, N, K):
+    """The tiles of the last wave are cut into 1, 2 or 4 column slices; the result does not change."""
+    os.environ["TILEGYM_B200_TAIL_DIV"] = tail_div
+    out = run_pt(dev, M, N, K, seed=14, bias=True)
+    os.environ["TILEGYM_B200_TAIL_DIV"] = "1"
+    a8, b8, sa, sb = (t.to(dev) for t in R.gen_per_tensor_case(M, N, K, 14))
+    bvec = torch.randn(N, generator=torch.Generator().manual_seed(21)).to(dev)
+    assert torch.equal(out, tg.fp8_scaled_mm(a8, b8, sa, sb, bvec))
 
 
 def test_cta_pair_and_single_cta_kernels_agree(dev):

@@ -329,7 +329,13 @@ int32_t tg_fp8_gemm_pertensor(const TgTensorDesc* C, const TgTensorDesc* A, cons
     if (group_m < 1) group_m = 1;
     if ((rc = make_map(&tmA, A->ptr, M, K, A->strides[0], 128)) != TG_OK) return rc;
     if ((rc = make_map(&tmB, B->ptr, N, K, B->strides[0], 128)) != TG_OK) return rc;
-    cudaError_t e2 = launch_gemm_pertensor_2cta(tmA, tmB, p, group_m, st.num_sms, cs);
+    // tiles of a partly filled last wave are cut into column slices (TILEGYM_B200_TAIL_DIV overrides: 1, 2, 4)
+    int tail_div = pertensor_2cta_tail_div(p.tiles_m * p.tiles_n, st.num_sms);
+    tail_div = env_int("TILEGYM_B200_TAIL_DIV", tail_div);
+    if (tail_div != 2 && tail_div != 4) tail_div = 1;
+    CUtensorMap tmBt;
+    if ((rc = make_map(&tmBt, B->ptr, N, K, B->strides[0], 128 / tail_div)) != TG_OK) return rc;
+    cudaError_t e2 = launch_gemm_pertensor_2cta(tmA, tmB, tmBt, p, group_m, tail_div, st.num_sms, cs);
     if (e2 != cudaSuccess) return fail(TG_ERR_LAUNCH, "GEMM (CTA pair) launch failed: %s", cudaGetErrorString(e2));
     return TG_OK;
   }

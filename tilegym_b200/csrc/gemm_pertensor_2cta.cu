@@ -95,9 +95,35 @@ __device__ __forceinline__ void pair_tile_coords(int t, int tiles_m, int tiles_n
   tn = r / gsize;
 }
 
+// Work list of one launch.  Units 0 .. full_tiles-1 are whole 256 x 256 tiles; the remaining tiles (those
+// that would form a mostly idle last wave) are cut into `tail_div` column slices of 256 / tail_div columns,
+// one unit each, so that the last wave spreads over more CTA pairs and finishes in a fraction of a tile time.
+struct PairPlan {
+  int group_m;
+  int full_tiles;
+  int tail_div;   // 1, 2 or 4
+  int num_units;  // full_tiles + (tiles - full_tiles) * tail_div
+};
+
+__device__ __forceinline__ void decode_unit(int u, const GemmParams& p, const PairPlan& plan, int& tm, int& tn,
+                                            int& col_off, int& bn) {
+  int t = u;
+  col_off = 0;
+  bn = kBN;
+  if (u >= plan.full_tiles) {
+    const int v = u - plan.full_tiles;
+    t = plan.full_tiles + v / plan.tail_div;
+    bn = kBN / plan.tail_div;
+    col_off = (v % plan.tail_div) * bn;
+  }
+  pair_tile_coords(t, p.tiles_m, p.tiles_n, plan.group_m, tm, tn);
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     tg_fp8_gemm_pertensor_2cta_kernel(const __grid_constant__ CUtensorMap tmA,
-                                      const __grid_constant__ CUtensorMap tmB, const GemmParams p, int group_m) {
+                                      const __grid_constant__ CUtensorMap tmB,
+                                      const __grid_constant__ CUtensorMap tmBt, const GemmParams p,
+                                      const PairPlan plan) {
   constexpr int S = kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -140,7 +166,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int num_tiles = p.tiles_m * p.tiles_n;  // pair tiles (256 x 256)
+  const int num_units = plan.num_units;
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
 
@@ -153,20 +179,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
-        int tm, tn;
-        pair_tile_coords(t, p.tiles_m, p.tiles_n, group_m, tm, tn);
+      for (int u = pair_id; u < num_units && ok; u += num_pairs) {
+        int tm, tn, col_off, bn;
+        decode_unit(u, p, plan, tm, tn, col_off, bn);
         const int a_row = tm * 256 + static_cast<int>(rank) * kBM;
-        const int b_row = tn * kBN + static_cast<int>(rank) * kBNHalf;
+        const int b_row = tn * kBN + col_off + static_cast<int>(rank) * (bn >> 1);
+        const CUtensorMap* mapB = (bn == kBN) ? &tmB : &tmBt;  // the slice map boxes bn / 2 rows
+        const uint32_t pair_tx = 2u * static_cast<uint32_t>(kABytes + (bn >> 1) * kBK);
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag)) {
             report_timeout(p.status, kRoleProducer * 1000 + 31);
             ok = false;
             break;
           }
-          if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, 2 * kStageBytes);  // both CTAs' bytes
+          if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, pair_tx);  // both CTAs' bytes
           tma_load_2d_pair(a_base + s * kABytes, &tmA, leader_full + 8 * s, kb * kBK, a_row);
-          tma_load_2d_pair(b_base + s * kBBytes, &tmB, leader_full + 8 * s, kb * kBK, b_row);
+          tma_load_2d_pair(b_base + s * kBBytes, mapB, leader_full + 8 * s, kb * kBK, b_row);
           if (++s == S) {
             s = 0;
             ph ^= 1u;
@@ -177,7 +205,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer (leader CTA only)
     if (lane == 0 && leader) {
-      constexpr uint32_t idesc = make_idesc_e4m3_f32(256, kBN);
       const uint32_t peer_empty = map_to_cta(bar_empty, 1);
       const uint32_t peer_tfull = map_to_cta(bar_tfull, 1);
       int s = 0;
@@ -185,7 +212,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       int buf = 0;
       uint32_t aph = 0;
       bool ok = true;
-      for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
+      for (int u = pair_id; u < num_units && ok; u += num_pairs) {
+        const int bn = (u < plan.full_tiles) ? kBN : kBN / plan.tail_div;
+        const uint32_t idesc = make_idesc_e4m3_f32(256, bn);
         if (!mbar_wait(bar_tempty + 8 * buf, aph ^ 1u, abort_flag)) {
           report_timeout(p.status, kRoleMma * 1000 + 31);
           break;
@@ -229,9 +258,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     const uint32_t leader_tempty = map_to_cta(bar_tempty, 0);
     int buf = 0;
     uint32_t aph = 0;
-    for (int t = pair_id; t < num_tiles; t += num_pairs) {
-      int tm, tn;
-      pair_tile_coords(t, p.tiles_m, p.tiles_n, group_m, tm, tn);
+    for (int u = pair_id; u < num_units; u += num_pairs) {
+      int tm, tn, col_off, bn;
+      decode_unit(u, p, plan, tm, tn, col_off, bn);
+      const int chunks = bn >> 5;
       bool w = mbar_wait(bar_tfull + 8 * buf, aph, abort_flag);
       w = __all_sync(0xffffffffu, w);
       if (!w) {
@@ -242,16 +272,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       const int64_t row = static_cast<int64_t>(tm) * 256 + static_cast<int>(rank) * kBM + q * 32 + lane;
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * kBN);
 #pragma unroll 1
-      for (int c = 0; c < kBN / 32; ++c) {
+      for (int c = 0; c < chunks; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(t_addr + c * 32, r);
         tmem_ld_wait();
-        if (c == kBN / 32 - 1) {
+        if (c == chunks - 1) {
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(leader_tempty + 8 * buf);
         }
-        if (row < p.M) epilogue_store32(p, row, tn * kBN + c * 32, reinterpret_cast<const float*>(r), scale, vec_ok);
+        if (row < p.M)
+          epilogue_store32(p, row, tn * kBN + col_off + c * 32, reinterpret_cast<const float*>(r), scale, vec_ok);
       }
       buf ^= 1;
       if (buf == 0) aph ^= 1u;
@@ -273,8 +304,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 
 }  // namespace
 
-cudaError_t launch_gemm_pertensor_2cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
-                                       int group_m, int num_sms, cudaStream_t stream) {
+// How many column slices the tiles of the last, partly filled wave are cut into (1 = not at all).
+int pertensor_2cta_tail_div(int tiles, int num_sms) {
+  const int pairs = num_sms / 2;
+  if (pairs < 1) return 1;
+  const int rem = tiles % pairs;
+  if (rem == 0) return 1;
+  if (rem * 4 <= pairs) return 4;
+  if (rem * 2 <= pairs) return 2;
+  return 1;
+}
+
+cudaError_t launch_gemm_pertensor_2cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmBt,
+                                       const GemmParams& p, int group_m, int tail_div, int num_sms,
+                                       cudaStream_t stream) {
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -286,8 +329,13 @@ cudaError_t launch_gemm_pertensor_2cta(const CUtensorMap& tmA, const CUtensorMap
   }
   const int tiles = p.tiles_m * p.tiles_n;
   int pairs = num_sms / 2;
-  if (tiles < pairs) pairs = tiles;
-  tg_fp8_gemm_pertensor_2cta_kernel<<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmA, tmB, p, group_m);
+  PairPlan plan;
+  plan.group_m = group_m;
+  plan.tail_div = (tail_div == 2 || tail_div == 4) ? tail_div : 1;
+  plan.full_tiles = (plan.tail_div == 1) ? tiles : tiles - tiles % pairs;
+  plan.num_units = plan.full_tiles + (tiles - plan.full_tiles) * plan.tail_div;
+  if (plan.num_units < pairs) pairs = plan.num_units;
+  tg_fp8_gemm_pertensor_2cta_kernel<<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmBt, p, plan);
   return cudaGetLastError();
 }
 

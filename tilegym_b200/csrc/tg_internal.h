@@ -45,8 +45,12 @@ struct GemmParams {
 cudaError_t launch_gemm_pertensor(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int bn,
                                   int num_sms, cudaStream_t stream);
 // CTA-pair (cta_group::2) kernel: 256 x 256 tiles; tmA and tmB both box 128 rows; p.tiles_* count 256-wide tiles.
-cudaError_t launch_gemm_pertensor_2cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
-                                       int group_m, int num_sms, cudaStream_t stream);
+// The tiles of the last, partly filled wave are cut into `tail_div` column slices (1, 2 or 4, from
+// pertensor_2cta_tail_div); tmBt boxes 128 / tail_div rows of B for them.
+int pertensor_2cta_tail_div(int tiles, int num_sms);
+cudaError_t launch_gemm_pertensor_2cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmBt,
+                                       const GemmParams& p, int group_m, int tail_div, int num_sms,
+                                       cudaStream_t stream);
 cudaError_t launch_gemm_blockscaled(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
                                     int num_sms, cudaStream_t stream);
 // CTA-pair block-scaled kernel: 256 x 192 tiles, tmA boxes 128 rows and tmB 96, p.tiles_n counts 192-wide tiles, no split-K.

@@ -53,28 +53,51 @@ def assemble(slabs: torch.Tensor) -> torch.Tensor:
 class ColumnParallelFP8Gemm:
     """C = (sa*A) . (sb*B)^T with B row-sharded over the ranks of `group`.
 
-    `out_slabs` ([G, M, N/G], bf16) is allocated once; `forward` launches the
-    local GEMM straight into this rank's slab, then all-gathers in place.
+    The M rows are processed in `chunks` slabs: the local GEMM of slab c writes straight into this
+    rank's part of `out` ([chunks, G, M/chunks, N/G]), and the all-gather of slab c runs on a second
+    stream while the GEMM of slab c+1 computes, so the NVLink transfer hides behind the tensor cores
+    as far as the bandwidth allows.  Logical element C[m, g*N/G + j] is out[m // mc, g, m % mc, j].
     """
 
     def __init__(self, B_shard: torch.Tensor, scale_b: torch.Tensor, M: int, group=None,
-                 bias_shard: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16):
+                 bias_shard: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
+                 chunks: int = 1):
         from . import ops  # the CUDA path; imported here so the index helpers above stay importable on CPU
 
+        if M % chunks != 0:
+            raise ValueError(f"M={M} is not divisible into {chunks} chunks")
         self._ops = ops
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.B, self.scale_b, self.bias = B_shard, scale_b, bias_shard
+        self.chunks, self.mc = chunks, M // chunks
         n = B_shard.shape[0]
-        self.out_slabs = torch.empty(self.world, M, n, dtype=out_dtype, device=B_shard.device)
+        self.out = torch.empty(chunks, self.world, self.mc, n, dtype=out_dtype, device=B_shard.device)
+        self.out_slabs = self.out[0] if chunks == 1 else None  # [G, M, N/G] when not chunked
+        self._comm_stream = torch.cuda.Stream(device=B_shard.device) if self.world > 1 else None
+        self._events = [torch.cuda.Event() for _ in range(chunks)]
 
     def forward(self, A: torch.Tensor, scale_a: torch.Tensor, gather: bool = True) -> torch.Tensor:
-        mine = self.out_slabs[self.rank]
-        self._ops.fp8_scaled_mm(A, self.B, scale_a, self.scale_b, self.bias, mine.dtype, out=mine)
-        if gather and self.world > 1:
-            dist.all_gather_into_tensor(self.out_slabs.view(-1), mine.view(-1), group=self.group)
-        return self.out_slabs
+        main = torch.cuda.current_stream(A.device)
+        do_gather = gather and self.world > 1
+        for c in range(self.chunks):
+            mine = self.out[c, self.rank]
+            a_c = A[c * self.mc:(c + 1) * self.mc]
+            self._ops.fp8_scaled_mm(a_c, self.B, scale_a, self.scale_b, self.bias, mine.dtype, out=mine)
+            if do_gather:
+                self._events[c].record(main)
+                with torch.cuda.stream(self._comm_stream):
+                    self._comm_stream.wait_event(self._events[c])
+                    dist.all_gather_into_tensor(self.out[c].view(-1), mine.view(-1), group=self.group)
+        if do_gather:
+            main.wait_stream(self._comm_stream)
+        return self.out
+
+    def logical(self) -> torch.Tensor:
+        """[chunks, M/chunks, G, N/G] strided view of the gathered result (no copy):
+        view[c, i, g, j] = C[c * M/chunks + i, g * N/G + j]."""
+        return self.out.permute(0, 2, 1, 3)
 
 
 def reference_gather(shards: List[torch.Tensor]) -> torch.Tensor:
