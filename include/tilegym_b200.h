@@ -97,6 +97,22 @@ TG_API int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc
                                 int32_t block_k, uint64_t workspace, uint64_t workspace_bytes,
                                 int32_t device_id, uint64_t stream);
 
+/* Column-parallel GEMM fused with the all-gather of its output (multi-GPU, one
+ * process per GPU).  This rank computes its slab C[M, n] = alpha*sa*sb*(A . B_shard^T)
+ * + bias and the kernel's epilogue stores every finished tile into C AND into the
+ * same slab of each peer GPU's output buffer over NVLink (plain, non-multicast bulk
+ * tensor stores to peer-mapped memory), so no separate collective pass runs.
+ * C: [M, n] bf16 / f16 view (row stride = full output width) of this rank's slab in
+ * its own buffer; peer_ptrs[i]: address of the same [M, n] view inside peer i's
+ * buffer (peer-mapped, e.g. CUDA IPC or a symmetric-memory allocation), num_peers
+ * <= 7.  Needs M, n >= 256 and 16-byte aligned rows.  The caller orders the ranks
+ * (a barrier after the call) before any rank reads the gathered result.
+ * The reference is single-GPU; there is no counterpart. */
+TG_API int32_t tg_fp8_gemm_pertensor_allgather(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
+                                               uint64_t scale_a, uint64_t scale_b, float alpha,
+                                               const TgTensorDesc* bias, const uint64_t* peer_ptrs,
+                                               int32_t num_peers, int32_t device_id, uint64_t stream);
+
 /* The small-M (M <= 64) path of tg_fp8_gemm_pertensor for callers that cannot
  * allocate device memory - a server whose pool already owns the GPU, or a
  * decode loop that must never reach cudaMalloc / cudaFree because they

@@ -107,6 +107,21 @@ int32_t make_map(CUtensorMap* map, uint64_t ptr, int64_t rows, int64_t K, int64_
   return TG_OK;
 }
 
+// 2-D map over a row-major bf16 / f16 output [rows, cols] with row pitch `pitch_bytes`, for bulk tensor
+// stores of 64-column x 32-row boxes out of 128-byte-swizzled shared memory; stores past the extents are clipped.
+int32_t make_out_map(CUtensorMap* map, uint64_t ptr, int64_t rows, int64_t cols, int64_t pitch_bytes, int32_t dtype) {
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_bytes)};
+  cuuint32_t box[2] = {64u, 32u};
+  cuuint32_t estr[2] = {1u, 1u};
+  const CUtensorMapDataType dt = dtype == TG_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = g_encode(map, dt, 2, reinterpret_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(TG_ERR_ARGS, "cuTensorMapEncodeTiled (output) failed with CUresult %d", static_cast<int>(r));
+  return TG_OK;
+}
+
 bool is_out_dtype(int32_t d) { return d == TG_F32 || d == TG_F16 || d == TG_BF16; }
 int esize(int32_t d) { return d == TG_F32 ? 4 : (d == TG_F16 || d == TG_BF16) ? 2 : 1; }
 
@@ -236,9 +251,12 @@ const char* tg_last_error_string(void) { return g_err; }
 
 uint64_t tg_fp8_gemm_workspace_bytes(int64_t, int64_t, int64_t) { return kWsCounterBytes + kWsPartialBytes; }
 
-int32_t tg_fp8_gemm_pertensor(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B, uint64_t scale_a,
+// Shared body of tg_fp8_gemm_pertensor (num_peers == 0) and tg_fp8_gemm_pertensor_allgather (the result
+// slab is also stored to peer_ptrs[0 .. num_peers), addresses of the same [M, N] view in peer GPUs' buffers).
+static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B, uint64_t scale_a,
                               uint64_t scale_b, float alpha, const TgTensorDesc* bias, float beta, uint64_t workspace,
-                              uint64_t workspace_bytes, int32_t device_id, uint64_t stream) {
+                              uint64_t workspace_bytes, const uint64_t* peer_ptrs, int32_t num_peers,
+                              int32_t device_id, uint64_t stream) {
   int32_t rc;
   if ((rc = check_operand(A, "A")) != TG_OK) return rc;
   if ((rc = check_operand(B, "B")) != TG_OK) return rc;
@@ -289,6 +307,15 @@ int32_t tg_fp8_gemm_pertensor(const TgTensorDesc* C, const TgTensorDesc* A, cons
   if (force && !strcmp(force, "gemm")) small = false;
   if (force && !strcmp(force, "smallm") && M <= 64) small = true;
 
+  // The output leaves through bulk tensor stores when it is two bytes wide, not accumulated into, and its
+  // rows are 16-byte aligned; the fused all-gather needs that path.
+  const bool tma_out_ok = (C->dtype == TG_BF16 || C->dtype == TG_F16) && beta == 0.0f && (C->ptr & 15u) == 0 &&
+                          ((C->strides[0] * 2) & 15) == 0;
+  const bool pair_kernel = M >= 256 && N >= 256 && env_int("TILEGYM_B200_2CTA", 1) != 0 &&
+                           getenv("TILEGYM_B200_BN") == nullptr && getenv("TILEGYM_B200_SPLITS") == nullptr;
+  if (num_peers > 0 && !(pair_kernel && tma_out_ok))
+    return fail(TG_ERR_ARGS, "the fused all-gather needs M, N >= 256, a bf16 / f16 output with 16-byte aligned rows and beta == 0");
+
   CUtensorMap tmA, tmB;
   if (small) {
     const int mp = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
@@ -315,8 +342,7 @@ int32_t tg_fp8_gemm_pertensor(const TgTensorDesc* C, const TgTensorDesc* A, cons
   }
 
   // Large problems: CTA-pair kernel (256 x 256 tiles, half the L2 traffic per SM).
-  if (M >= 256 && N >= 256 && env_int("TILEGYM_B200_2CTA", 1) != 0 && getenv("TILEGYM_B200_BN") == nullptr &&
-      getenv("TILEGYM_B200_SPLITS") == nullptr) {
+  if (pair_kernel) {
     p.tiles_m = static_cast<int32_t>((M + 255) / 256);
     p.tiles_n = static_cast<int32_t>((N + 255) / 256);
     p.splits = 1;
@@ -335,7 +361,14 @@ int32_t tg_fp8_gemm_pertensor(const TgTensorDesc* C, const TgTensorDesc* A, cons
     if (tail_div != 2 && tail_div != 4) tail_div = 1;
     CUtensorMap tmBt;
     if ((rc = make_map(&tmBt, B->ptr, N, K, B->strides[0], 128 / tail_div)) != TG_OK) return rc;
-    cudaError_t e2 = launch_gemm_pertensor_2cta(tmA, tmB, tmBt, p, group_m, tail_div, st.num_sms, cs);
+    CUtensorMap out_maps[8];
+    int num_out = 0;
+    if (tma_out_ok && (num_peers > 0 || env_int("TILEGYM_B200_TMA_STORE", 1) != 0)) {
+      if ((rc = make_out_map(&out_maps[num_out++], C->ptr, M, N, C->strides[0] * 2, C->dtype)) != TG_OK) return rc;
+      for (int i = 0; i < num_peers; ++i)
+        if ((rc = make_out_map(&out_maps[num_out++], peer_ptrs[i], M, N, C->strides[0] * 2, C->dtype)) != TG_OK) return rc;
+    }
+    cudaError_t e2 = launch_gemm_pertensor_2cta(tmA, tmB, tmBt, out_maps, num_out, p, group_m, tail_div, st.num_sms, cs);
     if (e2 != cudaSuccess) return fail(TG_ERR_LAUNCH, "GEMM (CTA pair) launch failed: %s", cudaGetErrorString(e2));
     return TG_OK;
   }
@@ -358,6 +391,26 @@ int32_t tg_fp8_gemm_pertensor(const TgTensorDesc* C, const TgTensorDesc* A, cons
   cudaError_t e = launch_gemm_pertensor(tmA, tmB, p, bn, st.num_sms, cs);
   if (e != cudaSuccess) return fail(TG_ERR_LAUNCH, "GEMM launch failed: %s", cudaGetErrorString(e));
   return TG_OK;
+}
+
+int32_t tg_fp8_gemm_pertensor(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B, uint64_t scale_a,
+                              uint64_t scale_b, float alpha, const TgTensorDesc* bias, float beta, uint64_t workspace,
+                              uint64_t workspace_bytes, int32_t device_id, uint64_t stream) {
+  return pertensor_impl(C, A, B, scale_a, scale_b, alpha, bias, beta, workspace, workspace_bytes, nullptr, 0,
+                        device_id, stream);
+}
+
+int32_t tg_fp8_gemm_pertensor_allgather(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
+                                        uint64_t scale_a, uint64_t scale_b, float alpha, const TgTensorDesc* bias,
+                                        const uint64_t* peer_ptrs, int32_t num_peers, int32_t device_id,
+                                        uint64_t stream) {
+  if (num_peers < 0 || num_peers > 7) return fail(TG_ERR_ARGS, "num_peers must be 0..7, got %d", num_peers);
+  if (num_peers > 0 && peer_ptrs == nullptr) return fail(TG_ERR_NULL, "peer_ptrs is null");
+  for (int i = 0; i < num_peers; ++i) {
+    if (peer_ptrs[i] == 0) return fail(TG_ERR_NULL, "peer pointer %d is null", i);
+    if (peer_ptrs[i] & 15u) return fail(TG_ERR_ALIGN, "peer pointer %d is not 16-byte aligned", i);
+  }
+  return pertensor_impl(C, A, B, scale_a, scale_b, alpha, bias, 0.0f, 0, 0, peer_ptrs, num_peers, device_id, stream);
 }
 
 int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,

@@ -11,6 +11,8 @@
 // Roles per CTA: warp 0 TMA producer, warp 1 MMA issuer (leader only) and TMEM
 // owner, warps 2..5 epilogue.  Two TMEM accumulator buffers overlap the
 // epilogue of tile i with the main loop of tile i+1.
+#include <cstring>
+
 #include "tg_gemm_common.cuh"
 
 namespace tg {
@@ -26,7 +28,12 @@ constexpr int kBBytes = kBNHalf * kBK;  // 16 KB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTmemCols = 2 * kBN;    // 512: two accumulator buffers
 constexpr int kCtrlBytes = 256;
-constexpr int kSmemBytes = kStages * kStageBytes + kCtrlBytes + 1024;
+// Output staging for the TMA-store epilogue: per epilogue warp two buffers of 32 rows x 128 bytes
+// (64 two-byte outputs per row, 128-byte swizzled).
+constexpr int kOutBufBytes = 32 * 128;
+constexpr int kOutStageBytes = 4 * 2 * kOutBufBytes;  // 32 KB
+constexpr int kSmemBytes = kStages * kStageBytes + kOutStageBytes + kCtrlBytes + 1024;
+static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 static_assert((2 * kStages + 4) * 8 + 8 <= kCtrlBytes, "control block");
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -95,6 +102,12 @@ __device__ __forceinline__ void pair_tile_coords(int t, int tiles_m, int tiles_n
   tn = r / gsize;
 }
 
+// Tensor maps of the output: entry 0 is this GPU's C; further entries are the same slab inside peer GPUs'
+// buffers (fused all-gather).  Plain (non-multicast) TMA stores are issued once per destination.
+struct OutMaps {
+  CUtensorMap m[8];
+};
+
 // Work list of one launch.  Units 0 .. full_tiles-1 are whole 256 x 256 tiles; the remaining tiles (those
 // that would form a mostly idle last wave) are cut into `tail_div` column slices of 256 / tail_div columns,
 // one unit each, so that the last wave spreads over more CTA pairs and finishes in a fraction of a tile time.
@@ -122,8 +135,9 @@ __device__ __forceinline__ void decode_unit(int u, const GemmParams& p, const Pa
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     tg_fp8_gemm_pertensor_2cta_kernel(const __grid_constant__ CUtensorMap tmA,
                                       const __grid_constant__ CUtensorMap tmB,
-                                      const __grid_constant__ CUtensorMap tmBt, const GemmParams p,
-                                      const PairPlan plan) {
+                                      const __grid_constant__ CUtensorMap tmBt,
+                                      const __grid_constant__ OutMaps omaps, const int num_out,
+                                      const GemmParams p, const PairPlan plan) {
   constexpr int S = kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -131,7 +145,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   uint8_t* smem = smem_raw + (base - raw);
   const uint32_t a_base = base;
   const uint32_t b_base = base + S * kABytes;
-  uint8_t* ctrl = smem + S * kStageBytes;
+  uint8_t* out_stage = smem + S * kStageBytes;
+  uint8_t* ctrl = out_stage + kOutStageBytes;
   const uint32_t bar_full = smem_u32(ctrl);      // S barriers; only the leader's are used
   const uint32_t bar_empty = bar_full + 8 * S;   // S barriers, one set per CTA
   const uint32_t bar_tfull = bar_empty + 8 * S;  // 2 barriers, one set per CTA
@@ -256,6 +271,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     if (p.scale_b != nullptr) scale *= __ldg(p.scale_b);
     const bool vec_ok = c_rows_aligned(p);
     const uint32_t leader_tempty = map_to_cta(bar_tempty, 0);
+    uint8_t* my_stage = out_stage + (warp - 2) * (2 * kOutBufBytes);
+    int sb = 0;
     int buf = 0;
     uint32_t aph = 0;
     for (int u = pair_id; u < num_units; u += num_pairs) {
@@ -271,6 +288,64 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       tc_fence_after();
       const int64_t row = static_cast<int64_t>(tm) * 256 + static_cast<int>(rank) * kBM + q * 32 + lane;
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * kBN);
+      if (num_out > 0) {
+        // TMA-store epilogue (two-byte outputs, beta == 0): 64 columns at a time go through a swizzled
+        // shared-memory buffer and leave as one bulk tensor store per destination; rows and columns past
+        // M / N are clipped by the tensor map.
+        const int row0 = tm * 256 + static_cast<int>(rank) * kBM + q * 32;
+#pragma unroll 1
+        for (int c = 0; c < (bn >> 6); ++c) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(t_addr + c * 64, r0);
+          tmem_ld_32x32(t_addr + c * 64 + 32, r1);
+          tmem_ld_wait();
+          if (c == (bn >> 6) - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_tempty + 8 * buf);
+          }
+          if (lane == 0) tma_store_wait_read<1>();  // the store that last read this buffer has drained it
+          __syncwarp();
+          const int col = tn * kBN + col_off + c * 64;
+          uint8_t* dst_row = my_stage + sb * kOutBufBytes + lane * 128;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              v[j] = __uint_as_float(g < 4 ? r0[8 * g + j] : r1[8 * (g - 4) + j]) * scale;
+            if (p.bias != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (col + 8 * g + j < p.N) v[j] += load_bias(p.bias, p.bias_dtype, col + 8 * g + j);
+            }
+            uint4 o;
+            if (p.out_dtype == TG_BF16) {
+              o.x = pack_bf16x2(v[0], v[1]);
+              o.y = pack_bf16x2(v[2], v[3]);
+              o.z = pack_bf16x2(v[4], v[5]);
+              o.w = pack_bf16x2(v[6], v[7]);
+            } else {
+              o.x = pack_f16x2(v[0], v[1]);
+              o.y = pack_f16x2(v[2], v[3]);
+              o.z = pack_f16x2(v[4], v[5]);
+              o.w = pack_f16x2(v[6], v[7]);
+            }
+            *reinterpret_cast<uint4*>(dst_row + ((g ^ (lane & 7)) << 4)) = o;  // 128-byte swizzle
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const uint32_t src = smem_u32(my_stage + sb * kOutBufBytes);
+            for (int d = 0; d < num_out; ++d) tma_store_2d(&omaps.m[d], src, col, row0);
+            tma_store_commit();
+          }
+          sb ^= 1;
+        }
+        buf ^= 1;
+        if (buf == 0) aph ^= 1u;
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < chunks; ++c) {
         uint32_t r[32];
@@ -287,6 +362,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       buf ^= 1;
       if (buf == 0) aph ^= 1u;
     }
+    if (num_out > 0 && lane == 0) tma_store_wait_all<0>();  // all bulk stores of this warp have completed
   }
 
   // ---------------------------------------------------------------- teardown
@@ -316,8 +392,12 @@ int pertensor_2cta_tail_div(int tiles, int num_sms) {
 }
 
 cudaError_t launch_gemm_pertensor_2cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmBt,
-                                       const GemmParams& p, int group_m, int tail_div, int num_sms,
-                                       cudaStream_t stream) {
+                                       const CUtensorMap* out_maps, int num_out, const GemmParams& p, int group_m,
+                                       int tail_div, int num_sms, cudaStream_t stream) {
+  if (num_out < 0 || num_out > 8) return cudaErrorInvalidValue;
+  OutMaps omaps;
+  memset(&omaps, 0, sizeof(omaps));
+  for (int i = 0; i < num_out; ++i) omaps.m[i] = out_maps[i];
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -335,7 +415,8 @@ cudaError_t launch_gemm_pertensor_2cta(const CUtensorMap& tmA, const CUtensorMap
   plan.full_tiles = (plan.tail_div == 1) ? tiles : tiles - tiles % pairs;
   plan.num_units = plan.full_tiles + (tiles - plan.full_tiles) * plan.tail_div;
   if (plan.num_units < pairs) pairs = plan.num_units;
-  tg_fp8_gemm_pertensor_2cta_kernel<<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmBt, p, plan);
+  tg_fp8_gemm_pertensor_2cta_kernel<<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmBt, omaps, num_out, p,
+                                                                                  plan);
   return cudaGetLastError();
 }
 

@@ -48,9 +48,12 @@ cudaError_t launch_gemm_pertensor(const CUtensorMap& tmA, const CUtensorMap& tmB
 // The tiles of the last, partly filled wave are cut into `tail_div` column slices (1, 2 or 4, from
 // pertensor_2cta_tail_div); tmBt boxes 128 / tail_div rows of B for them.
 int pertensor_2cta_tail_div(int tiles, int num_sms);
+// out_maps[0 .. num_out): tensor maps (two-byte elements, box 64 x 32, 128-byte swizzle) of the output slab
+// in this GPU's buffer and, for the fused all-gather, in the peers' buffers; num_out == 0 selects the
+// register -> global store epilogue (needed for fp32 output, beta != 0 or unaligned rows).
 cudaError_t launch_gemm_pertensor_2cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmBt,
-                                       const GemmParams& p, int group_m, int tail_div, int num_sms,
-                                       cudaStream_t stream);
+                                       const CUtensorMap* out_maps, int num_out, const GemmParams& p, int group_m,
+                                       int tail_div, int num_sms, cudaStream_t stream);
 cudaError_t launch_gemm_blockscaled(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
                                     int num_sms, cudaStream_t stream);
 // CTA-pair block-scaled kernel: 256 x 192 tiles, tmA boxes 128 rows and tmB 96, p.tiles_n counts 192-wide tiles, no split-K.

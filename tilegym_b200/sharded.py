@@ -100,6 +100,57 @@ class ColumnParallelFP8Gemm:
         return self.out.permute(0, 2, 1, 3)
 
 
+class FusedColumnParallelFP8Gemm:
+    """Column-parallel GEMM whose kernel also performs the all-gather.
+
+    Every rank owns a full [M, N] output in symmetric (peer-mapped) memory.  The GEMM epilogue of rank g
+    stores each finished tile of its slab C[:, g*n:(g+1)*n] into its own buffer and, through bulk tensor
+    stores to peer memory over NVLink, into the same columns of every other rank's buffer; the transfer
+    runs tile by tile behind the tensor cores, and the result lands directly in row-major [M, N] (the NCCL
+    path produces slab-major [G, M, N/G]).  `forward` ends with a symmetric-memory barrier, after which
+    every rank may read the whole output.
+    """
+
+    def __init__(self, B_shard: torch.Tensor, scale_b: torch.Tensor, M: int, group=None,
+                 bias_shard: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _lib, ops
+
+        self._lib, self._ops, self._ctypes = _lib, ops, ctypes
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.B, self.scale_b, self.bias = B_shard, scale_b, bias_shard
+        self.n = B_shard.shape[0]
+        self.M, self.N = M, self.n * self.world
+        dev = B_shard.device
+        self.out = symm_mem.empty((M, self.N), dtype=out_dtype, device=dev)
+        self.handle = symm_mem.rendezvous(self.out, group=self.group)
+        esz = self.out.element_size()
+        col_off = self.rank * self.n * esz
+        peers = [int(ptr) + col_off for r, ptr in enumerate(self.handle.buffer_ptrs) if r != self.rank]
+        self._peer_arr = (ctypes.c_uint64 * max(1, len(peers)))(*peers)
+        self._num_peers = len(peers)
+        self.mine = self.out[:, self.rank * self.n:(self.rank + 1) * self.n]  # [M, n] view, row stride N
+
+    def forward(self, A: torch.Tensor, scale_a: torch.Tensor, sync: bool = True) -> torch.Tensor:
+        _lib = self._lib
+        dev = A.device
+        if sync:
+            self.handle.barrier()  # nobody is still reading the previous result while peers overwrite it
+        rc = _lib.lib().tg_fp8_gemm_pertensor_allgather(
+            _lib.ref(_lib.desc(self.mine)), _lib.ref(_lib.desc(A)), _lib.ref(_lib.desc(self.B)),
+            scale_a.data_ptr(), self.scale_b.data_ptr(), 1.0, _lib.ref(_lib.desc(self.bias)), self._peer_arr,
+            self._num_peers, dev.index, torch.cuda.current_stream(dev).cuda_stream,
+        )
+        _lib.check_rc(rc)
+        if sync:
+            self.handle.barrier()  # every rank's stores into this buffer have completed
+        return self.out
+
+
 def reference_gather(shards: List[torch.Tensor]) -> torch.Tensor:
     """What the sharded path must equal: the column-wise concatenation."""
     return torch.cat(shards, dim=-1)
