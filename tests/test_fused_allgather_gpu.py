@@ -1,0 +1,56 @@
+"""The fused GEMM + all-gather kernel on two GPUs (skipped on a single-GPU box): every rank's [M, N] buffer
+must equal the 1-GPU oracle result after one call, and agree bit for bit with the NCCL all-gather path."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, path):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dev = torch.device(f"cuda:{rank}")
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from oracle import torch_ref as R
+    from tilegym_b200 import _lib, sharded
+
+    M, N, K = 512, 512 * world, 1024
+    a8, b8, sa, sb = R.gen_per_tensor_case(M, N, K, 9)
+    ref = R.ref_fp8_scaled_mm(a8, b8, sa, sb)
+    shard = sharded.shard_weight(b8.view(torch.uint8), world, rank).view(torch.float8_e4m3fn).to(dev)
+    fused = sharded.FusedColumnParallelFP8Gemm(shard, sb.to(dev), M)
+    out = fused.forward(a8.to(dev), sa.to(dev))
+    torch.cuda.synchronize(dev)
+    ok_oracle = R.check_tolerance(out, ref)["ok"]
+    nccl = sharded.ColumnParallelFP8Gemm(shard, sb.to(dev), M, chunks=2)
+    slabs = nccl.forward(a8.to(dev), sa.to(dev))  # [chunks, G, M/chunks, n]
+    via_nccl = slabs.permute(0, 2, 1, 3).reshape(M, N)
+    same = bool(torch.equal(via_nccl, out))
+    _lib.device_status(rank)
+    flags = torch.tensor([int(ok_oracle), int(same)], device=dev)
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        torch.save({"oracle": int(flags[0]), "same_as_nccl": int(flags[1])}, path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_fused_allgather_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    path = str(tmp_path / "res.pt")
+    mp.spawn(_worker, args=(2, _free_port(), path), nprocs=2, join=True)
+    res = torch.load(path)
+    assert res["oracle"] == 1 and res["same_as_nccl"] == 1, res
