@@ -14,6 +14,20 @@ namespace tg {
 
 namespace {
 
+// Debug aid (compile with -DTG_TRACE): CTA 0 stamps %globaltimer at the steps of its first 256 k-blocks into
+// the partial-sum area of the workspace as [k-block][8] uint64 (0-2 MMA thread, 3-5 first promotion warp).
+#ifdef TG_TRACE
+#define TG_BS_STAMP(i, slot)                                                                            \
+  do {                                                                                                  \
+    if (blockIdx.x == 0 && (i) < 256 && p.ws_partial != nullptr)                                        \
+      reinterpret_cast<unsigned long long*>(p.ws_partial)[(i) * 8 + (slot)] = globaltimer_ns();        \
+  } while (0)
+#else
+#define TG_BS_STAMP(i, slot) \
+  do {                       \
+  } while (0)
+#endif
+
 constexpr int kBN = 128;
 constexpr int kEpiWarps = 8;
 constexpr int kThreads = 64 + 32 * kEpiWarps;  // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
@@ -102,38 +116,47 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
+      // all 32 lanes walk the loops (uniform control flow); one elected lane issues the tensor-core work
+      const bool elected = elect_one();
       constexpr uint32_t idesc = make_idesc_e4m3_f32(kBM, kBN);
       int s = 0;
       uint32_t ph = 0;
       int buf = 0;
       uint32_t aph = 0;
       bool ok = true;
+      [[maybe_unused]] int it = 0;
       for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
         const int t = u / p.splits, sp = u - t * p.splits;
         const int kb0 = sp * p.kb_per_split;
         const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
-        for (int kb = kb0; kb < kb1; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           if (!mbar_wait(bar_tempty + 8 * buf, aph ^ 1u, abort_flag)) {
             report_timeout(p.status, kRoleMma * 1000 + 11);
             ok = false;
             break;
           }
+          if (elected) TG_BS_STAMP(it, 0);
           if (!mbar_wait(bar_full + 8 * s, ph, abort_flag)) {
             report_timeout(p.status, kRoleMma * 1000 + 12);
             ok = false;
             break;
           }
+          if (elected) TG_BS_STAMP(it, 1);
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * kBN);
           const uint64_t adesc = make_kmajor_sw128_desc(a_base + s * kABytes);
           const uint64_t bdesc = make_kmajor_sw128_desc(b_base + s * kBBytes);
+          if (elected) {
 #pragma unroll
-          for (int k = 0; k < kBK / kUmmaK; ++k) {
-            mma_f8f6f4(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, k > 0 ? 1u : 0u);
+            for (int k = 0; k < kBK / kUmmaK; ++k) {
+              mma_f8f6f4(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, k > 0 ? 1u : 0u);
+            }
+            tc_commit(bar_empty + 8 * s);
+            tc_commit(bar_tfull + 8 * buf);  // this k-block's partial product is complete
+            TG_BS_STAMP(it, 2);
           }
-          tc_commit(bar_empty + 8 * s);
-          tc_commit(bar_tfull + 8 * buf);  // this k-block's partial product is complete
+          __syncwarp();
           if (++s == S) {
             s = 0;
             ph ^= 1u;
@@ -154,6 +177,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     int buf = 0;
     uint32_t aph = 0;
     bool ok = true;
+    [[maybe_unused]] int eit = 0;
     for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
       const int t = u / p.splits, sp = u - t * p.splits;
       int tm, tn;
@@ -170,7 +194,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int j = 0; j < 64; ++j) acc[j] = 0.f;
       float sc_next = (kb0 < kb1 && row_ok) ? __ldg(as_row + kb0) * __ldg(bs_row + kb0) : 0.f;
 #pragma unroll 1
-      for (int kb = kb0; kb < kb1; ++kb) {
+      for (int kb = kb0; kb < kb1; ++kb, ++eit) {
         const float sc = sc_next;
         if (kb + 1 < kb1 && row_ok) sc_next = __ldg(as_row + kb + 1) * __ldg(bs_row + kb + 1);
         bool w = mbar_wait(bar_tfull + 8 * buf, aph, abort_flag);
@@ -181,12 +205,14 @@ __global__ void __launch_bounds__(kThreads, 1)
           break;
         }
         tc_fence_after();
+        if (threadIdx.x == 64) TG_BS_STAMP(eit, 3);
         const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                                 static_cast<uint32_t>(buf * kBN + half * 64);
         uint32_t r0[32], r1[32];
         tmem_ld_32x32(t_addr, r0);
         tmem_ld_32x32(t_addr + 32, r1);
         tmem_ld_wait();
+        if (threadIdx.x == 64) TG_BS_STAMP(eit, 4);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
@@ -194,6 +220,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(r0[j]), sc, acc[j]);
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[32 + j] = fmaf(__uint_as_float(r1[j]), sc, acc[32 + j]);
+        if (threadIdx.x == 64) TG_BS_STAMP(eit, 5);
         if (++buf == kAccBufs) {
           buf = 0;
           aph ^= 1u;

@@ -187,9 +187,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer (both CTAs)
-    if (lane == 0) {
-      prefetch_tmap(&tmA);
-      prefetch_tmap(&tmB);
+    // All 32 lanes walk the loops (warp-uniform control flow, so addresses and descriptors stay in
+    // uniform registers); one elected lane issues the TMA copies.
+    const bool elected = elect_one();
+    {
+      if (elected) {
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+      }
       const uint32_t leader_full = map_to_cta(bar_full, 0);
       int s = 0;
       uint32_t ph = 0;
@@ -202,14 +207,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         const CUtensorMap* mapB = (bn == kBN) ? &tmB : &tmBt;  // the slice map boxes bn / 2 rows
         const uint32_t pair_tx = 2u * static_cast<uint32_t>(kABytes + (bn >> 1) * kBK);
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag)) {
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag))) {
             report_timeout(p.status, kRoleProducer * 1000 + 31);
             ok = false;
             break;
           }
-          if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, pair_tx);  // both CTAs' bytes
-          tma_load_2d_pair(a_base + s * kABytes, &tmA, leader_full + 8 * s, kb * kBK, a_row);
-          tma_load_2d_pair(b_base + s * kBBytes, mapB, leader_full + 8 * s, kb * kBK, b_row);
+          if (elected) {
+            if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, pair_tx);  // both CTAs' bytes
+            tma_load_2d_pair(a_base + s * kABytes, &tmA, leader_full + 8 * s, kb * kBK, a_row);
+            tma_load_2d_pair(b_base + s * kBBytes, mapB, leader_full + 8 * s, kb * kBK, b_row);
+          }
+          __syncwarp();
           if (++s == S) {
             s = 0;
             ph ^= 1u;
@@ -219,7 +227,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer (leader CTA only)
-    if (lane == 0 && leader) {
+    // The whole warp walks the loops (warp-uniform control flow: the descriptors stay in uniform registers,
+    // which takes the per-instruction issue cost off the critical path); one elected lane issues the MMAs.
+    if (leader) {
+      const bool elected = elect_one();
       const uint32_t peer_empty = map_to_cta(bar_empty, 1);
       const uint32_t peer_tfull = map_to_cta(bar_tfull, 1);
       int s = 0;
@@ -230,14 +241,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       for (int u = pair_id; u < num_units && ok; u += num_pairs) {
         const int bn = (u < plan.full_tiles) ? kBN : kBN / plan.tail_div;
         const uint32_t idesc = make_idesc_e4m3_f32(256, bn);
-        if (!mbar_wait(bar_tempty + 8 * buf, aph ^ 1u, abort_flag)) {
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_tempty + 8 * buf, aph ^ 1u, abort_flag))) {
           report_timeout(p.status, kRoleMma * 1000 + 31);
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * kBN);
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag)) {
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_full + 8 * s, ph, abort_flag))) {
             report_timeout(p.status, kRoleMma * 1000 + 32);
             ok = false;
             break;
@@ -245,20 +256,26 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
           tc_fence_after();
           const uint64_t adesc = make_kmajor_sw128_desc(a_base + s * kABytes);
           const uint64_t bdesc = make_kmajor_sw128_desc(b_base + s * kBBytes);
+          if (elected) {
 #pragma unroll
-          for (int k = 0; k < kBK / kUmmaK; ++k) {
-            mma_f8f6f4_pair(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < kBK / kUmmaK; ++k) {
+              mma_f8f6f4_pair(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            }
+            tc_commit_pair(bar_empty + 8 * s);   // this CTA's stage is free again ...
+            tc_commit_pair(peer_empty + 8 * s);  // ... and so is the peer's
           }
-          tc_commit_pair(bar_empty + 8 * s);   // this CTA's stage is free again ...
-          tc_commit_pair(peer_empty + 8 * s);  // ... and so is the peer's
+          __syncwarp();
           if (++s == S) {
             s = 0;
             ph ^= 1u;
           }
         }
         if (!ok) break;
-        tc_commit_pair(bar_tfull + 8 * buf);
-        tc_commit_pair(peer_tfull + 8 * buf);
+        if (elected) {
+          tc_commit_pair(bar_tfull + 8 * buf);
+          tc_commit_pair(peer_tfull + 8 * buf);
+        }
+        __syncwarp();
         buf ^= 1;
         if (buf == 0) aph ^= 1u;
       }
