@@ -87,9 +87,12 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int num_units = num_tiles * p.splits;
 
   if (warp == 0) {
-    if (lane == 0) {
-      prefetch_tmap(&tmA);
-      prefetch_tmap(&tmB);
+    {
+      const bool elected = elect_one();  // warp-uniform loops, one lane issues the copies
+      if (elected) {
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+      }
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -100,14 +103,17 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int kb0 = sp * p.kb_per_split;
         const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag)) {
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag))) {
             report_timeout(p.status, kRoleProducer * 1000 + 11);
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(bar_full + 8 * s, kStageBytes);
-          tma_load_2d(a_base + s * kABytes, &tmA, bar_full + 8 * s, kb * kBK, tm * kBM);
-          tma_load_2d(b_base + s * kBBytes, &tmB, bar_full + 8 * s, kb * kBK, tn * kBN);
+          if (elected) {
+            mbar_arrive_expect_tx(bar_full + 8 * s, kStageBytes);
+            tma_load_2d(a_base + s * kABytes, &tmA, bar_full + 8 * s, kb * kBK, tm * kBM);
+            tma_load_2d(b_base + s * kBBytes, &tmB, bar_full + 8 * s, kb * kBK, tn * kBN);
+          }
+          __syncwarp();
           if (++s == S) {
             s = 0;
             ph ^= 1u;

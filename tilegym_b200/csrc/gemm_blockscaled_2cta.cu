@@ -147,9 +147,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   const int num_pairs = gridDim.x >> 1;
 
   if (warp == 0) {
-    if (lane == 0) {
-      prefetch_tmap(&tmA);
-      prefetch_tmap(&tmB);
+    {
+      const bool elected = elect_one();  // warp-uniform loops, one lane issues the copies
+      if (elected) {
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+      }
       const uint32_t leader_full = map_to_cta(bar_full, 0);
       int s = 0;
       uint32_t ph = 0;
@@ -160,14 +163,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         const int a_row = tm * 256 + static_cast<int>(rank) * kBM;
         const int b_row = tn * kBN + static_cast<int>(rank) * kBNHalf;
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag)) {
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag))) {
             report_timeout(p.status, kRoleProducer * 1000 + 41);
             ok = false;
             break;
           }
-          if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, 2 * kStageBytes);
-          tma_load_2d_pair(a_base + s * kABytes, &tmA, leader_full + 8 * s, kb * kBK, a_row);
-          tma_load_2d_pair(b_base + s * kBBytes, &tmB, leader_full + 8 * s, kb * kBK, b_row);
+          if (elected) {
+            if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, 2 * kStageBytes);
+            tma_load_2d_pair(a_base + s * kABytes, &tmA, leader_full + 8 * s, kb * kBK, a_row);
+            tma_load_2d_pair(b_base + s * kBBytes, &tmB, leader_full + 8 * s, kb * kBK, b_row);
+          }
+          __syncwarp();
           if (++s == S) {
             s = 0;
             ph ^= 1u;
@@ -176,7 +182,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && leader) {
+    if (leader) {
+      const bool elected = elect_one();  // warp-uniform loops, one lane issues the tensor-core work
       constexpr uint32_t idesc = make_idesc_e4m3_f32(256, kBN);
       const uint32_t peer_tfull = map_to_cta(bar_tfull, 1);
       int s = 0;
@@ -186,12 +193,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       bool ok = true;
       for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(bar_tempty + 8 * buf, aph ^ 1u, abort_flag)) {
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_tempty + 8 * buf, aph ^ 1u, abort_flag))) {
             report_timeout(p.status, kRoleMma * 1000 + 41);
             ok = false;
             break;
           }
-          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag)) {
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_full + 8 * s, ph, abort_flag))) {
             report_timeout(p.status, kRoleMma * 1000 + 42);
             ok = false;
             break;
@@ -200,13 +207,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
           const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * kBN);
           const uint64_t adesc = make_kmajor_sw128_desc(a_base + s * kABytes);
           const uint64_t bdesc = make_kmajor_sw128_desc(b_base + s * kBBytes);
+          if (elected) {
 #pragma unroll
-          for (int k = 0; k < kBK / kUmmaK; ++k) {
-            mma_f8f6f4_pair(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, k > 0 ? 1u : 0u);
+            for (int k = 0; k < kBK / kUmmaK; ++k) {
+              mma_f8f6f4_pair(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, k > 0 ? 1u : 0u);
+            }
+            // one k-block's partial product per buffer; the promotion warps free the smem stage when they see it
+            tc_commit_pair(bar_tfull + 8 * buf);
+            tc_commit_pair(peer_tfull + 8 * buf);
           }
-          // one k-block's partial product per buffer; the promotion warps free the smem stage when they see it
-          tc_commit_pair(bar_tfull + 8 * buf);
-          tc_commit_pair(peer_tfull + 8 * buf);
+          __syncwarp();
           if (++s == S) {
             s = 0;
             ph ^= 1u;

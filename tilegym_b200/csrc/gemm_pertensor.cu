@@ -77,9 +77,12 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
-    if (lane == 0) {
-      prefetch_tmap(&tmA);
-      prefetch_tmap(&tmB);
+    {
+      const bool elected = elect_one();  // warp-uniform loops, one lane issues the copies
+      if (elected) {
+        prefetch_tmap(&tmA);
+        prefetch_tmap(&tmB);
+      }
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -90,14 +93,17 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int kb0 = sp * p.kb_per_split;
         const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag)) {
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag))) {
             report_timeout(p.status, kRoleProducer * 1000 + 1);
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(bar_full + 8 * s, Cfg::kStageBytes);
-          tma_load_2d(a_base + s * Cfg::kABytes, &tmA, bar_full + 8 * s, kb * kBK, tm * kBM);
-          tma_load_2d(b_base + s * Cfg::kBBytes, &tmB, bar_full + 8 * s, kb * kBK, tn * BN);
+          if (elected) {
+            mbar_arrive_expect_tx(bar_full + 8 * s, Cfg::kStageBytes);
+            tma_load_2d(a_base + s * Cfg::kABytes, &tmA, bar_full + 8 * s, kb * kBK, tm * kBM);
+            tma_load_2d(b_base + s * Cfg::kBBytes, &tmB, bar_full + 8 * s, kb * kBK, tn * BN);
+          }
+          __syncwarp();
           if (++s == S) {
             s = 0;
             ph ^= 1u;
@@ -107,7 +113,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    {
+      const bool elected = elect_one();  // warp-uniform loops, one lane issues the tensor-core work
       constexpr uint32_t idesc = make_idesc_e4m3_f32(kBM, BN);
       int s = 0;
       uint32_t ph = 0;
@@ -118,14 +125,14 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int t = u / p.splits, sp = u - t * p.splits;
         const int kb0 = sp * p.kb_per_split;
         const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
-        if (!mbar_wait(bar_tempty + 8 * buf, aph ^ 1u, abort_flag)) {
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_tempty + 8 * buf, aph ^ 1u, abort_flag))) {
           report_timeout(p.status, kRoleMma * 1000 + 1);
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BN);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag)) {
+          if (!__all_sync(0xffffffffu, mbar_wait(bar_full + 8 * s, ph, abort_flag))) {
             report_timeout(p.status, kRoleMma * 1000 + 2);
             ok = false;
             break;
@@ -133,18 +140,22 @@ __global__ void __launch_bounds__(kThreads, 1)
           tc_fence_after();
           const uint64_t adesc = make_kmajor_sw128_desc(a_base + s * Cfg::kABytes);
           const uint64_t bdesc = make_kmajor_sw128_desc(b_base + s * Cfg::kBBytes);
+          if (elected) {
 #pragma unroll
-          for (int k = 0; k < kBK / kUmmaK; ++k) {
-            mma_f8f6f4(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < kBK / kUmmaK; ++k) {
+              mma_f8f6f4(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            }
+            tc_commit(bar_empty + 8 * s);  // frees the smem stage once these MMAs have read it
           }
-          tc_commit(bar_empty + 8 * s);  // frees the smem stage once these MMAs have read it
+          __syncwarp();
           if (++s == S) {
             s = 0;
             ph ^= 1u;
           }
         }
         if (!ok) break;
-        tc_commit(bar_tfull + 8 * buf);  // accumulator complete
+        if (elected) tc_commit(bar_tfull + 8 * buf);  // accumulator complete
+        __syncwarp();
         buf ^= 1;
         if (buf == 0) aph ^= 1u;
       }

@@ -163,17 +163,24 @@ __global__ void __launch_bounds__(kThreads, 2)
   if (threadIdx.x == 0) TG_STAMP(1);
 
   if (warp == 0) {
-    if (lane == 0) {
+    pre = __shfl_sync(0xffffffffu, pre, 0);      // thread 0 issued the first ring
+    pol_w = __shfl_sync(0xffffffffu, pol_w, 0);
+    pol_x = __shfl_sync(0xffffffffu, pol_x, 0);
+    {
+      const bool elected = elect_one();  // warp-uniform loops, one lane issues the copies
       int s = pre % S;
       uint32_t ph = (pre == S) ? 1u : 0u;
       for (int kb = kb0 + pre; kb < kb1; ++kb) {
-        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag)) {
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag))) {
           report_timeout(p.status, kRoleProducer * 1000 + 21);
           break;
         }
-        mbar_arrive_expect_tx(bar_full + 8 * s, stage_tx);
-        tma_load_2d_hint(w_base + s * Cfg::kWBytes, &tmW, bar_full + 8 * s, kb * kBK, row0, pol_w);
-        tma_load_2d_hint(x_base + s * Cfg::kXBytes, &tmX, bar_full + 8 * s, kb * kBK, 0, pol_x);
+        if (elected) {
+          mbar_arrive_expect_tx(bar_full + 8 * s, stage_tx);
+          tma_load_2d_hint(w_base + s * Cfg::kWBytes, &tmW, bar_full + 8 * s, kb * kBK, row0, pol_w);
+          tma_load_2d_hint(x_base + s * Cfg::kXBytes, &tmX, bar_full + 8 * s, kb * kBK, 0, pol_x);
+        }
+        __syncwarp();
         if (++s == S) {
           s = 0;
           ph ^= 1u;
@@ -181,34 +188,39 @@ __global__ void __launch_bounds__(kThreads, 2)
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
+      const bool elected = elect_one();  // warp-uniform loops, one lane issues the tensor-core work
       constexpr uint32_t idesc = make_idesc_e4m3_f32(kBM, MP);
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
       for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait(bar_full + 8 * s, ph, abort_flag)) {
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_full + 8 * s, ph, abort_flag))) {
           report_timeout(p.status, kRoleMma * 1000 + 21);
           ok = false;
           break;
         }
         tc_fence_after();
-        if (kb == kb0) TG_STAMP(3);
+        if (kb == kb0 && elected) TG_STAMP(3);
         const uint64_t wdesc = make_kmajor_sw128_desc(w_base + s * Cfg::kWBytes);
         const uint64_t xdesc = make_kmajor_sw128_desc(x_base + s * Cfg::kXBytes);
+        if (elected) {
 #pragma unroll
-        for (int k = 0; k < kBK / kUmmaK; ++k) {
-          // the MMA always spans 128 lanes; lanes >= tile_rows see stale shared memory and are never stored
-          mma_f8f6f4(tmem_base, wdesc + 2u * k, xdesc + 2u * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            // the MMA always spans 128 lanes; lanes >= tile_rows see stale shared memory and are never stored
+            mma_f8f6f4(tmem_base, wdesc + 2u * k, xdesc + 2u * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(bar_empty + 8 * s);
         }
-        tc_commit(bar_empty + 8 * s);
+        __syncwarp();
         if (++s == S) {
           s = 0;
           ph ^= 1u;
         }
       }
-      if (ok) tc_commit(bar_tfull);
-      TG_STAMP(4);
+      if (ok && elected) tc_commit(bar_tfull);
+      if (elected) TG_STAMP(4);
+      __syncwarp();
     }
   }
 
