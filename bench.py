@@ -237,11 +237,32 @@ def run_ours_single(args):
     h2d = sum(t.numel() * t.element_size() for t in host_in)
     d2h = sum(t.numel() * t.element_size() for t in host_out)
 
+    # Three streams: host->device copies, GEMMs (the current stream) and device->host copies overlap across
+    # the four GEMMs of a step and across steps; events keep each device buffer from being overwritten
+    # while a GEMM or a copy still uses it.  Every byte counted in h2d / d2h crosses PCIe inside the timed region.
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    ev_in = [torch.cuda.Event() for _ in cases]      # activation copy i has landed
+    ev_gemm = [torch.cuda.Event() for _ in cases]    # GEMM i is done (input consumed, output ready)
+    ev_out = [torch.cuda.Event() for _ in cases]     # result copy i has left the device buffer
+    main = torch.cuda.current_stream(dev)
+    for e in ev_gemm + ev_out:
+        e.record(main)
+
     def step_e2e():
-        for (name, a8, b8, sa, sb, out), hin, hout in zip(cases, host_in, host_out):
-            a8.copy_(hin, non_blocking=True)
+        for i, ((name, a8, b8, sa, sb, out), hin, hout) in enumerate(zip(cases, host_in, host_out)):
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_gemm[i])  # the previous step's GEMM has read this activation buffer
+                a8.copy_(hin, non_blocking=True)
+                ev_in[i].record(s_in)
+            main.wait_event(ev_in[i])
+            main.wait_event(ev_out[i])       # the previous step's result has been copied out of `out`
             tg.fp8_scaled_mm(a8, b8, sa, sb, None, torch.bfloat16, out=out)
-            hout.copy_(out, non_blocking=True)
+            ev_gemm[i].record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_gemm[i])
+                hout.copy_(out, non_blocking=True)
+                ev_out[i].record(s_out)
+        main.wait_stream(s_out)              # the step's results are on the host when the step ends
 
     e2e_steps = max(3, min(args.steps, 20))
     sec_e2e = timed(step_e2e, e2e_steps, 3, dev)

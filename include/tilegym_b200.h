@@ -171,6 +171,15 @@ TG_API int32_t tg_quant_pertensor(const TgTensorDesc* Y, uint64_t scale_out, con
 TG_API int32_t tg_weight_quant_block(const TgTensorDesc* Y, const TgTensorDesc* S, const TgTensorDesc* X,
                               int32_t block, int32_t device_id, uint64_t stream);
 
+/* Process-wide promise that the B operand (weights) of small-M GEMMs (M <= 64) is
+ * never written by the kernel that precedes the GEMM on its stream.  The small-M
+ * kernel is launched with programmatic dependent launch; with this promise it
+ * starts streaming weights while the previous kernel's last CTAs are still
+ * finishing (activations, scales, bias and C are touched only after the
+ * previous kernel has completed either way).  Returns the previous setting.
+ * No reference counterpart. */
+TG_API int32_t tg_set_static_weights(int32_t on);
+
 /* Reads (and clears) the device-side status word of `device_id` after
  * synchronising the device: 0, or TG_ERR_TIMEOUT with *detail set to a code
  * naming the wait that gave up.  detail may be NULL. */

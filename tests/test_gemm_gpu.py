@@ -20,7 +20,7 @@ import tilegym_b200 as tg  # noqa: E402
 from tilegym_b200 import _lib  # noqa: E402
 
 KNOBS = ("TILEGYM_B200_BN", "TILEGYM_B200_SPLITS", "TILEGYM_B200_FORCE_PATH", "TILEGYM_B200_SMALLM_WS",
-         "TILEGYM_B200_2CTA", "TILEGYM_B200_GROUP_M", "TILEGYM_B200_BS_PAIR", "TILEGYM_B200_TILE_ROWS", "TILEGYM_B200_TAIL_DIV")
+         "TILEGYM_B200_2CTA", "TILEGYM_B200_GROUP_M", "TILEGYM_B200_BS_PAIR", "TILEGYM_B200_TILE_ROWS", "TILEGYM_B200_TAIL_DIV", "TILEGYM_B200_PDL", "TILEGYM_B200_STATIC_WEIGHTS", "TILEGYM_B200_TMA_STORE")
 
 
 @pytest.fixture(autouse=True)
@@ -133,6 +133,35 @@ def test_cta_pair_and_single_cta_kernels_agree(dev):
     os.environ["TILEGYM_B200_2CTA"] = "0"
     single = tg.fp8_scaled_mm(a8, b8, sa, sb)
     assert torch.equal(pair, single)  # same fp32 accumulation order inside the tensor core, same epilogue
+
+
+def test_static_weights_mode_back_to_back(dev):
+    """With the static-weights promise, decode GEMMs launched back to back (programmatic dependent launch:
+    weights stream in before the previous kernel has finished) still read the activations the previous
+    kernel wrote: a chain y1 = x W1^T, y2 = quant(y1) W2^T equals the chain without the promise."""
+    g = torch.Generator().manual_seed(3)
+    w1 = (torch.randn(4096, 4096, generator=g) * 0.02).to(dev)
+    w2 = (torch.randn(4096, 4096, generator=g) * 0.02).to(dev)
+    q1, s1 = tg.quant_per_tensor(w1)
+    q2, s2 = tg.quant_per_tensor(w2)
+    x, sx = tg.quant_per_tensor(torch.randn(16, 4096, generator=g).to(dev))
+
+    def chain():
+        outs = []
+        for _ in range(4):
+            y1 = tg.fp8_scaled_mm(x, q1, sx, s1)
+            yq, sy = tg.quant_per_tensor(y1)
+            outs.append(tg.fp8_scaled_mm(yq, q2, sy, s2))
+            outs.append(tg.fp8_scaled_mm(x, q2, sx, s2))  # two GEMMs directly behind each other
+        return torch.stack(outs)
+
+    base = chain()
+    prev = tg.set_static_weights(True)
+    try:
+        fast = chain()
+    finally:
+        tg.set_static_weights(prev)
+    assert torch.equal(base, fast)
 
 
 def test_split_k_is_bit_stable(dev):

@@ -15,6 +15,7 @@ from .ops import (  # noqa: F401
     gemm_alpha_beta,
     matmul,
     quant_per_tensor,
+    set_static_weights,
     w8a8_block_fp8_matmul,
     weight_dequant,
     weight_quant_block,

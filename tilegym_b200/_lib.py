@@ -65,6 +65,7 @@ _lib: Optional[ctypes.CDLL] = None
 _P = ctypes.POINTER(TensorDesc)
 SIGNATURES = {
     "tg_version": (ctypes.c_int32, []),
+    "tg_set_static_weights": (ctypes.c_int32, [ctypes.c_int32]),
     "tg_last_error_string": (ctypes.c_char_p, []),
     "tg_fp8_gemm_workspace_bytes": (ctypes.c_uint64, [ctypes.c_int64] * 3),
     "tg_fp8_gemm_pertensor": (

@@ -150,6 +150,10 @@ int32_t check_output(const TgTensorDesc* C, int64_t M, int64_t N) {
   return TG_OK;
 }
 
+// Process-wide promise (tg_set_static_weights): the B operand of small-M GEMMs is never written by the
+// kernel that precedes the GEMM on its stream (weights of a Linear layer), see GemmParams::flags.
+int32_t g_static_weights = 0;
+
 constexpr uint64_t kWsCounterBytes = 64ull << 10;
 constexpr uint64_t kWsPartialBytes = 48ull << 20;
 
@@ -247,6 +251,12 @@ extern "C" {
 
 int32_t tg_version(void) { return 100; }
 
+int32_t tg_set_static_weights(int32_t on) {
+  const int32_t old = g_static_weights;
+  g_static_weights = on ? 1 : 0;
+  return old;
+}
+
 const char* tg_last_error_string(void) { return g_err; }
 
 uint64_t tg_fp8_gemm_workspace_bytes(int64_t, int64_t, int64_t) { return kWsCounterBytes + kWsPartialBytes; }
@@ -325,6 +335,10 @@ static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, cons
     // distributed shared memory; TILEGYM_B200_SMALLM_WS=1 selects the global-workspace reduction.
     const bool use_ws = env_int("TILEGYM_B200_SMALLM_WS", 0) != 0;
     const bool ws_ok = have_ws;
+    // bit 1: launch with programmatic stream serialization (the kernel waits before touching global memory);
+    // bit 0: the caller promised static weights, whose loads may then start before that wait
+    p.flags = (env_int("TILEGYM_B200_PDL", 1) != 0 ? 2 : 0) |
+              ((g_static_weights != 0 || env_int("TILEGYM_B200_STATIC_WEIGHTS", 0) != 0) ? 1 : 0);
     choose_smallm_config(N, p.num_kb, st.num_sms, mp, &p.tile_rows, &p.splits, &p.kb_per_split);
     if (use_ws && !ws_ok) {
       p.splits = 1;

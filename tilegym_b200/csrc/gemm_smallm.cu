@@ -116,6 +116,7 @@ __global__ void __launch_bounds__(kThreads, 2)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  griddep_launch_dependents();  // the next kernel's CTAs may take the place of ours as we finish
   if (threadIdx.x == 0) TG_STAMP(0);
 
   // one work unit per CTA: weight-row tile tn (p.tile_rows rows), K split sp
@@ -141,11 +142,18 @@ __global__ void __launch_bounds__(kThreads, 2)
     pol_w = policy_evict_first();  // weights are read once
     pol_x = policy_evict_last();   // activations are re-read by every CTA
     pre = min(S, kb1 - kb0);
+    // Programmatic dependent launch: this grid may have been started while the previous kernel on the
+    // stream was still finishing.  Weights declared static are streamed right away; everything the
+    // previous kernel may have produced (the activations) is touched only after griddep_wait().
+    const bool early_w = (p.flags & 1) != 0;
+    if (!early_w) griddep_wait();
     for (int i = 0; i < pre; ++i) {
       mbar_arrive_expect_tx(bar_full + 8 * i, stage_tx);
       tma_load_2d_hint(w_base + i * Cfg::kWBytes, &tmW, bar_full + 8 * i, (kb0 + i) * kBK, row0, pol_w);
-      tma_load_2d_hint(x_base + i * Cfg::kXBytes, &tmX, bar_full + 8 * i, (kb0 + i) * kBK, 0, pol_x);
     }
+    if (early_w) griddep_wait();
+    for (int i = 0; i < pre; ++i)
+      tma_load_2d_hint(x_base + i * Cfg::kXBytes, &tmX, bar_full + 8 * i, (kb0 + i) * kBK, 0, pol_x);
     TG_STAMP(2);
   }
   if (warp == 1) {
@@ -160,6 +168,7 @@ __global__ void __launch_bounds__(kThreads, 2)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  griddep_wait();  // every thread: no global read or write below may overtake the previous kernel
   if (threadIdx.x == 0) TG_STAMP(1);
 
   if (warp == 0) {
@@ -373,13 +382,16 @@ cudaError_t launch_mp_cluster(const CUtensorMap& tmW, const CUtensorMap& tmX, co
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = SmCfg<MP>::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = static_cast<unsigned>(p.splits);
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  // programmatic dependent launch: this grid may start while the previous kernel's last CTAs finish
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = (p.flags & 2) ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, tg_fp8_gemm_smallm_kernel<MP, true>, tmW, tmX, p);
 }
 
@@ -387,9 +399,17 @@ template <int MP>
 cudaError_t launch_mp(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, cudaStream_t stream) {
   cudaError_t e = configure_once<MP, false>();
   if (e != cudaSuccess) return e;
-  const int grid = p.tiles_n * p.splits;
-  tg_fp8_gemm_smallm_kernel<MP, false><<<grid, kThreads, SmCfg<MP>::kSmemBytes, stream>>>(tmW, tmX, p);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(p.tiles_n * p.splits), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = SmCfg<MP>::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (p.flags & 2) ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, tg_fp8_gemm_smallm_kernel<MP, false>, tmW, tmX, p);
 }
 
 }  // namespace

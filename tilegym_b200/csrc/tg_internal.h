@@ -39,6 +39,9 @@ struct GemmParams {
   uint32_t* ws_counters;  // one per output tile, zero on entry and on exit
   // diagnostics
   int32_t* status;  // device status word
+  // bit 0 (small-M kernel): the weight operand is not written by the kernel that precedes this one on the
+  // stream, so its TMA loads may be issued before the programmatic-dependent-launch wait
+  int32_t flags;
 };
 
 // Launchers (each sets its kernel's shared-memory attribute once per device).

@@ -354,6 +354,16 @@ def matmul(
     return c
 
 
+def set_static_weights(on: bool = True) -> bool:
+    """Promise (process-wide) that the weight operand of decode-sized GEMMs (at most 64 rows) is never
+    written by the kernel that runs just before the GEMM on its stream - true for the parameters of a
+    Linear layer.  The small-M kernel is launched with programmatic dependent launch and then starts
+    streaming weights while the previous kernel's last thread blocks are still finishing; activations,
+    scales, bias and the output are still only touched after the previous kernel has completed.
+    Returns the previous setting."""
+    return bool(_lib.lib().tg_set_static_weights(1 if on else 0))
+
+
 def quant_per_tensor(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """Per-tensor e4m3 quantisation: (q, scale) with scale = amax/448 as a
     one-element fp32 device tensor (1.0 for an all-zero input)."""
