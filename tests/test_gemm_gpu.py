@@ -20,7 +20,7 @@ import tilegym_b200 as tg  # noqa: E402
 from tilegym_b200 import _lib  # noqa: E402
 
 KNOBS = ("TILEGYM_B200_BN", "TILEGYM_B200_SPLITS", "TILEGYM_B200_FORCE_PATH", "TILEGYM_B200_SMALLM_WS",
-         "TILEGYM_B200_2CTA", "TILEGYM_B200_GROUP_M", "TILEGYM_B200_BS_PAIR", "TILEGYM_B200_TILE_ROWS", "TILEGYM_B200_TAIL_DIV", "TILEGYM_B200_PDL", "TILEGYM_B200_STATIC_WEIGHTS", "TILEGYM_B200_TMA_STORE")
+         "TILEGYM_B200_2CTA", "TILEGYM_B200_GROUP_M", "TILEGYM_B200_BS_PAIR", "TILEGYM_B200_BS_WIDE", "TILEGYM_B200_TILE_ROWS", "TILEGYM_B200_TAIL_DIV", "TILEGYM_B200_PDL", "TILEGYM_B200_STATIC_WEIGHTS", "TILEGYM_B200_TMA_STORE")
 
 
 @pytest.fixture(autouse=True)
@@ -312,6 +312,30 @@ def test_block_scaled_cta_pair_kernel_tails_and_agreement(dev, M, N, K):
     os.environ["TILEGYM_B200_BS_PAIR"] = "0"
     single = tg.w8a8_block_fp8_matmul(*args, [128, 128])
     torch.testing.assert_close(single, pair, rtol=1e-5, atol=1e-5)  # the 128 x 128 kernel may split K here
+
+
+@pytest.mark.parametrize("M,N,K,dtype", [(2500, 3900, 400, torch.float32), (4096, 2304, 1152, torch.bfloat16),
+                                         (1300, 7200, 2176, torch.float16)])
+def test_block_scaled_wide_tile_kernel_tails_and_agreement(dev, M, N, K, dtype):
+    """Problems whose 128 x 256 tiles fill the GPU take the wide-tile kernel: ragged M / N / K against the
+    oracle, and bit-for-bit against the 128 x 128 kernel (same k-block order, same fused multiply-adds)."""
+    g = torch.Generator().manual_seed(M + N + K)
+    A = (torch.randn(M, K, generator=g) * 0.1).to(torch.float8_e4m3fn)
+    B = (torch.randn(N, K, generator=g) * 0.1).to(torch.float8_e4m3fn)
+    As = torch.rand(M, -(-K // 128), generator=g) + 0.1
+    Bs = torch.rand(-(-N // 128), -(-K // 128), generator=g) + 0.1
+    ref = R.ref_w8a8_block_fp8_matmul(A, B, As, Bs, [128, 128], dtype)
+    args = [t.to(dev) for t in (A, B, As, Bs)]
+    os.environ["TILEGYM_B200_SPLITS"] = "1"
+    os.environ["TILEGYM_B200_BS_WIDE"] = "1"
+    wide = tg.w8a8_block_fp8_matmul(*args, [128, 128], dtype)
+    if dtype == torch.float32:
+        torch.testing.assert_close(wide.cpu(), ref, rtol=1e-4, atol=1e-4)
+    else:
+        assert R.check_tolerance(wide, ref)["ok"]
+    os.environ["TILEGYM_B200_BS_WIDE"] = "0"
+    narrow = tg.w8a8_block_fp8_matmul(*args, [128, 128], dtype)
+    assert torch.equal(wide, narrow)
 
 
 def test_block_scaled_split_k_and_leading_dims(dev):

@@ -509,6 +509,17 @@ int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, co
       return fail(TG_ERR_LAUNCH, "block-scaled GEMM (CTA pair) launch failed: %s", cudaGetErrorString(e2));
     return TG_OK;
   }
+  // Problems whose 128 x 256 tiles fill the GPU take the wide-tile kernel (a third less shared-memory traffic
+  // per flop than 128 x 128 tiles); TILEGYM_B200_BS_WIDE=0 keeps them on the 128 x 128 kernel.
+  const int64_t wide_tiles = static_cast<int64_t>(p.tiles_m) * ((N + 255) / 256);
+  if (p.splits == 1 && wide_tiles >= st.num_sms && env_int("TILEGYM_B200_BS_WIDE", 1) != 0) {
+    if ((rc = make_map(&tmB, B->ptr, N, K, B->strides[0], 256)) != TG_OK) return rc;
+    p.tiles_n = static_cast<int32_t>((N + 255) / 256);
+    cudaError_t e3 = launch_gemm_blockscaled_wide(tmA, tmB, p, st.num_sms, cs);
+    if (e3 != cudaSuccess)
+      return fail(TG_ERR_LAUNCH, "block-scaled GEMM (wide tile) launch failed: %s", cudaGetErrorString(e3));
+    return TG_OK;
+  }
   cudaError_t e = launch_gemm_blockscaled(tmA, tmB, p, st.num_sms, cs);
   if (e != cudaSuccess) return fail(TG_ERR_LAUNCH, "block-scaled GEMM launch failed: %s", cudaGetErrorString(e));
   return TG_OK;

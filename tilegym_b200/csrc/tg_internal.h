@@ -59,6 +59,9 @@ cudaError_t launch_gemm_pertensor_2cta(const CUtensorMap& tmA, const CUtensorMap
                                        int tail_div, int num_sms, cudaStream_t stream);
 cudaError_t launch_gemm_blockscaled(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
                                     int num_sms, cudaStream_t stream);
+// Wide-tile block-scaled kernel: 128 x 256 tiles (tmB boxes 256 rows, p.tiles_n counts 256-wide tiles), no split-K.
+cudaError_t launch_gemm_blockscaled_wide(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
+                                         int num_sms, cudaStream_t stream);
 // CTA-pair block-scaled kernel: 256 x 192 tiles, tmA boxes 128 rows and tmB 96, p.tiles_n counts 192-wide tiles, no split-K.
 cudaError_t launch_gemm_blockscaled_2cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
                                          int group_m, int num_sms, cudaStream_t stream);

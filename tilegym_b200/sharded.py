@@ -130,7 +130,9 @@ class FusedColumnParallelFP8Gemm:
         self.handle = symm_mem.rendezvous(self.out, group=self.group)
         esz = self.out.element_size()
         col_off = self.rank * self.n * esz
-        peers = [int(ptr) + col_off for r, ptr in enumerate(self.handle.buffer_ptrs) if r != self.rank]
+        # rank g sends to g+1, g+2, ... so that at any moment the ranks' stores fan out to different receivers
+        ptrs = self.handle.buffer_ptrs
+        peers = [int(ptrs[(self.rank + i) % self.world]) + col_off for i in range(1, self.world)]
         self._peer_arr = (ctypes.c_uint64 * max(1, len(peers)))(*peers)
         self._num_peers = len(peers)
         self.mine = self.out[:, self.rank * self.n:(self.rank + 1) * self.n]  # [M, n] view, row stride N
