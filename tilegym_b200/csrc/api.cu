@@ -515,7 +515,11 @@ int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, co
   if (p.splits == 1 && wide_tiles >= st.num_sms && env_int("TILEGYM_B200_BS_WIDE", 1) != 0) {
     if ((rc = make_map(&tmB, B->ptr, N, K, B->strides[0], 256)) != TG_OK) return rc;
     p.tiles_n = static_cast<int32_t>((N + 255) / 256);
-    cudaError_t e3 = launch_gemm_blockscaled_wide(tmA, tmB, p, st.num_sms, cs);
+    CUtensorMap tmC;
+    const bool tma_out = (C->dtype == TG_BF16 || C->dtype == TG_F16) && (C->ptr & 15u) == 0 &&
+                         ((C->strides[0] * 2) & 15) == 0 && env_int("TILEGYM_B200_TMA_STORE", 1) != 0;
+    if (tma_out && (rc = make_out_map(&tmC, C->ptr, M, N, C->strides[0] * 2, C->dtype)) != TG_OK) return rc;
+    cudaError_t e3 = launch_gemm_blockscaled_wide(tmA, tmB, tma_out ? &tmC : nullptr, p, st.num_sms, cs);
     if (e3 != cudaSuccess)
       return fail(TG_ERR_LAUNCH, "block-scaled GEMM (wide tile) launch failed: %s", cudaGetErrorString(e3));
     return TG_OK;

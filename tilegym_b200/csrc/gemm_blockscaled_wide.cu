@@ -7,12 +7,27 @@
 // (exact for arbitrary fp32 scales), by eight warps that each own 32 rows x 128 columns: 128 fp32
 // accumulators per thread.  That needs more than the 168 registers a 384-thread CTA gets per thread, so the
 // producer / MMA warpgroup hands registers to the two promotion warpgroups with setmaxnreg.
+// Two-byte outputs leave through per-warp swizzled staging buffers and bulk tensor stores.
 // Roles: warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, warps 2-3 idle, warps 4-11 promotion + store.
 #include "tg_gemm_common.cuh"
 
 namespace tg {
 
 namespace {
+
+// Debug aid (compile with -DTG_TRACE): CTA 0 stamps %globaltimer at the steps of its first 256 k-blocks into
+// the partial-sum area of the workspace as [k-block][8] uint64 (0-2 MMA warp, 3-6 first promotion warp).
+#ifdef TG_TRACE
+#define TG_BSW_STAMP(i, slot)                                                                      \
+  do {                                                                                             \
+    if (blockIdx.x == 0 && (i) < 256 && p.ws_partial != nullptr)                                   \
+      reinterpret_cast<unsigned long long*>(p.ws_partial)[(i) * 8 + (slot)] = globaltimer_ns();   \
+  } while (0)
+#else
+#define TG_BSW_STAMP(i, slot) \
+  do {                        \
+  } while (0)
+#endif
 
 constexpr int kBN = 256;
 constexpr int kEpiWarps = 8;
@@ -24,7 +39,9 @@ constexpr int kBBytes = kBN * kBK;  // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTmemCols = kAccBufs * kBN;  // 512
 constexpr int kCtrlBytes = 256;
-constexpr int kSmemBytes = kStages * kStageBytes + kCtrlBytes + 1024;
+constexpr int kOutBufBytes = 32 * 128;  // per promotion warp: 32 rows x 64 two-byte columns, 128-byte swizzle
+constexpr int kOutStageBytes = kEpiWarps * kOutBufBytes;
+constexpr int kSmemBytes = kStages * kStageBytes + kOutStageBytes + kCtrlBytes + 1024;
 static_assert((2 * kStages + 2 * kAccBufs) * 8 + 8 <= kCtrlBytes, "control block");
 static_assert(kSmemBytes <= 227 * 1024, "shared memory per CTA");
 
@@ -39,9 +56,24 @@ __device__ __forceinline__ void fma16x2(float2* acc, const uint32_t (&r)[32], fl
     acc[j] = __ffma2_rn(make_float2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])), sc2, acc[j]);
 }
 
+// Activation scales of one row for k-blocks kb .. kb+3 (0 where out of range or the row is not in the problem).
+__device__ __forceinline__ void load_as4(const float* as_row, int kb, int num_kb, bool in, bool vec, float (&a)[4]) {
+  if (in && vec && kb + 4 <= num_kb) {
+    const float4 v = __ldg(reinterpret_cast<const float4*>(as_row + kb));
+    a[0] = v.x;
+    a[1] = v.y;
+    a[2] = v.z;
+    a[3] = v.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) a[i] = (in && kb + i < num_kb) ? __ldg(as_row + kb + i) : 0.f;
+  }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
     tg_fp8_gemm_blockscaled_wide_kernel(const __grid_constant__ CUtensorMap tmA,
-                                        const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+                                        const __grid_constant__ CUtensorMap tmB,
+                                        const __grid_constant__ CUtensorMap tmC, const GemmParams p, int tma_out) {
   constexpr int S = kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -49,7 +81,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint8_t* smem = smem_raw + (base - raw);
   const uint32_t a_base = base;
   const uint32_t b_base = base + S * kABytes;
-  uint8_t* ctrl = smem + S * kStageBytes;
+  uint8_t* out_stage = smem + S * kStageBytes;  // 1024-byte aligned
+  uint8_t* ctrl = out_stage + kOutStageBytes;
   const uint32_t bar_full = smem_u32(ctrl);
   const uint32_t bar_empty = bar_full + 8 * S;
   const uint32_t bar_tfull = bar_empty + 8 * S;
@@ -124,18 +157,21 @@ __global__ void __launch_bounds__(kThreads, 1)
       int buf = 0;
       uint32_t aph = 0;
       bool ok = true;
+      [[maybe_unused]] int it = 0;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
           if (!mbar_wait(bar_tempty + 8 * buf, aph ^ 1u, abort_flag)) {
             report_timeout(p.status, kRoleMma * 1000 + 51);
             ok = false;
             break;
           }
+          if (elected) TG_BSW_STAMP(it, 0);
           if (!mbar_wait(bar_full + 8 * s, ph, abort_flag)) {
             report_timeout(p.status, kRoleMma * 1000 + 52);
             ok = false;
             break;
           }
+          if (elected) TG_BSW_STAMP(it, 1);
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * kBN);
           const uint64_t adesc = make_kmajor_sw128_desc(a_base + s * kABytes);
@@ -147,6 +183,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             tc_commit(bar_empty + 8 * s);
             tc_commit(bar_tfull + 8 * buf);  // this k-block's partial product is complete
+            TG_BSW_STAMP(it, 2);
           }
           __syncwarp();
           if (++s == S) {
@@ -167,9 +204,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int q = warp & 3;   // TMEM lane quadrant
     const int half = e >> 2;  // which 128 of the tile's 256 columns = which quantisation block
     const bool vec_ok = c_rows_aligned(p);
+    // rows of As that start 16-byte aligned are read four k-blocks at a time: a warp's 32 rows cost 32
+    // L1 transactions per load, and L1 shares its data path with the tensor core's operand reads
+    const bool as_vec = ((reinterpret_cast<uintptr_t>(p.As) & 15u) == 0) && ((p.ldas & 3) == 0);
+    uint8_t* my_stage = out_stage + e * kOutBufBytes;
     int buf = 0;
     uint32_t aph = 0;
     bool ok = true;
+    [[maybe_unused]] int eit = 0;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
@@ -182,44 +224,90 @@ __global__ void __launch_bounds__(kThreads, 1)
       float2 acc2[64];
 #pragma unroll
       for (int j = 0; j < 64; ++j) acc2[j] = make_float2(0.f, 0.f);
-      float sc_next = in ? __ldg(as_row) * __ldg(bs_row) : 0.f;
 #pragma unroll 1
-      for (int kb = 0; kb < p.num_kb; ++kb) {
-        const float2 sc2 = make_float2(sc_next, sc_next);
-        if (kb + 1 < p.num_kb && in) sc_next = __ldg(as_row + kb + 1) * __ldg(bs_row + kb + 1);
-        bool w = mbar_wait(bar_tfull + 8 * buf, aph, abort_flag);
-        w = __all_sync(0xffffffffu, w);
-        if (!w) {
-          report_timeout(p.status, kRoleEpilogue * 1000 + 51);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
-                                static_cast<uint32_t>(buf * kBN + half * 128);
-        // two 32-column reads in flight while the previous two are multiplied in
-        uint32_t ra[32], rb[32];
-        tmem_ld_32x32(t_addr, ra);
-        tmem_ld_32x32(t_addr + 32, rb);
-        tmem_ld_wait();
-        fma16x2(acc2, ra, sc2);
-        tmem_ld_32x32(t_addr + 64, ra);
-        fma16x2(acc2 + 16, rb, sc2);
-        tmem_ld_32x32(t_addr + 96, rb);
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);  // the buffer is in registers: hand it back
-        fma16x2(acc2 + 32, ra, sc2);
-        fma16x2(acc2 + 48, rb, sc2);
-        if (++buf == kAccBufs) {
-          buf = 0;
-          aph ^= 1u;
+      for (int kbg = 0; kbg < p.num_kb && ok; kbg += 4) {
+        float a_cur[4];
+        load_as4(as_row, kbg, p.num_kb, in, as_vec, a_cur);
+#pragma unroll 1
+        for (int i = 0; i < 4; ++i) {  // not unrolled: four copies of the body spill
+          const int kb = kbg + i;
+          if (kb >= p.num_kb) break;
+          const float sc = in ? a_cur[0] * __ldg(bs_row + kb) : 0.f;  // the Bs load is warp-uniform
+          a_cur[0] = a_cur[1];  // rotate instead of indexing: the array stays in registers
+          a_cur[1] = a_cur[2];
+          a_cur[2] = a_cur[3];
+          const float2 sc2 = make_float2(sc, sc);
+          bool w = mbar_wait(bar_tfull + 8 * buf, aph, abort_flag);
+          w = __all_sync(0xffffffffu, w);
+          if (!w) {
+            report_timeout(p.status, kRoleEpilogue * 1000 + 51);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          if (threadIdx.x == 128) TG_BSW_STAMP(eit, 3);
+          const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                                  static_cast<uint32_t>(buf * kBN + half * 128);
+          // two 32-column reads in flight while the previous two are multiplied in
+          uint32_t ra[32], rb[32];
+          tmem_ld_32x32(t_addr, ra);
+          tmem_ld_32x32(t_addr + 32, rb);
+          tmem_ld_wait();
+          if (threadIdx.x == 128) TG_BSW_STAMP(eit, 4);
+          fma16x2(acc2, ra, sc2);
+          tmem_ld_32x32(t_addr + 64, ra);
+          fma16x2(acc2 + 16, rb, sc2);
+          tmem_ld_32x32(t_addr + 96, rb);
+          tmem_ld_wait();
+          if (threadIdx.x == 128) TG_BSW_STAMP(eit, 5);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);  // the buffer is in registers: hand it back
+          fma16x2(acc2 + 32, ra, sc2);
+          fma16x2(acc2 + 48, rb, sc2);
+          if (threadIdx.x == 128) TG_BSW_STAMP(eit, 6);
+          ++eit;
+          if (++buf == kAccBufs) {
+            buf = 0;
+            aph ^= 1u;
+          }
         }
       }
       if (!ok) break;
-      if (row < p.M) {
-        const int col0 = tn * kBN + half * 128;
+      const int col0 = tn * kBN + half * 128;
+      if (tma_out) {
+        // two-byte outputs with 16-byte aligned rows: 64 columns at a time go through this warp's swizzled
+        // staging buffer and leave as one bulk tensor store, which clips rows >= M and columns >= N
+        const int row0 = tm * kBM + q * 32;
+        uint8_t* dst_row = my_stage + lane * 128;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint4 o[8];
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const float2 v0 = acc2[h * 32 + g * 4], v1 = acc2[h * 32 + g * 4 + 1];
+            const float2 v2 = acc2[h * 32 + g * 4 + 2], v3 = acc2[h * 32 + g * 4 + 3];
+            if (p.out_dtype == TG_BF16) {
+              o[g] = make_uint4(pack_bf16x2(v0.x, v0.y), pack_bf16x2(v1.x, v1.y), pack_bf16x2(v2.x, v2.y),
+                                pack_bf16x2(v3.x, v3.y));
+            } else {
+              o[g] = make_uint4(pack_f16x2(v0.x, v0.y), pack_f16x2(v1.x, v1.y), pack_f16x2(v2.x, v2.y),
+                                pack_f16x2(v3.x, v3.y));
+            }
+          }
+          if (lane == 0) tma_store_wait_read<0>();  // the previous store has drained the staging buffer
+          __syncwarp();
+#pragma unroll
+          for (int g = 0; g < 8; ++g) *reinterpret_cast<uint4*>(dst_row + ((g ^ (lane & 7)) << 4)) = o[g];
+          fence_proxy_async_smem();
+          __syncwarp();
+          const int col = col0 + h * 64;
+          if (lane == 0 && col < p.N && row0 < p.M) {
+            tma_store_2d(&tmC, smem_u32(my_stage), col, row0);
+            tma_store_commit();
+          }
+        }
+      } else if (row < p.M) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           float acc[32];
@@ -232,6 +320,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
     }
+    if (tma_out && lane == 0) tma_store_wait_all<0>();  // this warp's bulk stores have completed
   }
 
   __syncwarp();
@@ -245,8 +334,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 
 }  // namespace
 
-cudaError_t launch_gemm_blockscaled_wide(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
-                                         int num_sms, cudaStream_t stream) {
+cudaError_t launch_gemm_blockscaled_wide(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap* tmC,
+                                         const GemmParams& p, int num_sms, cudaStream_t stream) {
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -258,7 +347,9 @@ cudaError_t launch_gemm_blockscaled_wide(const CUtensorMap& tmA, const CUtensorM
   }
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < num_sms ? tiles : num_sms;
-  tg_fp8_gemm_blockscaled_wide_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmB, p);
+  // tmC == nullptr selects the register -> global store epilogue (fp32 output or unaligned rows)
+  tg_fp8_gemm_blockscaled_wide_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmC != nullptr ? *tmC : tmA, p,
+                                                                              tmC != nullptr ? 1 : 0);
   return cudaGetLastError();
 }
 

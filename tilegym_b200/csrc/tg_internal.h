@@ -60,8 +60,10 @@ cudaError_t launch_gemm_pertensor_2cta(const CUtensorMap& tmA, const CUtensorMap
 cudaError_t launch_gemm_blockscaled(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
                                     int num_sms, cudaStream_t stream);
 // Wide-tile block-scaled kernel: 128 x 256 tiles (tmB boxes 256 rows, p.tiles_n counts 256-wide tiles), no split-K.
-cudaError_t launch_gemm_blockscaled_wide(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
-                                         int num_sms, cudaStream_t stream);
+// tmC: tensor map of the output (two-byte elements, box 64 x 32, 128-byte swizzle) for the bulk-store epilogue,
+// or nullptr for register -> global stores (fp32 output, unaligned rows).
+cudaError_t launch_gemm_blockscaled_wide(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap* tmC,
+                                         const GemmParams& p, int num_sms, cudaStream_t stream);
 // CTA-pair block-scaled kernel: 256 x 192 tiles, tmA boxes 128 rows and tmB 96, p.tiles_n counts 192-wide tiles, no split-K.
 cudaError_t launch_gemm_blockscaled_2cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
                                          int group_m, int num_sms, cudaStream_t stream);
