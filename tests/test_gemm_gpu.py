@@ -347,6 +347,19 @@ def test_block_scaled_split_k_and_leading_dims(dev):
     assert out.shape == (2, 70, 256) and R.check_tolerance(out, ref)["ok"]
 
 
+def test_block_scaled_forced_split_count_is_clamped_to_the_workspace(dev):
+    """A split count whose partial tiles would not fit the workspace (here 192 tiles x 12 splits x 64 KiB) is
+    reduced by the library instead of being taken literally."""
+    os.environ["TILEGYM_B200_SPLITS"] = "12"
+    os.environ["TILEGYM_B200_BS_WIDE"] = "0"
+    a8, b8, As, Bs = R.gen_block_scaled_case(128, 24576, 1536, seed=77)
+    ref = R.ref_w8a8_block_fp8_matmul(a8, b8, As, Bs, [128, 128], torch.bfloat16)
+    out = tg.w8a8_block_fp8_matmul(a8.to(dev), b8.to(dev), As.to(dev), Bs.to(dev), [128, 128], torch.bfloat16)
+    res = R.check_tolerance(out, ref)
+    assert res["ok"], res
+    _lib.device_status(0)  # no fault, no expired wait
+
+
 def test_block_scaled_rejects_other_blocks_and_dtypes(dev):
     a = torch.zeros(128, 128, dtype=torch.float8_e4m3fn, device=dev)
     with pytest.raises(RuntimeError, match="INVALID_ARGS"):

@@ -165,12 +165,12 @@ void choose_splits(int tiles, int num_kb, int num_sms, int64_t tile_floats, int 
     s = target_ctas / tiles;
     const int max_by_k = num_kb / min_kb;
     if (s > max_by_k) s = max_by_k;
-    while (s > 1 && static_cast<uint64_t>(tiles) * s * tile_floats * 4 > kWsPartialBytes) --s;
-    if (s < 1) s = 1;
   }
   s = env_int("TILEGYM_B200_SPLITS", s);
   if (s < 1) s = 1;
   if (s > num_kb) s = num_kb;
+  // the partial tiles of all splits must fit the workspace, whoever chose the split count
+  while (s > 1 && static_cast<uint64_t>(tiles) * s * tile_floats * 4 > kWsPartialBytes) --s;
   int per = (num_kb + s - 1) / s;
   s = (num_kb + per - 1) / per;  // every split owns at least one k-block
   (void)num_sms;
@@ -345,8 +345,9 @@ static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, cons
       p.kb_per_split = p.num_kb;
     }
     p.tiles_n = static_cast<int32_t>((N + p.tile_rows - 1) / p.tile_rows);
-    if (use_ws && p.tiles_n * 4 > static_cast<int64_t>(kWsCounterBytes / 4))
-      return fail(TG_ERR_ARGS, "N is too large for the workspace reduction");
+    if (use_ws && (p.tiles_n * 4 > static_cast<int64_t>(kWsCounterBytes / 4) ||
+                   static_cast<uint64_t>(p.tiles_n) * p.splits * 128 * mp * 4 > kWsPartialBytes))
+      return fail(TG_ERR_ARGS, "N (times the K splits) is too large for the workspace reduction");
     if ((rc = make_map(&tmB, B->ptr, N, K, B->strides[0], p.tile_rows)) != TG_OK) return rc;
     if ((rc = make_map(&tmA, A->ptr, M, K, A->strides[0], mp)) != TG_OK) return rc;
     cudaError_t e = (use_ws || p.splits == 1) ? launch_gemm_smallm(tmB, tmA, p, mp, cs)
@@ -509,22 +510,26 @@ int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, co
       return fail(TG_ERR_LAUNCH, "block-scaled GEMM (CTA pair) launch failed: %s", cudaGetErrorString(e2));
     return TG_OK;
   }
-  // Problems whose 128 x 256 tiles fill the GPU take the wide-tile kernel (a third less shared-memory traffic
-  // per flop than 128 x 128 tiles); TILEGYM_B200_BS_WIDE=0 keeps them on the 128 x 128 kernel.
+  // Problems with at least half a wave of 128 x 256 tiles (and no K split) take the wide-tile kernel (a third
+  // less shared-memory traffic per flop than 128 x 128 tiles); TILEGYM_B200_BS_WIDE=0 keeps them on the
+  // 128 x 128 kernel.
   const int64_t wide_tiles = static_cast<int64_t>(p.tiles_m) * ((N + 255) / 256);
-  if (p.splits == 1 && wide_tiles >= st.num_sms && env_int("TILEGYM_B200_BS_WIDE", 1) != 0) {
+  // two-byte outputs with 16-byte aligned rows leave through shared memory and bulk tensor stores
+  CUtensorMap tmC;
+  const bool tma_out = (C->dtype == TG_BF16 || C->dtype == TG_F16) && (C->ptr & 15u) == 0 &&
+                       ((C->strides[0] * 2) & 15) == 0 && env_int("TILEGYM_B200_TMA_STORE", 1) != 0;
+  if (tma_out && (rc = make_out_map(&tmC, C->ptr, M, N, C->strides[0] * 2, C->dtype)) != TG_OK) return rc;
+  // (measured: from half a wave of wide tiles on, the wide kernel also streams a small-M problem faster)
+  if (p.splits == 1 && wide_tiles >= env_int("TILEGYM_B200_BS_WIDE_MIN", (st.num_sms + 1) / 2) &&
+      env_int("TILEGYM_B200_BS_WIDE", 1) != 0) {
     if ((rc = make_map(&tmB, B->ptr, N, K, B->strides[0], 256)) != TG_OK) return rc;
     p.tiles_n = static_cast<int32_t>((N + 255) / 256);
-    CUtensorMap tmC;
-    const bool tma_out = (C->dtype == TG_BF16 || C->dtype == TG_F16) && (C->ptr & 15u) == 0 &&
-                         ((C->strides[0] * 2) & 15) == 0 && env_int("TILEGYM_B200_TMA_STORE", 1) != 0;
-    if (tma_out && (rc = make_out_map(&tmC, C->ptr, M, N, C->strides[0] * 2, C->dtype)) != TG_OK) return rc;
     cudaError_t e3 = launch_gemm_blockscaled_wide(tmA, tmB, tma_out ? &tmC : nullptr, p, st.num_sms, cs);
     if (e3 != cudaSuccess)
       return fail(TG_ERR_LAUNCH, "block-scaled GEMM (wide tile) launch failed: %s", cudaGetErrorString(e3));
     return TG_OK;
   }
-  cudaError_t e = launch_gemm_blockscaled(tmA, tmB, p, st.num_sms, cs);
+  cudaError_t e = launch_gemm_blockscaled(tmA, tmB, tma_out ? &tmC : nullptr, p, st.num_sms, cs);
   if (e != cudaSuccess) return fail(TG_ERR_LAUNCH, "block-scaled GEMM launch failed: %s", cudaGetErrorString(e));
   return TG_OK;
 }

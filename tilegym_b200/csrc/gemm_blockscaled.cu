@@ -7,6 +7,7 @@
 // tcgen05.ld and FMA it, times As*Bs, into fp32 register accumulators, while
 // the MMA warp is already filling the next of four TMEM buffers.  The tile is
 // 128 x 128 = the quantisation block, so one weight scale covers a k-block.
+// Two-byte outputs leave through per-warp swizzled staging buffers and bulk tensor stores.
 // Replaces the kernel at src/tilegym/suites/unsloth/cutile/fp8.py:243-334.
 #include "tg_gemm_common.cuh"
 
@@ -15,16 +16,26 @@ namespace tg {
 namespace {
 
 // Debug aid (compile with -DTG_TRACE): CTA 0 stamps %globaltimer at the steps of its first 256 k-blocks into
-// the partial-sum area of the workspace as [k-block][8] uint64 (0-2 MMA thread, 3-5 first promotion warp).
+// the partial-sum area of the workspace, 40 MiB in, as [k-block][8] uint64 (0-2 MMA thread, 3-5 first promotion warp).
 #ifdef TG_TRACE
 #define TG_BS_STAMP(i, slot)                                                                            \
   do {                                                                                                  \
     if (blockIdx.x == 0 && (i) < 256 && p.ws_partial != nullptr)                                        \
-      reinterpret_cast<unsigned long long*>(p.ws_partial)[(i) * 8 + (slot)] = globaltimer_ns();        \
+      (reinterpret_cast<unsigned long long*>(p.ws_partial) + (5u << 20))[(i) * 8 + (slot)] = globaltimer_ns();        \
+  } while (0)
+// second table, 41 MiB in: per CTA, the times of its first unit's steps after the k-loop (first promotion warp)
+#define TG_BS_STAMP2(slot)                                                                                        \
+  do {                                                                                                            \
+    if (threadIdx.x == 64 && p.ws_partial != nullptr && !stamped2)                                                \
+      (reinterpret_cast<unsigned long long*>(p.ws_partial) + (5u << 20) + (1u << 17))[blockIdx.x * 8 + (slot)] =   \
+          globaltimer_ns();                                                                                       \
   } while (0)
 #else
 #define TG_BS_STAMP(i, slot) \
   do {                       \
+  } while (0)
+#define TG_BS_STAMP2(slot) \
+  do {                     \
   } while (0)
 #endif
 
@@ -38,12 +49,15 @@ constexpr int kBBytes = kBN * kBK;
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTmemCols = kAccBufs * kBN;  // 512
 constexpr int kCtrlBytes = 256;
-constexpr int kSmemBytes = kStages * kStageBytes + kCtrlBytes + 1024;
+constexpr int kOutBufBytes = 32 * 128;  // per promotion warp: 32 rows x 64 two-byte columns, 128-byte swizzle
+constexpr int kOutStageBytes = kEpiWarps * kOutBufBytes;
+constexpr int kSmemBytes = kStages * kStageBytes + kOutStageBytes + kCtrlBytes + 1024;
+static_assert(kSmemBytes <= 227 * 1024, "shared memory per CTA");
 static_assert((2 * kStages + 2 * kAccBufs) * 8 + 8 <= kCtrlBytes, "control block");
 
 __global__ void __launch_bounds__(kThreads, 1)
     tg_fp8_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                                   const GemmParams p) {
+                                   const __grid_constant__ CUtensorMap tmC, const GemmParams p, int tma_out) {
   constexpr int S = kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -51,7 +65,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint8_t* smem = smem_raw + (base - raw);
   const uint32_t a_base = base;
   const uint32_t b_base = base + S * kABytes;
-  uint8_t* ctrl = smem + S * kStageBytes;
+  uint8_t* out_stage = smem + S * kStageBytes;  // 1024-byte aligned
+  uint8_t* ctrl = out_stage + kOutStageBytes;
   const uint32_t bar_full = smem_u32(ctrl);
   const uint32_t bar_empty = bar_full + 8 * S;
   const uint32_t bar_tfull = bar_empty + 8 * S;
@@ -180,10 +195,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int q = warp & 3;   // TMEM lane quadrant
     const int half = e >> 2;  // which 64 of the tile's 128 columns
     const bool vec_ok = c_rows_aligned(p);
+    uint8_t* my_stage = out_stage + e * kOutBufBytes;
     int buf = 0;
     uint32_t aph = 0;
     bool ok = true;
     [[maybe_unused]] int eit = 0;
+    [[maybe_unused]] bool stamped2 = false;
+    TG_BS_STAMP2(0);
     for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
       const int t = u / p.splits, sp = u - t * p.splits;
       int tm, tn;
@@ -233,50 +251,58 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
       if (!ok) break;
+      TG_BS_STAMP2(1);
       const int col0 = tn * kBN + half * 64;
+      const int row0 = tm * kBM + q * 32;
       if (p.splits == 1) {
-        if (row_ok) {
+        if (tma_out) {
+          stage_and_store64(&tmC, my_stage, lane, acc, p.out_dtype, col0, row0, p.M, p.N);
+        } else if (row_ok) {
           epilogue_store32(p, row, col0, acc, 1.0f, vec_ok);
           epilogue_store32(p, row, col0 + 32, acc + 32, 1.0f, vec_ok);
         }
       } else {
-        float* part = p.ws_partial + (static_cast<int64_t>(t) * p.splits + sp) * (kBM * kBN) +
-                      (half * 2) * (kBM * 32) + row_in_tile * 32;
+        // partial tile of (tile, split): per warp 16 float4 per thread, lane-contiguous, so that every store
+        // and load instruction of a warp covers 512 consecutive bytes
+        float4* part = reinterpret_cast<float4*>(p.ws_partial) +
+                       ((static_cast<int64_t>(t) * p.splits + sp) * kEpiWarps + e) * (16 * 32) + lane;
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          float4* dst = reinterpret_cast<float4*>(part + c * (kBM * 32));
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            dst[j] = make_float4(acc[32 * c + 4 * j], acc[32 * c + 4 * j + 1], acc[32 * c + 4 * j + 2],
-                                 acc[32 * c + 4 * j + 3]);
-        }
-        if (splitk_arrive_is_last(p.ws_counters + t * kEpiWarps + e, p.splits)) {
+        for (int j = 0; j < 16; ++j)
+          __stcg(part + j * 32, make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]));
+        TG_BS_STAMP2(2);
+        const bool last_arriver = splitk_arrive_is_last(p.ws_counters + t * kEpiWarps + e, p.splits);
+        TG_BS_STAMP2(3);
+        if (last_arriver) {
 #pragma unroll
           for (int j = 0; j < 64; ++j) acc[j] = 0.f;
-          const float* tile_part = p.ws_partial + static_cast<int64_t>(t) * p.splits * (kBM * kBN) +
-                                   (half * 2) * (kBM * 32) + row_in_tile * 32;
+          const float4* tile_part = reinterpret_cast<const float4*>(p.ws_partial) +
+                                    (static_cast<int64_t>(t) * p.splits * kEpiWarps + e) * (16 * 32) + lane;
           for (int s2 = 0; s2 < p.splits; ++s2) {  // fixed order: bit-stable result
+            const float4* src = tile_part + static_cast<int64_t>(s2) * (kEpiWarps * 16 * 32);
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-              const float4* src =
-                  reinterpret_cast<const float4*>(tile_part + static_cast<int64_t>(s2) * (kBM * kBN) + c * (kBM * 32));
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                float4 v = __ldcg(src + j);
-                acc[32 * c + 4 * j] += v.x;
-                acc[32 * c + 4 * j + 1] += v.y;
-                acc[32 * c + 4 * j + 2] += v.z;
-                acc[32 * c + 4 * j + 3] += v.w;
-              }
+            for (int j = 0; j < 16; ++j) {
+              const float4 v = __ldcg(src + j * 32);
+              acc[4 * j] += v.x;
+              acc[4 * j + 1] += v.y;
+              acc[4 * j + 2] += v.z;
+              acc[4 * j + 3] += v.w;
             }
           }
-          if (row_ok) {
+          TG_BS_STAMP2(4);
+          if (tma_out) {
+            stage_and_store64(&tmC, my_stage, lane, acc, p.out_dtype, col0, row0, p.M, p.N);
+          } else if (row_ok) {
             epilogue_store32(p, row, col0, acc, 1.0f, vec_ok);
             epilogue_store32(p, row, col0 + 32, acc + 32, 1.0f, vec_ok);
           }
+          TG_BS_STAMP2(5);
         }
       }
+#ifdef TG_TRACE
+      stamped2 = true;
+#endif
     }
+    if (tma_out && lane == 0) tma_store_wait_all<0>();  // this warp's bulk stores have completed
   }
 
   __syncwarp();
@@ -290,8 +316,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 
 }  // namespace
 
-cudaError_t launch_gemm_blockscaled(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
-                                    int num_sms, cudaStream_t stream) {
+cudaError_t launch_gemm_blockscaled(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap* tmC,
+                                    const GemmParams& p, int num_sms, cudaStream_t stream) {
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -303,7 +329,9 @@ cudaError_t launch_gemm_blockscaled(const CUtensorMap& tmA, const CUtensorMap& t
   }
   const int units = p.tiles_m * p.tiles_n * p.splits;
   const int grid = units < num_sms ? units : num_sms;
-  tg_fp8_gemm_blockscaled_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmB, p);
+  // tmC == nullptr selects the register -> global store epilogue (fp32 output or unaligned rows)
+  tg_fp8_gemm_blockscaled_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmC != nullptr ? *tmC : tmA, p,
+                                                                         tmC != nullptr ? 1 : 0);
   return cudaGetLastError();
 }
 

@@ -16,12 +16,12 @@ namespace tg {
 namespace {
 
 // Debug aid (compile with -DTG_TRACE): CTA 0 stamps %globaltimer at the steps of its first 256 k-blocks into
-// the partial-sum area of the workspace as [k-block][8] uint64 (0-2 MMA warp, 3-6 first promotion warp).
+// the partial-sum area of the workspace, 40 MiB in, as [k-block][8] uint64 (0-2 MMA warp, 3-6 first promotion warp).
 #ifdef TG_TRACE
 #define TG_BSW_STAMP(i, slot)                                                                      \
   do {                                                                                             \
     if (blockIdx.x == 0 && (i) < 256 && p.ws_partial != nullptr)                                   \
-      reinterpret_cast<unsigned long long*>(p.ws_partial)[(i) * 8 + (slot)] = globaltimer_ns();   \
+      (reinterpret_cast<unsigned long long*>(p.ws_partial) + (5u << 20))[(i) * 8 + (slot)] = globaltimer_ns();   \
   } while (0)
 #else
 #define TG_BSW_STAMP(i, slot) \

@@ -160,6 +160,36 @@ __device__ __forceinline__ void epilogue_store32(const GemmParams& p, int64_t ro
   }
 }
 
+// Bulk-store epilogue of one warp for two-byte outputs: the warp's 32 rows x 64 columns (v[0..64) of this
+// lane's row) are converted, written to the warp's 4 KB staging buffer in the 128-byte-swizzle layout and
+// sent with one bulk tensor store, which clips rows >= M and columns >= N.  `stage` must be 1024-byte
+// aligned; the previous store out of it is waited for (its shared-memory reads only) before it is refilled.
+__device__ __forceinline__ void stage_and_store64(const CUtensorMap* tmC, uint8_t* stage, int lane, const float* v,
+                                                  int out_dtype, int col, int row0, int M, int N) {
+  uint4 o[8];
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    if (out_dtype == TG_BF16) {
+      o[g] = make_uint4(pack_bf16x2(v[8 * g], v[8 * g + 1]), pack_bf16x2(v[8 * g + 2], v[8 * g + 3]),
+                        pack_bf16x2(v[8 * g + 4], v[8 * g + 5]), pack_bf16x2(v[8 * g + 6], v[8 * g + 7]));
+    } else {
+      o[g] = make_uint4(pack_f16x2(v[8 * g], v[8 * g + 1]), pack_f16x2(v[8 * g + 2], v[8 * g + 3]),
+                        pack_f16x2(v[8 * g + 4], v[8 * g + 5]), pack_f16x2(v[8 * g + 6], v[8 * g + 7]));
+    }
+  }
+  if (lane == 0) tma_store_wait_read<0>();
+  __syncwarp();
+  uint8_t* dst_row = stage + lane * 128;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) *reinterpret_cast<uint4*>(dst_row + ((g ^ (lane & 7)) << 4)) = o[g];
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0 && col < N && row0 < M) {
+    tma_store_2d(tmC, smem_u32(stage), col, row0);
+    tma_store_commit();
+  }
+}
+
 // Split-K arrival: after a warp has written its partial results and fenced,
 // lane 0 bumps the counter of its (tile, slice); the warp that brings it to
 // `splits` is the last one, resets the counter for the next call and reduces.

@@ -57,8 +57,9 @@ int pertensor_2cta_tail_div(int tiles, int num_sms);
 cudaError_t launch_gemm_pertensor_2cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmBt,
                                        const CUtensorMap* out_maps, int num_out, const GemmParams& p, int group_m,
                                        int tail_div, int num_sms, cudaStream_t stream);
-cudaError_t launch_gemm_blockscaled(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
-                                    int num_sms, cudaStream_t stream);
+// tmC as for the wide-tile kernel below (nullptr: register -> global stores).
+cudaError_t launch_gemm_blockscaled(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap* tmC,
+                                    const GemmParams& p, int num_sms, cudaStream_t stream);
 // Wide-tile block-scaled kernel: 128 x 256 tiles (tmB boxes 256 rows, p.tiles_n counts 256-wide tiles), no split-K.
 // tmC: tensor map of the output (two-byte elements, box 64 x 32, 128-byte swizzle) for the bulk-store epilogue,
 // or nullptr for register -> global stores (fp32 output, unaligned rows).
