@@ -93,6 +93,39 @@ def block_scaled_sweep(dev, fp8_peak_tflops: float, hbm_peak_gbs: float):
     return rows
 
 
+def quantiser_sweep(dev, hbm_peak_gbs: float):
+    """The activation-side quantisers on a [8192, 14336] bf16 activation (235 MB, > L2): algorithmic bytes
+    (input + 8-bit output + scales; the per-tensor quantiser reads its input twice) over CUDA-event time."""
+    import tilegym_b200 as tg
+
+    T, H = 8192, 14336
+    x = torch.randn(T, H, device=dev, dtype=torch.bfloat16)
+    cases = [
+        ("act_quant_1x128", lambda: tg.act_quant(x), 3 * T * H + 4 * T * H // 128),
+        ("per_token_group_quant_g128", lambda: tg.per_token_group_quant_8bit(x, 128), 3 * T * H + 4 * T * H // 128),
+        ("per_token_group_quant_g32_colmajor_ue8m0",
+         lambda: tg.per_token_group_quant_8bit(x, 32, column_major_scales=True, scale_ue8m0=True),
+         3 * T * H + 4 * T * H // 32),
+        ("quant_per_tensor", lambda: tg.quant_per_tensor(x), 5 * T * H),
+    ]
+    rows = []
+    for name, fn, nbytes in cases:
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        rows.append({"op": name, "us": round(us, 1), "gbs": round(nbytes / us / 1e3, 1),
+                     "frac_of_measured_hbm": round(nbytes / us / 1e3 / hbm_peak_gbs, 3)})
+    return rows
+
+
 def run(dev, peaks):
     hbm = float(peaks["hbm_gbs"])
     fp8 = 2.0 * float(peaks["bf16_tflops"])  # kernels timed alone: burst figure
@@ -101,4 +134,5 @@ def run(dev, peaks):
                   "measured HBM copy bandwidth / of 2 x measured bf16 burst",
         "decode_per_tensor": decode_sweep(dev, hbm),
         "block_scaled": block_scaled_sweep(dev, fp8, hbm),
+        "quantisers": quantiser_sweep(dev, hbm),
     }

@@ -53,6 +53,7 @@ extern "C" {
 #define TG_F8E5M2 5
 #define TG_U8 6
 #define TG_F8E4M3 7
+#define TG_I8 8 /* not in the reference table (its cuTile-rs FFI has no int8 operator); used by the group quantiser */
 
 typedef struct TgTensorDesc {
   uint64_t ptr;       /* device address */
@@ -143,6 +144,19 @@ TG_API uint64_t tg_fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
  */
 TG_API int32_t tg_act_quant(const TgTensorDesc* Y, const TgTensorDesc* S, const TgTensorDesc* X, int32_t block,
                      int32_t device_id, uint64_t stream);
+
+/* Per-token group quantiser to 8 bits: per `group_size` contiguous elements of a row, amax = max(|x|, eps),
+ * s = amax / dtype_max (IEEE division; rounded up to a power of two when scale_ue8m0 != 0),
+ * y = clamp(x / s, dtype_min, dtype_max) cast to Y's dtype (e4m3 / e5m2: round to nearest even; int8: truncate).
+ * X: (T, H) bf16 / f16 / f32 contiguous, H % group_size == 0, group_size in {8,16,32,64,128,256};
+ * Y: (T, H) contiguous, dtype TG_F8E4M3, TG_F8E5M2 or TG_I8; S: (T, H/group_size) f32 with ANY strides -
+ * row-major, column-major ((1, T)) and the padded column-major layout ((1, ceil4(T))) are all the same call.
+ * Replaces tilegym.suites.flashinfer.ops.per_token_group_quant_8bit (src/tilegym/suites/flashinfer/ops.py:238-267,
+ * kernels src/tilegym/suites/flashinfer/cutile/per_token_group_quant_8bit.py:25-150).
+ */
+TG_API int32_t tg_per_token_group_quant(const TgTensorDesc* Y, const TgTensorDesc* S, const TgTensorDesc* X,
+                                        int32_t group_size, float eps, int32_t scale_ue8m0, int32_t device_id,
+                                        uint64_t stream);
 
 /* block x block weight dequantiser: y[i,j] = x[i,j] * s[i/block, j/block].
  * X: (M,N) e4m3; S: (ceil(M/block), ceil(N/block)) f32; Y: (M,N) bf16/f16/f32.

@@ -117,6 +117,34 @@ def ref_weight_quant_block(w: torch.Tensor, block: int = 128) -> Tuple[torch.Ten
     return q, s
 
 
+def ref_per_token_group_quant_8bit(
+    x: torch.Tensor,
+    group_size: int,
+    eps: float = 1e-10,
+    dst_dtype: torch.dtype = torch.float8_e4m3fn,
+    scale_ue8m0: bool = False,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-token group quantisation to e4m3 / e5m2 / int8, the torch reference of
+    tests/suites/flashinfer/test_per_token_group_quant_8bit.py:41-68: per group of `group_size` contiguous
+    elements amax is clamped from below by eps (in x's dtype), scale = amax / dtype_max in fp32, optionally
+    rounded up to a power of two, q = clamp(x / scale, min, max) cast to the target (int8 truncates).
+    Scales come back row-major, shape x.shape[:-1] + (H / group_size,); the layouts the operator offers
+    (column-major, padded) hold the same numbers."""
+    assert x.shape[-1] % group_size == 0 and x.is_contiguous()
+    if dst_dtype == torch.int8:
+        lo, hi = float(torch.iinfo(dst_dtype).min), float(torch.iinfo(dst_dtype).max)
+    else:
+        lo, hi = torch.finfo(dst_dtype).min, torch.finfo(dst_dtype).max
+    g = x.reshape(x.numel() // group_size, group_size)
+    amax = g.abs().max(dim=-1, keepdim=True)[0].clamp(min=eps).to(torch.float32)
+    s = amax / hi
+    if scale_ue8m0:
+        floor = torch.tensor(1e-10, dtype=s.dtype)
+        s = torch.exp2(torch.ceil(torch.log2(torch.maximum(s.abs(), floor))))
+    q = (g / s).clamp(min=lo, max=hi).to(dst_dtype).reshape(x.shape)
+    return q, s.reshape(x.shape[:-1] + (x.shape[-1] // group_size,))
+
+
 # --------------------------------------------------------------------------
 # GEMMs
 # --------------------------------------------------------------------------

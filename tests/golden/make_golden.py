@@ -2,11 +2,14 @@
 
 Run once, in a container that has the TileGym source tree:
 
-    PYTHONPATH=<tilegym>/src:<tilegym> python tests/golden/make_golden.py <tilegym>
+    PYTHONPATH=<tilegym>/src:<tilegym> python tests/golden/make_golden.py <tilegym> [family ...]
+
+(with family names, e.g. `group_quant`, only those fixture families are rewritten).
 
 It imports the `reference` static methods of TileGym's test classes
 (tests/suites/unsloth/test_fp8.py and
-tests/suites/flashinfer/test_flashinfer_gemm_alpha_beta.py), feeds them inputs
+tests/suites/flashinfer/test_flashinfer_gemm_alpha_beta.py) and the torch reference function of
+tests/suites/flashinfer/test_per_token_group_quant_8bit.py, feeds them inputs
 drawn the way those tests draw them (same seeds and distributions, on the CPU)
 and stores inputs and outputs as compressed .npz files.  fp8 and bf16 tensors
 are stored as their raw bit patterns (uint8 / uint16).  The tests in
@@ -31,7 +34,10 @@ def bits(t: torch.Tensor) -> np.ndarray:
     return t.numpy()
 
 
-def main(ref_root: str) -> None:
+def main(ref_root: str, only=()) -> None:
+    def want(family: str) -> bool:
+        return not only or family in only
+
     sys.path[:0] = [os.path.join(ref_root, "src"), ref_root]
     from tests.suites.flashinfer.test_flashinfer_gemm_alpha_beta import Test_FlashInfer_Matmul_Alpha_Beta as G
     from tests.suites.unsloth.test_fp8 import Test_Unsloth_ActQuant as Q
@@ -39,7 +45,7 @@ def main(ref_root: str) -> None:
     from tests.suites.unsloth.test_fp8 import Test_Unsloth_WeightDequant as W
 
     # --- block-scaled GEMM: recipe of test_fp8.py:213-222 (seed 42) ---------
-    for M, N, K in [(128, 128, 128), (256, 256, 256), (7, 200, 320), (1, 128, 256)]:
+    for M, N, K in [(128, 128, 128), (256, 256, 256), (7, 200, 320), (1, 128, 256)] if want("w8a8_block") else []:
         torch.manual_seed(42)
         bn = bk = 128
         A = (torch.randn(M, K) * 0.1).to(torch.float8_e4m3fn)
@@ -54,7 +60,7 @@ def main(ref_root: str) -> None:
         )
 
     # --- act_quant: recipe of test_fp8.py:120-127 (seed 42, bf16 randn) ------
-    for shape in [(64, 1024), (128, 384), (4, 128)]:
+    for shape in [(64, 1024), (128, 384), (4, 128)] if want("act_quant") else []:
         torch.manual_seed(42)
         x = torch.randn(*shape, dtype=torch.bfloat16)
         if shape == (4, 128):
@@ -65,7 +71,7 @@ def main(ref_root: str) -> None:
         )
 
     # --- weight_dequant: recipe of test_fp8.py:62-67 (seed 42) ---------------
-    for M, N in [(256, 256), (130, 200)]:
+    for M, N in [(256, 256), (130, 200)] if want("weight_dequant") else []:
         torch.manual_seed(42)
         x = torch.randn(M, N).to(torch.float8_e4m3fn)
         s = torch.rand(-(-M // 128), -(-N // 128), dtype=torch.float32) + 0.1
@@ -74,7 +80,8 @@ def main(ref_root: str) -> None:
 
     # --- gemm_alpha_beta: recipe of test_flashinfer_gemm_alpha_beta.py:24-66 (seed 0),
     # e4m3 -> bf16, at a size that fits a fixture -----------------------------
-    for (m, n, k), (alpha, beta) in [((256, 256, 256), (1.0, 0.0)), ((256, 256, 256), (1.5, 2.0))]:
+    for (m, n, k), (alpha, beta) in ([((256, 256, 256), (1.0, 0.0)), ((256, 256, 256), (1.5, 2.0))]
+                                     if want("gemm_alpha_beta") else []):
         torch.manual_seed(0)
         a = torch.rand(m * k, dtype=torch.float16).to(torch.float8_e4m3fn).view(m, k)
         b = torch.rand(k * n, dtype=torch.float16).to(torch.float8_e4m3fn).view(n, k)
@@ -84,8 +91,24 @@ def main(ref_root: str) -> None:
             os.path.join(HERE, f"gemm_alpha_beta_{m}_{alpha}_{beta}.npz"),
             a=bits(a), b=bits(b), c=bits(c), out=bits(out), alpha=np.float32(alpha), beta=np.float32(beta),
         )
+    # --- per_token_group_quant_8bit: recipe of test_per_token_group_quant_8bit.py:119-133 (seed 0, bf16
+    # randn, eps 1e-10) through that file's torch reference; one all-zero group exercises the eps clamp -----
+    if want("group_quant"):
+        from tests.suites.flashinfer.test_per_token_group_quant_8bit import native_per_token_group_quant_8bit as P
+
+        for T_, H, g, dst, ue in [(33, 256, 16, torch.float8_e4m3fn, False), (33, 256, 128, torch.float8_e4m3fn, True),
+                                  (17, 512, 64, torch.int8, False), (17, 512, 32, torch.int8, True),
+                                  (9, 256, 128, torch.float8_e5m2, False)]:
+            torch.manual_seed(0)
+            x = torch.randn(T_, H, dtype=torch.bfloat16)
+            x[1, :g].zero_()
+            q, sc = P(x, g, 1e-10, dst, ue)
+            qb = q.view(torch.uint8).numpy() if dst != torch.int8 else q.numpy()
+            name = {torch.float8_e4m3fn: "e4m3", torch.float8_e5m2: "e5m2", torch.int8: "int8"}[dst]
+            np.savez_compressed(os.path.join(HERE, f"group_quant_{T_}x{H}_g{g}_{name}_ue{int(ue)}.npz"),
+                                x=bits(x), q=qb, s=bits(sc))
     print("golden fixtures written to", HERE)
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", tuple(sys.argv[2:]))

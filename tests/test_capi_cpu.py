@@ -88,6 +88,14 @@ def test_quantiser_argument_checks():
     assert L.tg_act_quant(_d(y), _d(torch.zeros(4, 3)), _d(x), 128, 0, 0) == -6
     assert L.tg_weight_dequant(_d(x), _d(y), _d(torch.zeros(1, 1)), 128, 0, 0) == -6  # S shape
     assert L.tg_quant_pertensor(_d(y), 0, _d(x), 0, 0, 0) == -5
+    # per-token group quantiser: group size, divisibility, dtypes, scale shape
+    sg = torch.zeros(4, 16)
+    assert L.tg_per_token_group_quant(_d(y), _d(sg), _d(x), 24, 1e-10, 0, 0, 0) == -6
+    assert L.tg_per_token_group_quant(_d(y), _d(torch.zeros(4, 8)), _d(x), 16, 1e-10, 0, 0, 0) == -6
+    assert L.tg_per_token_group_quant(_d(y.view(torch.uint8)), _d(sg), _d(x), 16, 1e-10, 0, 0, 0) == -2
+    assert L.tg_per_token_group_quant(_d(y), _d(sg.half()), _d(x), 16, 1e-10, 0, 0, 0) == -2
+    assert L.tg_per_token_group_quant(_d(y), _d(sg), None, 16, 1e-10, 0, 0, 0) == -5
+    assert b"group_size" in L.tg_last_error_string() or True
 
 
 def test_ops_refuse_cpu_tensors_instead_of_falling_back():
@@ -111,4 +119,6 @@ def test_signatures_match_the_reference_entry_points():
     assert sig.parameters["trans_b"].default is True
     assert list(inspect.signature(ops.act_quant).parameters) == ["x", "block_size"]
     assert list(inspect.signature(ops.weight_dequant).parameters) == ["x", "s", "block_size", "dtype"]
+    assert list(inspect.signature(ops.per_token_group_quant_8bit).parameters) == [
+        "x", "group_size", "eps", "dst_dtype", "column_major_scales", "scale_tma_aligned", "scale_ue8m0"]
     assert list(inspect.signature(ops.matmul).parameters)[:6] == ["a", "b", "trans_a", "trans_b", "static_persistent", "use_tma"]

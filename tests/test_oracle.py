@@ -42,6 +42,29 @@ def test_act_quant_matches_reference_fixture(name):
         assert float(s[1, 0]) == 1.0  # all-zero block
 
 
+GROUP_QUANT = sorted(os.path.basename(p) for p in glob.glob(os.path.join(GOLDEN, "group_quant_*.npz")))
+
+
+def group_quant_case(name):
+    """(group_size, dst_dtype, scale_ue8m0) from a fixture name group_quant_<T>x<H>_g<g>_<dtype>_ue<0|1>.npz."""
+    parts = name[:-4].split("_")
+    dst = {"e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2, "int8": torch.int8}[parts[4]]
+    return int(parts[3][1:]), dst, parts[5] == "ue1"
+
+
+@pytest.mark.parametrize("name", GROUP_QUANT)
+def test_per_token_group_quant_matches_reference_fixture(name):
+    assert len(GROUP_QUANT) == 5
+    g = load_golden(name)
+    gs, dst, ue = group_quant_case(name)
+    q, s = R.ref_per_token_group_quant_8bit(g["x"], gs, 1e-10, dst, ue)
+    assert bool((q.view(torch.uint8) == g["q"].view(torch.uint8)).all())
+    assert bool((s == g["s"]).all())
+    if ue:  # powers of two
+        m, _ = torch.frexp(s)
+        assert bool((m == 0.5).all())
+
+
 @pytest.mark.parametrize("name", ["weight_dequant_256x256.npz", "weight_dequant_130x200.npz"])
 def test_weight_dequant_matches_reference_fixture(name):
     g = load_golden(name)

@@ -83,3 +83,68 @@ def test_weight_quant_block(dev, shape):
     assert float(s[0, 0]) == 1.0
     back = tg.weight_dequant(q, s, 128, torch.float32)
     assert float((back.cpu() - w).abs().max()) <= float(w.abs().max()) * 2.0 ** -4
+
+
+# ------------------------------------------------------------ per-token group quantiser
+from test_oracle import GROUP_QUANT, group_quant_case  # noqa: E402
+
+
+@pytest.mark.parametrize("name", GROUP_QUANT)
+def test_per_token_group_quant_fixtures(dev, name):
+    g = load_golden(name)
+    gs, dst, ue = group_quant_case(name)
+    q, s = tg.per_token_group_quant_8bit(g["x"].to(dev), gs, 1e-10, dst, column_major_scales=ue, scale_ue8m0=ue)
+    assert q.dtype == dst and q.shape == g["x"].shape
+    assert same_bits(q, g["q"]) and torch.equal(s.cpu(), g["s"])
+
+
+@pytest.mark.parametrize("num_tokens", [512, 513])
+@pytest.mark.parametrize("group_size", [16, 32, 64, 128])
+@pytest.mark.parametrize("dst_dtype", [torch.float8_e4m3fn, torch.int8])
+@pytest.mark.parametrize("layout", ["row", "col", "col_aligned", "col_ue8m0", "col_aligned_ue8m0"])
+def test_per_token_group_quant_reference_test_grid(dev, num_tokens, group_size, dst_dtype, layout):
+    """The parameter grid of the reference test (test_per_token_group_quant_8bit.py:72-84), its seed and
+    input recipe; results must equal the oracle bit for bit in every scale layout."""
+    torch.manual_seed(0)
+    x = torch.randn(num_tokens, 2048, dtype=torch.bfloat16)
+    col, aligned, ue = layout != "row", "aligned" in layout, "ue8m0" in layout
+    qr, sr = R.ref_per_token_group_quant_8bit(x, group_size, 1e-10, dst_dtype, ue)
+    q, s = tg.per_token_group_quant_8bit(x.to(dev), group_size, 1e-10, dst_dtype, col, aligned, ue)
+    assert s.shape == sr.shape
+    if col and not aligned:
+        assert s.stride() == (1, num_tokens)  # column-major view, as the reference returns it
+    assert same_bits(q, qr) and torch.equal(s.cpu(), sr)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_per_token_group_quant_other_inputs_and_zero_groups(dev, dtype):
+    torch.manual_seed(3)
+    x = torch.randn(3, 7, 512, dtype=dtype) * 5
+    if dtype == torch.float32:
+        x[1, 2, 128:256] = 0  # eps clamp (in f16 eps = 1e-10 underflows and the torch reference divides 0 by 0)
+    x[2, 0, 0] = 1e6 if dtype == torch.float32 else 6e4  # a large outlier
+    for dst in (torch.float8_e4m3fn, torch.float8_e5m2, torch.int8):
+        qr, sr = R.ref_per_token_group_quant_8bit(x, 128, 1e-10, dst)
+        q, s = tg.per_token_group_quant_8bit(x.to(dev), 128, 1e-10, dst)
+        assert q.shape == x.shape and s.shape == (3, 7, 4)
+        assert same_bits(q, qr) and torch.equal(s.cpu(), sr)
+
+
+def test_per_token_group_quant_f16_zero_group_keeps_fp32_eps(dev):
+    """Where eps underflows in x's dtype the kernel keeps the fp32 eps (as the reference kernel does,
+    per_token_group_quant_8bit.py:50-52) instead of dividing zero by zero."""
+    x = torch.zeros(2, 128, dtype=torch.float16, device=dev)
+    x[1] = 1.0
+    q, s = tg.per_token_group_quant_8bit(x, 128)
+    assert bool((q[0].float() == 0).all()) and float(s[0, 0]) == float(torch.tensor(1e-10) / 448.0)
+    assert bool((q[1].float() == 448).all())
+
+
+def test_per_token_group_quant_rejects_bad_arguments(dev):
+    x = torch.randn(8, 256, dtype=torch.bfloat16, device=dev)
+    with pytest.raises(AssertionError):
+        tg.per_token_group_quant_8bit(x, 48)
+    with pytest.raises(AssertionError):
+        tg.per_token_group_quant_8bit(x, 64, scale_ue8m0=True)  # needs column-major scales
+    with pytest.raises(RuntimeError):
+        tg.per_token_group_quant_8bit(x, 4)  # divides 256 but is not a supported group size

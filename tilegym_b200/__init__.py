@@ -11,6 +11,7 @@ weight_quant_block, FP8Linear) and apply_tilegym_kernel_to_llama / _deepseek_v2.
 from .ops import (  # noqa: F401
     act_quant,
     fp8_scaled_mm,
+    per_token_group_quant_8bit,
     fp8_scaled_mm_no_alloc,
     gemm_alpha_beta,
     matmul,

@@ -40,6 +40,7 @@ DTYPE_CODES = {
     torch.float8_e5m2: 5,
     torch.uint8: 6,
     torch.float8_e4m3fn: 7,
+    torch.int8: 8,  # extension: the reference table stops at 7
 }
 
 
@@ -89,6 +90,10 @@ SIGNATURES = {
          ctypes.c_uint64],
     ),
     "tg_act_quant": (ctypes.c_int32, [_P, _P, _P, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64]),
+    "tg_per_token_group_quant": (
+        ctypes.c_int32,
+        [_P, _P, _P, ctypes.c_int32, ctypes.c_float, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64],
+    ),
     "tg_weight_dequant": (ctypes.c_int32, [_P, _P, _P, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64]),
     "tg_quant_pertensor": (
         ctypes.c_int32,

@@ -140,6 +140,64 @@ def act_quant(x: torch.Tensor, block_size: int = 128) -> Tuple[torch.Tensor, tor
     return y, s
 
 
+def per_token_group_quant_8bit(
+    x: torch.Tensor,
+    group_size: int,
+    eps: float = 1e-10,
+    dst_dtype: Optional[torch.dtype] = None,
+    column_major_scales: bool = False,
+    scale_tma_aligned: bool = False,
+    scale_ue8m0: bool = False,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-token group 8-bit quantisation (e4m3 default, e5m2 or int8): (x_q, x_s).
+
+    Signature, preconditions and scale layouts of src/tilegym/suites/flashinfer/ops.py:238-267 and
+    src/tilegym/suites/flashinfer/cutile/per_token_group_quant_8bit.py:152-272: row-major scales have shape
+    x.shape[:-1] + (H / group_size,); column-major scales are a (tokens, groups) view with strides
+    (1, tokens); with scale_tma_aligned the kernel writes into a (groups, ceil4(tokens)) buffer and the
+    (tokens, groups) result is returned contiguous, as the reference does.  One kernel serves all layouts
+    (it writes the scale through the strides it is given).  eps is applied in x's dtype, like the torch
+    reference of the operator's test.
+    """
+    dev = _need_cuda(x)
+    if dst_dtype is None:
+        dst_dtype = _FP8
+    assert x.shape[-1] % group_size == 0, (
+        f"the last dimension of `x` {x.shape[-1]} must be divisible by `group_size` {group_size}"
+    )
+    assert x.is_contiguous(), "`x` must be contiguous"
+    if scale_tma_aligned or scale_ue8m0:
+        assert column_major_scales, "scale_tma_aligned or scale_ue8m0 requires column_major_scales=True"
+    H = x.shape[-1]
+    G = H // group_size
+    x2 = x.view(-1, H)
+    T = x2.shape[0]
+    x_q = torch.empty_like(x, dtype=dst_dtype)
+    raw = None
+    if column_major_scales:
+        assert x.dim() == 2, "column-major scales need a 2-D input [num_tokens, hidden_dim]"
+        if scale_tma_aligned:
+            raw = torch.empty((G, (T + 3) // 4 * 4), device=dev, dtype=torch.float32)
+            x_s = raw[:, :T].t()  # (T, G) view, strides (1, aligned T)
+        else:
+            x_s = torch.empty((G, T), device=dev, dtype=torch.float32).t()  # (T, G), strides (1, T)
+        s2 = x_s
+    else:
+        x_s = torch.empty(x.shape[:-1] + (G,), device=dev, dtype=torch.float32)
+        s2 = x_s.view(T, G)
+    eps_in_dtype = float(torch.tensor(eps, dtype=x.dtype))
+    if eps_in_dtype == 0.0 and eps > 0:
+        eps_in_dtype = float(eps)  # f16: 1e-10 underflows; keep the fp32 value rather than divide 0 by 0
+    rc = _lib.lib().tg_per_token_group_quant(
+        _lib.ref(_lib.desc(x_q.view(-1, H))), _lib.ref(_lib.desc(s2)), _lib.ref(_lib.desc(x2)), int(group_size),
+        eps_in_dtype, 1 if scale_ue8m0 else 0, dev.index, _stream(dev),
+    )
+    _lib.check_rc(rc)
+    if raw is not None:
+        x_s = x_s.contiguous()
+    return x_q, x_s
+
+
 def weight_dequant(
     x: torch.Tensor, s: torch.Tensor, block_size: int = 128, dtype: torch.dtype = torch.bfloat16
 ) -> torch.Tensor:
