@@ -148,7 +148,7 @@ TG_API int32_t tg_act_quant(const TgTensorDesc* Y, const TgTensorDesc* S, const 
 /* Per-token group quantiser to 8 bits: per `group_size` contiguous elements of a row, amax = max(|x|, eps),
  * s = amax / dtype_max (IEEE division; rounded up to a power of two when scale_ue8m0 != 0),
  * y = clamp(x / s, dtype_min, dtype_max) cast to Y's dtype (e4m3 / e5m2: round to nearest even; int8: truncate).
- * X: (T, H) bf16 / f16 / f32 contiguous, H % group_size == 0, group_size in {8,16,32,64,128,256};
+ * X: (T, H) bf16 / f16 / f32 contiguous, H % group_size == 0, group_size in {8,16,32,64,128,256,512};
  * Y: (T, H) contiguous, dtype TG_F8E4M3, TG_F8E5M2 or TG_I8; S: (T, H/group_size) f32 with ANY strides -
  * row-major, column-major ((1, T)) and the padded column-major layout ((1, ceil4(T))) are all the same call.
  * Replaces tilegym.suites.flashinfer.ops.per_token_group_quant_8bit (src/tilegym/suites/flashinfer/ops.py:238-267,

@@ -130,6 +130,25 @@ def test_per_token_group_quant_other_inputs_and_zero_groups(dev, dtype):
         assert same_bits(q, qr) and torch.equal(s.cpu(), sr)
 
 
+@pytest.mark.parametrize("dst", [torch.float8_e4m3fn, torch.float8_e5m2, torch.int8])
+def test_quantisers_equal_ieee_division_on_16m_elements(dev, dst):
+    """The kernels divide through a shared reciprocal plus a guarded correction; over 16.8 M elements with row
+    magnitudes spread over 12 decades the bytes must still equal the oracle's x / s."""
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(4096, 4096, generator=g) * torch.logspace(-6, 6, 4096).unsqueeze(1)
+    x = x.to(torch.bfloat16)
+    qr, sr = R.ref_per_token_group_quant_8bit(x, 64, 1e-10, dst)
+    q, s = tg.per_token_group_quant_8bit(x.to(dev), 64, 1e-10, dst)
+    assert torch.equal(s.cpu(), sr) and same_bits(q, qr)
+    if dst == torch.float8_e4m3fn:
+        yr, s2r = R.ref_act_quant(x)
+        y, s2 = tg.act_quant(x.to(dev))
+        assert torch.equal(s2.cpu(), s2r) and same_bits(y, yr)
+        pr, psr = R.ref_quant_per_tensor(x)
+        pq, ps = tg.quant_per_tensor(x.to(dev))
+        assert torch.equal(ps.cpu(), psr) and same_bits(pq, pr)
+
+
 def test_per_token_group_quant_f16_zero_group_keeps_fp32_eps(dev):
     """Where eps underflows in x's dtype the kernel keeps the fp32 eps (as the reference kernel does,
     per_token_group_quant_8bit.py:50-52) instead of dividing zero by zero."""
@@ -148,3 +167,6 @@ def test_per_token_group_quant_rejects_bad_arguments(dev):
         tg.per_token_group_quant_8bit(x, 64, scale_ue8m0=True)  # needs column-major scales
     with pytest.raises(RuntimeError):
         tg.per_token_group_quant_8bit(x, 4)  # divides 256 but is not a supported group size
+    q, s = tg.per_token_group_quant_8bit(x, 8)  # the smallest supported group
+    qr, sr = R.ref_per_token_group_quant_8bit(x.cpu(), 8)
+    assert same_bits(q, qr) and torch.equal(s.cpu(), sr)

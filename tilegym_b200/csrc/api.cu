@@ -568,7 +568,7 @@ int32_t tg_act_quant(const TgTensorDesc* Y, const TgTensorDesc* S, const TgTenso
   if (numel(Y) != n || numel(S) != n / block) return fail(TG_ERR_ARGS, "Y / S sizes do not match X");
   if (n == 0) return TG_OK;
   if (X->ptr == 0 || Y->ptr == 0 || S->ptr == 0) return fail(TG_ERR_NULL, "data pointer is null");
-  if ((X->ptr & 15u) || (Y->ptr & 3u) || (S->ptr & 3u)) return fail(TG_ERR_ALIGN, "X must be 16-byte, Y and S 4-byte aligned");
+  if ((X->ptr & 15u) || (Y->ptr & 15u) || (S->ptr & 3u)) return fail(TG_ERR_ALIGN, "X and Y must be 16-byte, S 4-byte aligned");
   DeviceGuard guard(device_id);
   if (guard.err != cudaSuccess) {
     cudaGetLastError();

@@ -1,7 +1,7 @@
 // Per-token group quantiser to 8 bits (e4m3, e5m2 or int8): the activation-side producer in front of an
 // FP8 GEMM when the group is not the fixed 1 x 128 block of tg_act_quant.  One streaming pass, HBM-bound
-// (bf16 in: 3 bytes per element): every thread owns 8 consecutive elements (one 16-byte load for bf16 / f16),
-// the group_size / 8 lanes of a group reduce |x| with shuffles, and one lane writes the scale through the
+// (bf16 in: 3 bytes per element): every thread owns 16 consecutive elements (two 16-byte loads for bf16 / f16),
+// the group_size / 16 lanes of a group reduce |x| with shuffles, and one lane writes the scale through the
 // caller's strides, which covers the row-major, column-major and padded column-major scale layouts alike.
 // Arithmetic follows tests/suites/flashinfer/test_per_token_group_quant_8bit.py:41-68 (the torch reference
 // of src/tilegym/suites/flashinfer/cutile/per_token_group_quant_8bit.py:152-272): amax clamped from below by
@@ -13,36 +13,41 @@
 
 #include <cstdio>
 
+#include <type_traits>
+
 #include "tg_internal.h"
+#include "tg_quant_common.cuh"
 
 namespace tg {
 namespace {
 
-enum DstKind : int { kE4M3 = 0, kE5M2 = 1, kInt8 = 2 };
-
-template <typename T>
-__device__ __forceinline__ void load8(const T* src, float (&v)[8]) {
+// EPT consecutive elements (8 or 16) as fp32; streaming loads (the input is read once).
+template <typename T, int EPT>
+__device__ __forceinline__ void load_elems(const T* src, float (&v)[EPT]) {
   if constexpr (sizeof(T) == 4) {
-    const float4 a = __ldcs(reinterpret_cast<const float4*>(src));
-    const float4 b = __ldcs(reinterpret_cast<const float4*>(src) + 1);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-  } else {
-    const uint4 t = __ldcs(reinterpret_cast<const uint4*>(src));
-    const T* e = reinterpret_cast<const T*>(&t);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if constexpr (sizeof(T) == 2 && std::is_same<T, __half>::value) v[j] = __half2float(e[j]);
-      else v[j] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(e)[j]);
+    for (int i = 0; i < EPT / 4; ++i) {
+      const float4 a = __ldcs(reinterpret_cast<const float4*>(src) + i);
+      v[4 * i] = a.x; v[4 * i + 1] = a.y; v[4 * i + 2] = a.z; v[4 * i + 3] = a.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < EPT / 8; ++i) {
+      const uint4 t = __ldcs(reinterpret_cast<const uint4*>(src) + i);
+      const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if constexpr (std::is_same<T, __half>::value) {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+          v[8 * i + 2 * j] = f.x;
+          v[8 * i + 2 * j + 1] = f.y;
+        } else {  // bf16 -> fp32 is a 16-bit shift
+          v[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
+          v[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        }
+      }
     }
   }
-}
-
-template <int KIND>
-__device__ __forceinline__ uint32_t to_8bit(float v) {
-  if constexpr (KIND == kE4M3) return static_cast<uint32_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
-  else if constexpr (KIND == kE5M2) return static_cast<uint32_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E5M2));
-  else return static_cast<uint32_t>(__float2int_rz(v)) & 0xffu;
 }
 
 // Smallest power of two >= max(|s|, 1e-10): ceil(log2) read off the exponent and mantissa bits, so the
@@ -54,67 +59,105 @@ __device__ __forceinline__ float round_up_pow2(float s) {
   return __uint_as_float(exp_bits);
 }
 
-// `tpg` = threads per group = group_size / 8 (1, 2, 4, 8, 16 or 32); groups never straddle a warp.
-template <typename T, int KIND>
+// Where group g's scale goes: row g / groups_per_row, column g % groups_per_row, through the caller's strides.
+// 64-bit division costs a few hundred instructions, so the common sizes take a 32-bit one.
+__device__ __forceinline__ int64_t scale_index(int64_t g, int64_t groups_per_row, int64_t row_stride,
+                                               int64_t group_stride) {
+  if (groups_per_row == 1) return g * row_stride;
+  if (g <= 0xffffffffll && groups_per_row <= 0xffffffffll) {
+    const uint32_t g32 = static_cast<uint32_t>(g), gpr = static_cast<uint32_t>(groups_per_row);
+    const uint32_t row = g32 / gpr;
+    return static_cast<int64_t>(row) * row_stride + static_cast<int64_t>(g32 - row * gpr) * group_stride;
+  }
+  const int64_t row = g / groups_per_row;
+  return row * row_stride + (g - row * groups_per_row) * group_stride;
+}
+
+// A thread owns a chunk of EPT consecutive elements; the `tpg` = group_size / EPT lanes (a power of two, at
+// most 32) that share a group sit next to each other in a warp.  `zero_to_one` selects the 1 x 128 activation
+// quantiser's rule (scale 1.0 for an all-zero group, no eps).
+template <typename T, int KIND, int EPT>
 __global__ void __launch_bounds__(256)
     tg_per_token_group_quant_kernel(uint8_t* __restrict__ y, float* __restrict__ s, const T* __restrict__ x,
                                     int64_t n_chunks, int tpg, int64_t groups_per_row, int64_t s_row_stride,
-                                    int64_t s_group_stride, float eps, float qmin, float qmax, int ue8m0) {
+                                    int64_t s_group_stride, float eps, float qmin, float qmax, int ue8m0,
+                                    int zero_to_one) {
   const int lane = threadIdx.x & 31;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int tpg_shift = 31 - __clz(tpg);
+  const int64_t span = static_cast<int64_t>(gridDim.x) * blockDim.x;
   // all lanes of a warp run the same number of iterations (the shuffles need them)
   for (int64_t base = static_cast<int64_t>(blockIdx.x) * blockDim.x + (threadIdx.x & ~31); base < n_chunks;
-       base += stride) {
+       base += span) {
     const int64_t c = base + lane;
     const bool live = c < n_chunks;
-    float v[8];
-    if (live) {
-      load8<T>(x + c * 8, v);
-    } else {
+    float v[EPT];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = 0.f;
-    }
+    for (int j = 0; j < EPT; ++j) v[j] = 0.f;
+    if (live) load_elems<T, EPT>(x + c * EPT, v);
     float amax = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    for (int j = 0; j < EPT; ++j) amax = fmaxf(amax, fabsf(v[j]));
     for (int o = tpg >> 1; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    amax = fmaxf(amax, eps);
-    float scale = __fdiv_rn(amax, qmax);
-    if (ue8m0) scale = round_up_pow2(scale);
-    uint32_t lo = 0, hi = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      lo |= to_8bit<KIND>(fminf(fmaxf(__fdiv_rn(v[j], scale), qmin), qmax)) << (8 * j);
-      hi |= to_8bit<KIND>(fminf(fmaxf(__fdiv_rn(v[4 + j], scale), qmin), qmax)) << (8 * j);
+    float scale;
+    if (zero_to_one) {
+      scale = __fdiv_rn(amax, qmax);
+      if (scale == 0.f) scale = 1.0f;
+    } else {
+      scale = __fdiv_rn(fmaxf(amax, eps), qmax);
+      if (ue8m0) scale = round_up_pow2(scale);
     }
+    const bool tame = q8_scale_is_tame(scale);
+    const float r = __frcp_rn(scale);
+    uint32_t out[EPT / 4];
+#pragma unroll
+    for (int w = 0; w < EPT / 4; ++w)
+      out[w] = q8_pair<KIND>(v[4 * w], v[4 * w + 1], scale, r, tame, qmin, qmax) |
+               (q8_pair<KIND>(v[4 * w + 2], v[4 * w + 3], scale, r, tame, qmin, qmax) << 16);
     if (live) {
-      __stcs(reinterpret_cast<uint2*>(y + c * 8), make_uint2(lo, hi));
-      if ((lane & (tpg - 1)) == 0) {
-        const int64_t g = c / tpg;
-        const int64_t row = g / groups_per_row;
-        s[row * s_row_stride + (g - row * groups_per_row) * s_group_stride] = scale;
-      }
+      if constexpr (EPT == 16)
+        __stcs(reinterpret_cast<uint4*>(y + c * EPT), make_uint4(out[0], out[1], out[2], out[3]));
+      else
+        __stcs(reinterpret_cast<uint2*>(y + c * EPT), make_uint2(out[0], out[1]));
+      if ((lane & (tpg - 1)) == 0) s[scale_index(c >> tpg_shift, groups_per_row, s_row_stride, s_group_stride)] = scale;
     }
   }
 }
 
-template <typename T>
+template <typename T, int EPT>
 cudaError_t launch_kind(int kind, uint8_t* y, float* s, const T* x, int64_t n_chunks, int tpg, int64_t gpr,
-                        int64_t srs, int64_t sgs, float eps, float qmin, float qmax, int ue8m0, int num_sms,
-                        cudaStream_t stream) {
+                        int64_t srs, int64_t sgs, float eps, float qmin, float qmax, int ue8m0, int zero_to_one,
+                        int num_sms, cudaStream_t stream) {
   const int threads = 256;
   int64_t blocks = (n_chunks + threads - 1) / threads;
   const int64_t cap = static_cast<int64_t>(num_sms) * 16;  // 8 resident CTAs per SM, two rounds
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   const dim3 grid(static_cast<unsigned>(blocks));
-  if (kind == kE4M3)
-    tg_per_token_group_quant_kernel<T, kE4M3><<<grid, threads, 0, stream>>>(y, s, x, n_chunks, tpg, gpr, srs, sgs, eps, qmin, qmax, ue8m0);
-  else if (kind == kE5M2)
-    tg_per_token_group_quant_kernel<T, kE5M2><<<grid, threads, 0, stream>>>(y, s, x, n_chunks, tpg, gpr, srs, sgs, eps, qmin, qmax, ue8m0);
+  if (kind == kQ8E4M3)
+    tg_per_token_group_quant_kernel<T, kQ8E4M3, EPT><<<grid, threads, 0, stream>>>(y, s, x, n_chunks, tpg, gpr, srs, sgs, eps, qmin, qmax, ue8m0, zero_to_one);
+  else if (kind == kQ8E5M2)
+    tg_per_token_group_quant_kernel<T, kQ8E5M2, EPT><<<grid, threads, 0, stream>>>(y, s, x, n_chunks, tpg, gpr, srs, sgs, eps, qmin, qmax, ue8m0, zero_to_one);
   else
-    tg_per_token_group_quant_kernel<T, kInt8><<<grid, threads, 0, stream>>>(y, s, x, n_chunks, tpg, gpr, srs, sgs, eps, qmin, qmax, ue8m0);
+    tg_per_token_group_quant_kernel<T, kQ8Int8, EPT><<<grid, threads, 0, stream>>>(y, s, x, n_chunks, tpg, gpr, srs, sgs, eps, qmin, qmax, ue8m0, zero_to_one);
   return cudaGetLastError();
+}
+
+// group_size 8 runs 8 elements per thread, everything else 16.
+cudaError_t launch_any(int x_dtype, int kind, uint8_t* y, float* s, const void* x, int64_t numel, int group_size,
+                       int64_t gpr, int64_t srs, int64_t sgs, float eps, float qmin, float qmax, int ue8m0,
+                       int zero_to_one, int num_sms, cudaStream_t stream) {
+#define TG_GQ_LAUNCH(T, EPT)                                                                                       \
+  launch_kind<T, EPT>(kind, y, s, static_cast<const T*>(x), numel / EPT, group_size / EPT, gpr, srs, sgs, eps, qmin, \
+                      qmax, ue8m0, zero_to_one, num_sms, stream)
+  if (group_size == 8) {
+    if (x_dtype == TG_BF16) return TG_GQ_LAUNCH(__nv_bfloat16, 8);
+    if (x_dtype == TG_F16) return TG_GQ_LAUNCH(__half, 8);
+    return TG_GQ_LAUNCH(float, 8);
+  }
+  if (x_dtype == TG_BF16) return TG_GQ_LAUNCH(__nv_bfloat16, 16);
+  if (x_dtype == TG_F16) return TG_GQ_LAUNCH(__half, 16);
+  return TG_GQ_LAUNCH(float, 16);
+#undef TG_GQ_LAUNCH
 }
 
 struct Guard {
@@ -136,6 +179,18 @@ struct Guard {
 }  // namespace
 }  // namespace tg
 
+namespace tg {
+// The 1 x 128 activation quantiser is the same kernel with its own zero rule (scale 1.0, no eps) and one
+// scale per 128-element block, stored densely.
+cudaError_t launch_act_quant(void* y, float* s, const void* x, int x_dtype, int64_t n_blocks, cudaStream_t stream) {
+  int dev = 0, num_sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+  return launch_any(x_dtype, kQ8E4M3, static_cast<uint8_t*>(y), s, x, n_blocks * 128, 128, 1, 1, 0, 0.f, -448.f,
+                    448.f, 0, 1, num_sms, stream);
+}
+}  // namespace tg
+
 using namespace tg;
 
 extern "C" TG_API int32_t tg_per_token_group_quant(const TgTensorDesc* Y, const TgTensorDesc* S,
@@ -147,17 +202,17 @@ extern "C" TG_API int32_t tg_per_token_group_quant(const TgTensorDesc* Y, const 
     return api_fail(TG_ERR_DTYPE, "X must be bf16, f16 or f32");
   int kind;
   float qmin, qmax;
-  if (Y->dtype == TG_F8E4M3) { kind = kE4M3; qmin = -448.f; qmax = 448.f; }
-  else if (Y->dtype == TG_F8E5M2) { kind = kE5M2; qmin = -57344.f; qmax = 57344.f; }
-  else if (Y->dtype == TG_I8) { kind = kInt8; qmin = -128.f; qmax = 127.f; }
+  if (Y->dtype == TG_F8E4M3) { kind = kQ8E4M3; qmin = -448.f; qmax = 448.f; }
+  else if (Y->dtype == TG_F8E5M2) { kind = kQ8E5M2; qmin = -57344.f; qmax = 57344.f; }
+  else if (Y->dtype == TG_I8) { kind = kQ8Int8; qmin = -128.f; qmax = 127.f; }
   else return api_fail(TG_ERR_DTYPE, "Y must be float8_e4m3fn (7), float8_e5m2 (5) or int8 (8)");
   if (S->dtype != TG_F32) return api_fail(TG_ERR_DTYPE, "S must be f32");
   if (X->ndim != 2 || Y->ndim != 2 || S->ndim != 2) return api_fail(TG_ERR_ARGS, "X, Y and S must be 2-D (flatten the leading dimensions)");
   const int64_t T = X->shape[0], H = X->shape[1];
   if (T < 0 || H <= 0) return api_fail(TG_ERR_ARGS, "X has a bad shape");
   if (group_size != 8 && group_size != 16 && group_size != 32 && group_size != 64 && group_size != 128 &&
-      group_size != 256) {
-    snprintf(msg, sizeof(msg), "group_size %d is not one of 8, 16, 32, 64, 128, 256", group_size);
+      group_size != 256 && group_size != 512) {
+    snprintf(msg, sizeof(msg), "group_size %d is not one of 8, 16, 32, 64, 128, 256, 512", group_size);
     return api_fail(TG_ERR_ARGS, msg);
   }
   if (H % group_size != 0) {
@@ -173,8 +228,8 @@ extern "C" TG_API int32_t tg_per_token_group_quant(const TgTensorDesc* Y, const 
   if (!(eps >= 0.f)) return api_fail(TG_ERR_ARGS, "eps must be >= 0");
   if (T == 0) return TG_OK;
   if (X->ptr == 0 || Y->ptr == 0 || S->ptr == 0) return api_fail(TG_ERR_NULL, "a data pointer is null");
-  if ((X->ptr & 15u) || (Y->ptr & 7u) || (S->ptr & 3u))
-    return api_fail(TG_ERR_ALIGN, "X needs 16-byte, Y 8-byte and S 4-byte alignment");
+  if ((X->ptr & 15u) || (Y->ptr & 15u) || (S->ptr & 3u))
+    return api_fail(TG_ERR_ALIGN, "X and Y need 16-byte, S 4-byte alignment");
   if (device_id < 0 || device_id >= 64) return api_fail(TG_ERR_DEVICE, "device id out of range");
 
   Guard guard(device_id);
@@ -187,20 +242,10 @@ extern "C" TG_API int32_t tg_per_token_group_quant(const TgTensorDesc* Y, const 
   int32_t rc;
   if ((rc = api_init_device(device_id, &num_sms, &status)) != TG_OK) return rc;
   cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
-  const int64_t n_chunks = T * H / 8;
-  const int tpg = group_size / 8;
   uint8_t* y = reinterpret_cast<uint8_t*>(Y->ptr);
   float* s = reinterpret_cast<float*>(S->ptr);
-  cudaError_t e;
-  if (X->dtype == TG_BF16)
-    e = launch_kind<__nv_bfloat16>(kind, y, s, reinterpret_cast<const __nv_bfloat16*>(X->ptr), n_chunks, tpg, G,
-                                   S->strides[0], S->strides[1], eps, qmin, qmax, scale_ue8m0, num_sms, cs);
-  else if (X->dtype == TG_F16)
-    e = launch_kind<__half>(kind, y, s, reinterpret_cast<const __half*>(X->ptr), n_chunks, tpg, G, S->strides[0],
-                            S->strides[1], eps, qmin, qmax, scale_ue8m0, num_sms, cs);
-  else
-    e = launch_kind<float>(kind, y, s, reinterpret_cast<const float*>(X->ptr), n_chunks, tpg, G, S->strides[0],
-                           S->strides[1], eps, qmin, qmax, scale_ue8m0, num_sms, cs);
+  const cudaError_t e = launch_any(X->dtype, kind, y, s, reinterpret_cast<const void*>(X->ptr), T * H, group_size, G,
+                                   S->strides[0], S->strides[1], eps, qmin, qmax, scale_ue8m0, 0, num_sms, cs);
   if (e != cudaSuccess) {
     snprintf(msg, sizeof(msg), "group quantiser launch failed: %s", cudaGetErrorString(e));
     return api_fail(TG_ERR_LAUNCH, msg);

@@ -1,13 +1,15 @@
 // e4m3 quantisers and the block dequantiser that sit either side of the FP8
 // GEMMs.  All of them are single-pass streaming kernels bound by HBM
-// bandwidth: 16-byte accesses, one warp per 128-element quantisation block
-// where a block reduction is needed.  Division is IEEE (div.rn): an
-// approximate reciprocal moves values across e4m3 rounding boundaries.
+// bandwidth.  Results equal an IEEE division (div.rn) followed by the cast: an
+// approximate reciprocal alone moves values across e4m3 rounding boundaries,
+// so the reciprocal path of tg_quant_common.cuh redoes exactly the elements
+// that sit next to a boundary with div.rn.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
 #include "tg_internal.h"
+#include "tg_quant_common.cuh"
 
 namespace tg {
 
@@ -52,30 +54,8 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-// ---------------------------------------------------------------- act_quant
-// One warp per block of 128 contiguous elements: lane l owns elements 4l..4l+3.
-// Follows src/tilegym/suites/unsloth/cutile/fp8.py:77-120 (amax/448, 1.0 for a
-// zero block, IEEE division, cast to e4m3).
-template <typename T>
-__global__ void __launch_bounds__(256) tg_act_quant_kernel(uint8_t* __restrict__ y, float* __restrict__ s,
-                                                           const T* __restrict__ x, int64_t n_blocks) {
-  const int lane = threadIdx.x & 31;
-  const int64_t warps_total = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
-  for (int64_t b = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); b < n_blocks;
-       b += warps_total) {
-    float v[4];
-    load4<T>(x + b * 128 + lane * 4, v);
-    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-    amax = warp_max(amax);
-    float scale = __fdiv_rn(amax, kE4M3Max);
-    if (scale == 0.f) scale = 1.0f;
-    uint32_t packed = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) packed |= static_cast<uint32_t>(to_e4m3(__fdiv_rn(v[j], scale))) << (8 * j);
-    *reinterpret_cast<uint32_t*>(y + b * 128 + lane * 4) = packed;
-    if (lane == 0) s[b] = scale;
-  }
-}
+// act_quant (1 x 128, src/tilegym/suites/unsloth/cutile/fp8.py:77-120: amax/448, 1.0 for a zero block, IEEE
+// division, cast to e4m3) is the per-token group kernel of group_quant.cu with 16 lanes per group.
 
 // ----------------------------------------------------------- weight_dequant
 // y[i,j] = x[i,j] * s[i/128, j/128]; each thread converts 16 consecutive
@@ -156,16 +136,22 @@ __global__ void __launch_bounds__(256) tg_quant_pertensor_kernel(uint8_t* __rest
   if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   const int64_t n4 = numel / 4;
-  for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < n4; g += stride) {
-    float v[4];
+  // x / scale through the shared reciprocal with the exactness check of tg_quant_common.cuh; the e4m3 cast
+  // saturates at +-448 by itself, which is the clamp
+  const bool tame = q8_scale_is_tame(scale);
+  const float r = __frcp_rn(scale);
+  for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < n4; g += 2 * stride) {
+    float v[4], w[4];
+    const bool second = g + stride < n4;
     load4<T>(x + g * 4, v);
-    uint32_t packed = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float qv = fminf(fmaxf(__fdiv_rn(v[j], scale), -kE4M3Max), kE4M3Max);
-      packed |= static_cast<uint32_t>(to_e4m3(qv)) << (8 * j);
-    }
-    *reinterpret_cast<uint32_t*>(y + g * 4) = packed;
+    if (second) load4<T>(x + (g + stride) * 4, w);
+    *reinterpret_cast<uint32_t*>(y + g * 4) =
+        q8_pair<kQ8E4M3>(v[0], v[1], scale, r, tame, -kE4M3Max, kE4M3Max) |
+        (q8_pair<kQ8E4M3>(v[2], v[3], scale, r, tame, -kE4M3Max, kE4M3Max) << 16);
+    if (second)
+      *reinterpret_cast<uint32_t*>(y + (g + stride) * 4) =
+          q8_pair<kQ8E4M3>(w[0], w[1], scale, r, tame, -kE4M3Max, kE4M3Max) |
+          (q8_pair<kQ8E4M3>(w[2], w[3], scale, r, tame, -kE4M3Max, kE4M3Max) << 16);
   }
   for (int64_t e = n4 * 4 + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < numel; e += stride) {
     float qv = fminf(fmaxf(__fdiv_rn(to_f32<T>(x[e]), scale), -kE4M3Max), kE4M3Max);
@@ -242,18 +228,8 @@ int grid_for(int64_t work_items, int threads, int cap) {
 
 }  // namespace
 
-cudaError_t launch_act_quant(void* y, float* s, const void* x, int x_dtype, int64_t n_blocks, cudaStream_t stream) {
-  if (n_blocks == 0) return cudaSuccess;
-  const int grid = grid_for(n_blocks, 8, 148 * 32);
-  uint8_t* yy = static_cast<uint8_t*>(y);
-  if (x_dtype == TG_BF16)
-    tg_act_quant_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(yy, s, static_cast<const __nv_bfloat16*>(x), n_blocks);
-  else if (x_dtype == TG_F16)
-    tg_act_quant_kernel<__half><<<grid, 256, 0, stream>>>(yy, s, static_cast<const __half*>(x), n_blocks);
-  else
-    tg_act_quant_kernel<float><<<grid, 256, 0, stream>>>(yy, s, static_cast<const float*>(x), n_blocks);
-  return cudaGetLastError();
-}
+// (launch_act_quant lives with the group quantiser in group_quant.cu: the 1 x 128 quantiser is that kernel
+// with 16 lanes per group.)
 
 cudaError_t launch_weight_dequant(void* y, int y_dtype, const uint8_t* x, const float* s, int64_t M, int64_t N,
                                   int64_t lds, cudaStream_t stream) {

@@ -1,0 +1,65 @@
+// Element-wise core of the 8-bit quantisers: bytes = cast(clamp(x / s, min, max)), identical to what an IEEE
+// (round-to-nearest) division followed by the cast gives, at a fraction of the instruction count.
+//
+// Two costs bound these streaming kernels before HBM does.  div.rn.f32 is 10-15 instructions per element, and
+// the float -> fp8 conversion unit converts about one lane (two values) per clock per SM sub-partition, so there
+// is room for exactly one two-wide conversion per pair of elements and nothing more.  Hence: the group's
+// reciprocal r = RN(1 / s) is computed once, a = x * r is within 1.2e-7 (relative, two ulps) of the true
+// quotient Q, and cast(a) == cast(RN(Q)) unless a lies within a few ulps of one of the TARGET format's
+// rounding boundaries - a test on the bits of a, no conversion needed.  Only those elements (about one in
+// 10^5, plus the target's subnormal range, where the boundaries sit elsewhere) are redone with __fdiv_rn.
+#pragma once
+#include <cuda_fp8.h>
+#include <stdint.h>
+
+namespace tg {
+
+enum Q8Kind : int { kQ8E4M3 = 0, kQ8E5M2 = 1, kQ8Int8 = 2 };
+
+// The reciprocal path needs a scale whose reciprocal and products stay in the normal range; the elements of a
+// group whose scale is outside it all take __fdiv_rn.
+__device__ __forceinline__ bool q8_scale_is_tame(float s) { return s > 1e-20f && s < 1e20f; }
+
+// May cast(a) differ from cast(q) for some q within 4 ulps of a?
+template <int KIND>
+__device__ __forceinline__ bool q8_unsafe(float a) {
+  if constexpr (KIND == kQ8Int8) {
+    // truncation changes at integers; beyond +-130 the clamp decides
+    const float rn = (a + 12582912.f) - 12582912.f;  // nearest integer for |a| < 2^22
+    return a != 0.f && fabsf(a) < 130.f && fabsf(a - rn) <= fabsf(a) * 4.8e-7f;
+  } else {
+    // round-to-nearest-even to 3 (e4m3) or 2 (e5m2) mantissa bits changes at the midpoints, where the
+    // dropped fp32 mantissa bits read 100...0; below the target's normal range the boundaries sit elsewhere
+    constexpr int kDrop = (KIND == kQ8E4M3) ? 20 : 21;
+    constexpr uint32_t kMask = (1u << kDrop) - 1u, kMid = 1u << (kDrop - 1);
+    constexpr uint32_t kTinyBits = (KIND == kQ8E4M3) ? 0x3d000000u : 0x39000000u;  // 2^-5, 2^-13: 2 x smallest normal
+    const uint32_t b = __float_as_uint(a) & 0x7fffffffu;
+    return ((b - (kMid - 4u)) & kMask) <= 8u || (b - 1u) < (kTinyBits - 1u);  // zero is exact: excluded
+  }
+}
+
+template <int KIND>
+__device__ __forceinline__ uint32_t q8_cast2(float lo, float hi, float qmin, float qmax) {
+  if constexpr (KIND == kQ8Int8) {
+    lo = fminf(fmaxf(lo, qmin), qmax);
+    hi = fminf(fmaxf(hi, qmin), qmax);
+    return (static_cast<uint32_t>(__float2int_rz(lo)) & 0xffu) | ((static_cast<uint32_t>(__float2int_rz(hi)) & 0xffu) << 8);
+  } else {
+    // the fp8 casts saturate to the largest finite value by themselves (the clamp) and keep NaN
+    return static_cast<uint32_t>(
+        __nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, KIND == kQ8E4M3 ? __NV_E4M3 : __NV_E5M2));
+  }
+}
+
+// Two neighbouring elements -> two bytes (x0 in the low byte).
+template <int KIND>
+__device__ __forceinline__ uint32_t q8_pair(float x0, float x1, float s, float r, bool tame, float qmin, float qmax) {
+  float a0 = x0 * r, a1 = x1 * r;
+  if (!tame || q8_unsafe<KIND>(a0) || q8_unsafe<KIND>(a1)) {
+    a0 = __fdiv_rn(x0, s);
+    a1 = __fdiv_rn(x1, s);
+  }
+  return q8_cast2<KIND>(a0, a1, qmin, qmax);
+}
+
+}  // namespace tg
