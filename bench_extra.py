@@ -126,6 +126,28 @@ def quantiser_sweep(dev, hbm_peak_gbs: float):
     return rows
 
 
+def grouped_sweep(dev, fp8_peak_tflops: float):
+    """Grouped (MoE-style) block-scaled GEMM on the DeepSeek-V2 expert shape (N, K) = (3072, 5120): 4096 rows
+    routed to 8 experts, evenly and raggedly; FLOPs = 2 * rows * N * K whatever the routing."""
+    import tilegym_b200 as tg
+
+    N, K, total = 3072, 5120, 4096
+    rows = []
+    for name, sizes in (("8 x 512", [512] * 8), ("ragged", [37, 901, 512, 3, 1200, 640, 0, 803])):
+        assert sum(sizes) == total
+        G = len(sizes)
+        a = torch.randn(total, K, device=dev).to(torch.float8_e4m3fn)
+        b = torch.randn(G, N, K, device=dev, dtype=torch.bfloat16).mul_(0.02).to(torch.float8_e4m3fn)
+        As = torch.rand(total, K // 128, device=dev) + 0.5
+        Bs = torch.rand(G, N // 128, K // 128, device=dev) + 0.5
+        ind = torch.tensor([0] + list(torch.tensor(sizes).cumsum(0)), dtype=torch.int32, device=dev)
+        us = graph_time_us(lambda i: tg.ragged_block_scaled_bmm(a, b, As, Bs, ind, max(sizes)), 4, replays=10)
+        flops = 2.0 * total * N * K
+        rows.append({"routing": name, "groups": G, "rows": total, "N": N, "K": K, "us": round(us, 2),
+                     "tflops": round(flops / us / 1e6, 1), "frac": round(flops / us / 1e6 / fp8_peak_tflops, 3)})
+    return rows
+
+
 def run(dev, peaks):
     hbm = float(peaks["hbm_gbs"])
     fp8 = 2.0 * float(peaks["bf16_tflops"])  # kernels timed alone: burst figure
@@ -134,5 +156,6 @@ def run(dev, peaks):
                   "measured HBM copy bandwidth / of 2 x measured bf16 burst",
         "decode_per_tensor": decode_sweep(dev, hbm),
         "block_scaled": block_scaled_sweep(dev, fp8, hbm),
+        "grouped_block_scaled": grouped_sweep(dev, fp8),
         "quantisers": quantiser_sweep(dev, hbm),
     }

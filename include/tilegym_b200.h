@@ -98,6 +98,23 @@ TG_API int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc
                                 int32_t block_k, uint64_t workspace, uint64_t workspace_bytes,
                                 int32_t device_id, uint64_t stream);
 
+/* Grouped (ragged, MoE-style) block-scaled GEMM: rows [m_indptr[g], m_indptr[g+1]) of A and C belong to group g
+ * and use weight B[g]:
+ *     C[m,n] = sum_kb  As[m,kb] * Bs[g, n/128, kb] * (A[m,kb-block] . B[g, n, kb-block])      for m in group g
+ * A: (M,K) e4m3, all groups' rows stacked; B: (G,N,K) e4m3 contiguous; As: (M, ceil(K/128)) f32;
+ * Bs: (G, ceil(N/128), ceil(K/128)) f32 contiguous; C: (M,N) f32 / f16 / bf16.
+ * m_indptr: DEVICE pointer to G+1 int32 offsets, non-decreasing, never read on the host (so the call can be
+ * captured in a CUDA graph whose routing changes between replays); groups may be empty and need no alignment;
+ * rows outside every group are left untouched; offsets are clamped to [0, M] on the device.
+ * Replaces tilegym.suites.flashinfer.ops.ragged_block_scaled_bmm for e4m3 inputs in the NT layout
+ * (src/tilegym/suites/flashinfer/ops.py:126-158, kernel
+ * src/tilegym/suites/flashinfer/cutile/gemm/ragged_block_scaled_bmm.py:497-616).
+ */
+TG_API int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
+                                               const TgTensorDesc* As, const TgTensorDesc* Bs, uint64_t m_indptr,
+                                               int32_t block_n, int32_t block_k, int32_t device_id,
+                                               uint64_t stream);
+
 /* Column-parallel GEMM fused with the all-gather of its output (multi-GPU, one
  * process per GPU).  This rank computes its slab C[M, n] = alpha*sa*sb*(A . B_shard^T)
  * + bias and the kernel's epilogue stores every finished tile into C AND into the

@@ -186,6 +186,36 @@ def ref_w8a8_block_fp8_matmul(
     return C.to(output_dtype).reshape(*A.shape[:-1], B.shape[0])
 
 
+def ref_ragged_block_scaled_bmm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    a_scale: torch.Tensor,
+    b_scale: torch.Tensor,
+    m_indptr: torch.Tensor,
+    block_n: int = 128,
+    block_k: int = 128,
+    out_dtype: torch.dtype = torch.bfloat16,
+) -> torch.Tensor:
+    """Ragged block-scaled GEMM, the torch reference of
+    tests/suites/flashinfer/test_flashinfer_ragged_block_scaled_bmm.py:77-136: for every group q the rows
+    [m_indptr[q], m_indptr[q+1]) of `a` are dequantised per (row, 128-K block), weight b[q] per 128 x 128
+    block, multiplied in fp32 and cast.  Rows outside every group stay zero; empty groups are skipped (the
+    reference asserts they do not occur)."""
+    total_m, K = a.shape
+    Q, N, _ = b.shape
+    af, bf = a.float(), b.float()
+    c = torch.zeros((total_m, N), dtype=out_dtype)
+    for q in range(Q):
+        lo, hi = int(m_indptr[q]), int(m_indptr[q + 1])
+        if hi <= lo:
+            continue
+        sa = torch.repeat_interleave(a_scale[lo:hi], block_k, dim=1)[:, :K]
+        sb = torch.repeat_interleave(b_scale[q], block_n, dim=0)[:N]
+        sb = torch.repeat_interleave(sb, block_k, dim=1)[:, :K]
+        c[lo:hi] = torch.mm(af[lo:hi] * sa, (bf[q] * sb).t()).to(out_dtype)
+    return c
+
+
 def ref_fp8_scaled_mm(
     A: torch.Tensor,
     B: torch.Tensor,

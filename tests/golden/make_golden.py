@@ -9,7 +9,8 @@ Run once, in a container that has the TileGym source tree:
 It imports the `reference` static methods of TileGym's test classes
 (tests/suites/unsloth/test_fp8.py and
 tests/suites/flashinfer/test_flashinfer_gemm_alpha_beta.py) and the torch reference function of
-tests/suites/flashinfer/test_per_token_group_quant_8bit.py, feeds them inputs
+tests/suites/flashinfer/test_per_token_group_quant_8bit.py and
+tests/suites/flashinfer/test_flashinfer_ragged_block_scaled_bmm.py, feeds them inputs
 drawn the way those tests draw them (same seeds and distributions, on the CPU)
 and stores inputs and outputs as compressed .npz files.  fp8 and bf16 tensors
 are stored as their raw bit patterns (uint8 / uint16).  The tests in
@@ -107,6 +108,27 @@ def main(ref_root: str, only=()) -> None:
             name = {torch.float8_e4m3fn: "e4m3", torch.float8_e5m2: "e5m2", torch.int8: "int8"}[dst]
             np.savez_compressed(os.path.join(HERE, f"group_quant_{T_}x{H}_g{g}_{name}_ue{int(ue)}.npz"),
                                 x=bits(x), q=qb, s=bits(sc))
+    # --- ragged_block_scaled_bmm: input recipe of test_flashinfer_ragged_block_scaled_bmm.py:157-190 (values
+    # spread over the e4m3 range, scales rand * 1e-2, 128-aligned segments as its cuTile path needs) on the CPU,
+    # through that test class's torch reference ------------------------------------------------------------
+    if want("ragged_bmm"):
+        from tests.suites.flashinfer.test_flashinfer_ragged_block_scaled_bmm import (
+            Test_FlashInfer_RaggedBlockScaledBMM as RB,
+        )
+
+        for Q, m, N, K, seed in [(4, 128, 256, 256, 0), (3, 256, 384, 512, 1)]:
+            torch.manual_seed(seed)
+            total_m = Q * m
+            ind = torch.arange(Q + 1, dtype=torch.int32) * m
+            a = ((torch.empty(total_m, K).normal_(mean=0.0, std=0.3) - 0.5) * 2 * 448).clamp(-448, 448)
+            b = ((torch.empty(Q, N, K).normal_(mean=0.0, std=0.3) - 0.5) * 2 * 448).clamp(-448, 448)
+            a, b = a.to(torch.float8_e4m3fn), b.to(torch.float8_e4m3fn)
+            sa = torch.rand(total_m, -(-K // 128)) * 1e-2
+            sb = torch.rand(Q, -(-N // 128), -(-K // 128)) * 1e-2
+            c = RB.reference(a, b, sa, sb, ind, 128, 128, False, True, torch.bfloat16)
+            np.savez_compressed(os.path.join(HERE, f"ragged_bmm_q{Q}_m{m}_{N}x{K}.npz"),
+                                a=bits(a), b=bits(b), a_scale=bits(sa), b_scale=bits(sb), m_indptr=ind.numpy(),
+                                c=bits(c))
     print("golden fixtures written to", HERE)
 
 

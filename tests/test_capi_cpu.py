@@ -78,6 +78,30 @@ def test_blockscaled_argument_checks():
     assert call(As.half(), Bs) == -2
 
 
+def test_grouped_blockscaled_argument_checks():
+    L = _lib.lib()
+    A = torch.zeros(256, 256, dtype=torch.float8_e4m3fn)
+    B = torch.zeros(2, 128, 256, dtype=torch.float8_e4m3fn)
+    C = torch.zeros(256, 128, dtype=torch.bfloat16)
+    As, Bs = torch.zeros(256, 2), torch.zeros(2, 1, 2)
+    ind = torch.zeros(3, dtype=torch.int32)
+
+    def call(c=C, a=A, b=B, sa=As, sb=Bs, ptr=None, bn=128):
+        return L.tg_fp8_gemm_blockscaled_grouped(_d(c), _d(a), _d(b), _d(sa), _d(sb),
+                                                 ind.data_ptr() if ptr is None else ptr, bn, 128, 0, 0)
+
+    assert call(b=B[0]) == -6  # B must be 3-D
+    assert call(b=torch.zeros(2, 128, 128, dtype=torch.float8_e4m3fn)) == -6  # K mismatch
+    assert call(sb=torch.zeros(2, 2, 2)) == -6  # Bs shape
+    assert call(sa=torch.zeros(255, 2)) == -6
+    assert call(c=torch.zeros(256, 64, dtype=torch.bfloat16)) == -6
+    assert call(bn=64) == -6
+    assert call(ptr=0) == -5
+    assert call(b=B.view(torch.uint8)) == -2
+    assert call(a=torch.zeros(0, 256, dtype=torch.float8_e4m3fn), c=torch.zeros(0, 128, dtype=torch.bfloat16),
+                sa=torch.zeros(0, 2)) == 0  # nothing to do, no device needed
+
+
 def test_quantiser_argument_checks():
     L = _lib.lib()
     x = torch.zeros(4, 256, dtype=torch.bfloat16)
@@ -119,6 +143,8 @@ def test_signatures_match_the_reference_entry_points():
     assert sig.parameters["trans_b"].default is True
     assert list(inspect.signature(ops.act_quant).parameters) == ["x", "block_size"]
     assert list(inspect.signature(ops.weight_dequant).parameters) == ["x", "s", "block_size", "dtype"]
+    assert list(inspect.signature(ops.ragged_block_scaled_bmm).parameters)[:10] == [
+        "a", "b", "a_scale", "b_scale", "m_indptr", "max_m", "max_m_device", "transpose_a", "transpose_b", "out_dtype"]
     assert list(inspect.signature(ops.per_token_group_quant_8bit).parameters) == [
         "x", "group_size", "eps", "dst_dtype", "column_major_scales", "scale_tma_aligned", "scale_ue8m0"]
     assert list(inspect.signature(ops.matmul).parameters)[:6] == ["a", "b", "trans_a", "trans_b", "static_persistent", "use_tma"]

@@ -42,6 +42,23 @@ def test_act_quant_matches_reference_fixture(name):
         assert float(s[1, 0]) == 1.0  # all-zero block
 
 
+@pytest.mark.parametrize("name", ["ragged_bmm_q4_m128_256x256.npz", "ragged_bmm_q3_m256_384x512.npz"])
+def test_ragged_block_scaled_bmm_matches_reference_fixture(name):
+    g = load_golden(name)
+    out = R.ref_ragged_block_scaled_bmm(g["a"], g["b"], g["a_scale"], g["b_scale"], g["m_indptr"])
+    assert bool((out.view(torch.int16) == g["c"].view(torch.int16)).all())
+
+
+def test_ragged_block_scaled_bmm_is_the_dense_gemm_per_group():
+    a8, b8, As, Bs = R.gen_block_scaled_case(96, 256, 384, seed=5)
+    ind = torch.tensor([0, 40, 40, 96], dtype=torch.int32)  # one empty group
+    b3 = torch.stack([b8, b8.flip(0), b8])
+    bs3 = torch.stack([Bs, Bs.flip(0), Bs])
+    out = R.ref_ragged_block_scaled_bmm(a8, b3, As, bs3, ind)
+    assert torch.equal(out[:40], R.ref_w8a8_block_fp8_matmul(a8[:40], b8, As[:40], Bs, None, torch.bfloat16))
+    assert torch.equal(out[40:], R.ref_w8a8_block_fp8_matmul(a8[40:], b8, As[40:], Bs, None, torch.bfloat16))
+
+
 GROUP_QUANT = sorted(os.path.basename(p) for p in glob.glob(os.path.join(GOLDEN, "group_quant_*.npz")))
 
 

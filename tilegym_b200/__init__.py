@@ -12,6 +12,7 @@ from .ops import (  # noqa: F401
     act_quant,
     fp8_scaled_mm,
     per_token_group_quant_8bit,
+    ragged_block_scaled_bmm,
     fp8_scaled_mm_no_alloc,
     gemm_alpha_beta,
     matmul,

@@ -89,6 +89,10 @@ SIGNATURES = {
         [_P, _P, _P, _P, _P, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int32,
          ctypes.c_uint64],
     ),
+    "tg_fp8_gemm_blockscaled_grouped": (
+        ctypes.c_int32,
+        [_P, _P, _P, _P, _P, ctypes.c_uint64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64],
+    ),
     "tg_act_quant": (ctypes.c_int32, [_P, _P, _P, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64]),
     "tg_per_token_group_quant": (
         ctypes.c_int32,

@@ -428,6 +428,81 @@ int32_t tg_fp8_gemm_pertensor_allgather(const TgTensorDesc* C, const TgTensorDes
   return pertensor_impl(C, A, B, scale_a, scale_b, alpha, bias, 0.0f, 0, 0, peer_ptrs, num_peers, device_id, stream);
 }
 
+int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
+                                        const TgTensorDesc* As, const TgTensorDesc* Bs, uint64_t m_indptr,
+                                        int32_t block_n, int32_t block_k, int32_t device_id, uint64_t stream) {
+  int32_t rc;
+  if ((rc = check_operand(A, "A")) != TG_OK) return rc;
+  if (B == nullptr || As == nullptr || Bs == nullptr) return fail(TG_ERR_NULL, "a descriptor is null");
+  if (B->dtype != TG_F8E4M3) return fail(TG_ERR_DTYPE, "B must be float8_e4m3fn (dtype code 7), got %d", B->dtype);
+  if (block_n != 128 || block_k != 128)
+    return fail(TG_ERR_ARGS, "only block_size [128, 128] is implemented, got [%d, %d]", block_n, block_k);
+  if (B->ndim != 3) return fail(TG_ERR_ARGS, "B must be [groups, N, K], got %d-D", B->ndim);
+  const int64_t M = A->shape[0], K = A->shape[1], G = B->shape[0], N = B->shape[1];
+  if (G <= 0 || N <= 0 || B->shape[2] != K) return fail(TG_ERR_ARGS, "B must be [groups >= 1, N >= 1, K = %lld]", (long long)K);
+  if (B->strides[2] != 1 || B->strides[1] != K || B->strides[0] != N * K) return fail(TG_ERR_ARGS, "B must be contiguous");
+  if (B->ptr == 0) return fail(TG_ERR_NULL, "B data pointer is null");
+  if ((B->ptr & 15u) != 0 || (K & 15) != 0) return fail(TG_ERR_ALIGN, "B needs a 16-byte aligned base and K %% 16 == 0 for TMA");
+  if (G * N > 0x7fffffff || G > 0x7fffff) return fail(TG_ERR_ARGS, "B is too large");
+  if ((rc = check_output(C, M, N)) != TG_OK) return rc;
+  const int64_t KB = (K + 127) / 128, NB = (N + 127) / 128;
+  if (As->dtype != TG_F32 || Bs->dtype != TG_F32) return fail(TG_ERR_DTYPE, "As and Bs must be f32");
+  if (As->ndim != 2 || As->shape[0] != M || As->shape[1] != KB || As->strides[1] != 1 || As->strides[0] < KB)
+    return fail(TG_ERR_ARGS, "As must be [M, ceil(K/128)] = [%lld, %lld] with contiguous rows", (long long)M, (long long)KB);
+  if (Bs->ndim != 3 || Bs->shape[0] != G || Bs->shape[1] != NB || Bs->shape[2] != KB || Bs->strides[2] != 1 ||
+      Bs->strides[1] != KB || Bs->strides[0] != NB * KB)
+    return fail(TG_ERR_ARGS, "Bs must be contiguous [groups, ceil(N/128), ceil(K/128)] = [%lld, %lld, %lld]", (long long)G,
+                (long long)NB, (long long)KB);
+  if ((M > 0 && As->ptr == 0) || Bs->ptr == 0) return fail(TG_ERR_NULL, "scale data pointer is null");
+  if ((As->ptr & 3u) || (Bs->ptr & 3u)) return fail(TG_ERR_ALIGN, "scale pointers must be 4-byte aligned");
+  if (m_indptr == 0) return fail(TG_ERR_NULL, "m_indptr is null");
+  if (m_indptr & 3u) return fail(TG_ERR_ALIGN, "m_indptr must be 4-byte aligned");
+  if (M == 0) return TG_OK;
+
+  DeviceGuard guard(device_id);
+  if (guard.err != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TG_ERR_DEVICE, "cannot select CUDA device %d", device_id);
+  }
+  if ((rc = init_device(device_id)) != TG_OK) return rc;
+  const DeviceState& st = g_dev[device_id];
+  cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = static_cast<int32_t>(M);
+  p.N = static_cast<int32_t>(N);
+  p.K = static_cast<int32_t>(K);
+  p.num_kb = static_cast<int32_t>(KB);
+  p.tiles_n = static_cast<int32_t>((N + 255) / 256);
+  p.C = reinterpret_cast<void*>(C->ptr);
+  p.ldc = C->strides[0];
+  p.out_dtype = C->dtype;
+  p.alpha = 1.0f;
+  p.As = reinterpret_cast<const float*>(As->ptr);
+  p.Bs = reinterpret_cast<const float*>(Bs->ptr);
+  p.ldas = As->strides[0];
+  p.ldbs = KB;
+  p.splits = 1;
+  p.kb_per_split = p.num_kb;
+  p.status = st.status;
+  p.m_indptr = reinterpret_cast<const int32_t*>(m_indptr);
+  p.num_groups = static_cast<int32_t>(G);
+  // every group adds at most one partly filled 128-row tile to the ceil(M / 128) a dense problem would have
+  const int64_t bound = (M + 127) / 128 + G;
+  if (bound * p.tiles_n > 0x3fffffff) return fail(TG_ERR_ARGS, "problem has too many tiles");
+  p.mtile_bound = static_cast<int32_t>(bound);
+  CUtensorMap tmA, tmB, tmC;
+  if ((rc = make_map(&tmA, A->ptr, M, K, A->strides[0], 128)) != TG_OK) return rc;
+  if ((rc = make_map(&tmB, B->ptr, G * N, K, K, 256)) != TG_OK) return rc;  // B viewed as [G * N, K]
+  const bool tma_out = (C->dtype == TG_BF16 || C->dtype == TG_F16) && (C->ptr & 15u) == 0 &&
+                       ((C->strides[0] * 2) & 15) == 0 && env_int("TILEGYM_B200_TMA_STORE", 1) != 0;
+  if (tma_out && (rc = make_out_map(&tmC, C->ptr, M, N, C->strides[0] * 2, C->dtype)) != TG_OK) return rc;
+  cudaError_t e = launch_gemm_blockscaled_grouped(tmA, tmB, tma_out ? &tmC : nullptr, p, st.num_sms, cs);
+  if (e != cudaSuccess) return fail(TG_ERR_LAUNCH, "grouped block-scaled GEMM launch failed: %s", cudaGetErrorString(e));
+  return TG_OK;
+}
+
 int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
                                 const TgTensorDesc* As, const TgTensorDesc* Bs, int32_t block_n, int32_t block_k,
                                 uint64_t workspace, uint64_t workspace_bytes, int32_t device_id, uint64_t stream) {

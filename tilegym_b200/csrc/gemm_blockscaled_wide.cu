@@ -8,6 +8,9 @@
 // accumulators per thread.  That needs more than the 168 registers a 384-thread CTA gets per thread, so the
 // producer / MMA warpgroup hands registers to the two promotion warpgroups with setmaxnreg.
 // Two-byte outputs leave through per-warp swizzled staging buffers and bulk tensor stores.
+// The same kernel runs the grouped (ragged, MoE-style) problem of
+// src/tilegym/suites/flashinfer/cutile/gemm/ragged_block_scaled_bmm.py:497-616: rows [m_indptr[g], m_indptr[g+1])
+// of A use weight g; only the tile look-up differs (locate_tile).
 // Roles: warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, warps 2-3 idle, warps 4-11 promotion + store.
 #include "tg_gemm_common.cuh"
 
@@ -48,7 +51,9 @@ static_assert(kSmemBytes <= 227 * 1024, "shared memory per CTA");
 // 384 threads x 168 registers fill the register file; 128 threads give up 128 each, 256 threads take 64 each.
 constexpr int kRegsLight = 40;
 constexpr int kRegsHeavy = 224;
-static_assert(128 * (168 - kRegsLight) >= 256 * (kRegsHeavy - 168), "register budget");
+constexpr int kRegsHeavyGrouped = 232;
+static_assert(128 * (168 - kRegsLight) >= 256 * (kRegsHeavyGrouped - 168) && kRegsHeavyGrouped >= kRegsHeavy,
+              "register budget");
 
 __device__ __forceinline__ void fma16x2(float2* acc, const uint32_t (&r)[32], float2 sc2) {
 #pragma unroll
@@ -70,6 +75,89 @@ __device__ __forceinline__ void load_as4(const float* as_row, int kb, int num_kb
   }
 }
 
+// Where a tile sits.  Plain GEMM: 128-row tile tm, 256-column tile tn.  Grouped GEMM: the 128-row tiles of all
+// groups are numbered consecutively (group g owns ceil(rows_g / 128) of them; a tile never spans two groups),
+// its rows stop at the end of its group, and its weights / weight scales are those of the group.
+struct TileRef {
+  int row0;     // first row of A, As and C
+  int row_end;  // rows >= row_end are not part of the tile's problem (not stored)
+  int col0;     // first column of C
+  int b_row0;   // first row in the 2-D view of B ([G * N, K] when grouped)
+  int bs_row0;  // row of Bs of the tile's first 128 columns
+  bool valid;
+};
+
+// All 32 lanes of the calling warp must be active (the grouped look-up scans m_indptr with shuffles); the
+// result is the same in every lane.
+// Number of 128-row tiles of all groups together (all 32 lanes active; same result in every lane).
+__device__ __forceinline__ int count_group_mtiles(const GemmParams& p, int lane) {
+  int sum = 0;
+  for (int g = lane; g < p.num_groups; g += 32) {
+    const int beg = min(max(__ldg(p.m_indptr + g), 0), p.M);
+    const int end = min(max(__ldg(p.m_indptr + g + 1), 0), p.M);
+    sum += end > beg ? (end - beg + 127) >> 7 : 0;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  return min(sum, p.mtile_bound);
+}
+
+// `mtiles`: count_group_mtiles() when grouped (tile ids run densely over [0, mtiles * tiles_n)), unused otherwise.
+template <bool kGrouped>
+__device__ __forceinline__ TileRef locate_tile(int t, int mtiles, const GemmParams& p, int lane) {
+  TileRef r;
+  if constexpr (!kGrouped) {
+    int tm, tn;
+    tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+    r.row0 = tm * kBM;
+    r.row_end = p.M;
+    r.col0 = tn * kBN;
+    r.b_row0 = tn * kBN;
+    r.bs_row0 = tn * 2;
+    r.valid = true;
+    return r;
+  } else {
+    // m-tiles vary fastest, so the CTAs running together share a few weight panels through L2
+    const int tn = t / mtiles;
+    const int j = t - tn * mtiles;
+    const int nb_per_group = (p.N + 127) >> 7;
+    r.valid = false;
+    r.row0 = r.row_end = r.b_row0 = r.bs_row0 = 0;
+    r.col0 = tn * kBN;
+    int before = 0;  // m-tiles of the groups already scanned
+    for (int g0 = 0; g0 < p.num_groups; g0 += 32) {
+      const int g = g0 + lane;
+      // clamped to [0, M]: whatever the offsets hold, no row outside A / C is ever touched
+      const int beg = g < p.num_groups ? min(max(__ldg(p.m_indptr + g), 0), p.M) : 0;
+      const int end = g < p.num_groups ? min(max(__ldg(p.m_indptr + g + 1), 0), p.M) : 0;
+      const int tiles = end > beg ? (end - beg + 127) >> 7 : 0;
+      int incl = tiles;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += n;
+      }
+      const int total = __shfl_sync(0xffffffffu, incl, 31);
+      if (j < before + total) {
+        const int first = before + incl - tiles;  // this lane's group owns m-tiles [first, first + tiles)
+        const unsigned owner = __ballot_sync(0xffffffffu, j >= first && j < first + tiles);
+        const int src = __ffs(owner) - 1;
+        const int mt = j - __shfl_sync(0xffffffffu, first, src);
+        const int grp = g0 + src;
+        r.row0 = __shfl_sync(0xffffffffu, beg, src) + mt * kBM;
+        r.row_end = __shfl_sync(0xffffffffu, end, src);
+        r.b_row0 = grp * p.N + tn * kBN;
+        r.bs_row0 = grp * nb_per_group + tn * 2;
+        r.valid = true;
+        return r;
+      }
+      before += total;
+    }
+    return r;
+  }
+}
+
+template <bool kGrouped>
 __global__ void __launch_bounds__(kThreads, 1)
     tg_fp8_gemm_blockscaled_wide_kernel(const __grid_constant__ CUtensorMap tmA,
                                         const __grid_constant__ CUtensorMap tmB,
@@ -114,7 +202,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int num_tiles = p.tiles_m * p.tiles_n;  // 128 x 256 tiles
+  // 128 x 256 tiles; grouped: every warp counts the groups' 128-row tiles itself (warp 0..11 all need it)
+  const int mtiles = kGrouped ? count_group_mtiles(p, lane) : 0;
+  const int num_tiles = kGrouped ? mtiles * p.tiles_n : p.tiles_m * p.tiles_n;
 
   if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsLight));
@@ -128,8 +218,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t ph = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        int tm, tn;
-        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        const TileRef tile = locate_tile<kGrouped>(t, mtiles, p, lane);
+        if (!tile.valid) continue;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag))) {
             report_timeout(p.status, kRoleProducer * 1000 + 51);
@@ -138,8 +228,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           if (elected) {
             mbar_arrive_expect_tx(bar_full + 8 * s, kStageBytes);
-            tma_load_2d(a_base + s * kABytes, &tmA, bar_full + 8 * s, kb * kBK, tm * kBM);
-            tma_load_2d(b_base + s * kBBytes, &tmB, bar_full + 8 * s, kb * kBK, tn * kBN);
+            tma_load_2d(a_base + s * kABytes, &tmA, bar_full + 8 * s, kb * kBK, tile.row0);
+            tma_load_2d(b_base + s * kBBytes, &tmB, bar_full + 8 * s, kb * kBK, tile.b_row0);
           }
           __syncwarp();
           if (++s == S) {
@@ -159,6 +249,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool ok = true;
       [[maybe_unused]] int it = 0;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (kGrouped && !locate_tile<kGrouped>(t, mtiles, p, lane).valid) continue;
         for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
           if (!mbar_wait(bar_tempty + 8 * buf, aph ^ 1u, abort_flag)) {
             report_timeout(p.status, kRoleMma * 1000 + 51);
@@ -198,29 +289,28 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsHeavy));
+    // (the register allocator fits the grouped variant without spills at 232 and the plain one at 224)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kGrouped ? kRegsHeavyGrouped : kRegsHeavy));
     // ---------------------------------------------------- promotion + store
     const int e = warp - 4;
     const int q = warp & 3;   // TMEM lane quadrant
     const int half = e >> 2;  // which 128 of the tile's 256 columns = which quantisation block
-    const bool vec_ok = c_rows_aligned(p);
     // rows of As that start 16-byte aligned are read four k-blocks at a time: a warp's 32 rows cost 32
     // L1 transactions per load, and L1 shares its data path with the tensor core's operand reads
     const bool as_vec = ((reinterpret_cast<uintptr_t>(p.As) & 15u) == 0) && ((p.ldas & 3) == 0);
-    uint8_t* my_stage = out_stage + e * kOutBufBytes;
     int buf = 0;
     uint32_t aph = 0;
     bool ok = true;
     [[maybe_unused]] int eit = 0;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-      int tm, tn;
-      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      const TileRef tile = locate_tile<kGrouped>(t, mtiles, p, lane);
+      if (!tile.valid) continue;
       const int row_in_tile = q * 32 + lane;
-      const int64_t row = static_cast<int64_t>(tm) * kBM + row_in_tile;
-      const int nb = tn * 2 + half;
-      const bool in = row < p.M && nb * 128 < p.N;
+      const int64_t row = static_cast<int64_t>(tile.row0) + row_in_tile;
+      const int col0 = tile.col0 + half * 128;
+      const bool in = row < tile.row_end && col0 < p.N;
       const float* as_row = p.As + (in ? row : 0) * p.ldas;
-      const float* bs_row = p.Bs + static_cast<int64_t>(in ? nb : 0) * p.ldbs;
+      const float* bs_row = p.Bs + static_cast<int64_t>(in ? tile.bs_row0 + half : 0) * p.ldbs;
       float2 acc2[64];
 #pragma unroll
       for (int j = 0; j < 64; ++j) acc2[j] = make_float2(0.f, 0.f);
@@ -274,11 +364,13 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
       if (!ok) break;
-      const int col0 = tn * kBN + half * 128;
-      if (tma_out) {
+      const int row0 = tile.row0 + q * 32;
+      // a bulk store clips at the ends of C only: in a grouped problem a 32-row slice that runs past the end
+      // of its group would overwrite the next group's rows, so such slices take the row-masked stores below
+      if (tma_out && (!kGrouped || row0 + 32 <= tile.row_end)) {
         // two-byte outputs with 16-byte aligned rows: 64 columns at a time go through this warp's swizzled
         // staging buffer and leave as one bulk tensor store, which clips rows >= M and columns >= N
-        const int row0 = tm * kBM + q * 32;
+        uint8_t* my_stage = out_stage + e * kOutBufBytes;
         uint8_t* dst_row = my_stage + lane * 128;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -307,7 +399,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             tma_store_commit();
           }
         }
-      } else if (row < p.M) {
+      } else if (row < tile.row_end) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           float acc[32];
@@ -316,7 +408,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             acc[2 * j] = acc2[c * 16 + j].x;
             acc[2 * j + 1] = acc2[c * 16 + j].y;
           }
-          epilogue_store32(p, row, col0 + c * 32, acc, 1.0f, vec_ok);
+          epilogue_store32(p, row, col0 + c * 32, acc, 1.0f, c_rows_aligned(p));
         }
       }
     }
@@ -334,23 +426,36 @@ __global__ void __launch_bounds__(kThreads, 1)
 
 }  // namespace
 
-cudaError_t launch_gemm_blockscaled_wide(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap* tmC,
-                                         const GemmParams& p, int num_sms, cudaStream_t stream) {
+namespace {
+template <bool kGrouped>
+cudaError_t launch_wide(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap* tmC, const GemmParams& p,
+                        int tiles, int num_sms, cudaStream_t stream) {
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(tg_fp8_gemm_blockscaled_wide_kernel,
+    cudaError_t e = cudaFuncSetAttribute(tg_fp8_gemm_blockscaled_wide_kernel<kGrouped>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < num_sms ? tiles : num_sms;
   // tmC == nullptr selects the register -> global store epilogue (fp32 output or unaligned rows)
-  tg_fp8_gemm_blockscaled_wide_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmC != nullptr ? *tmC : tmA, p,
-                                                                              tmC != nullptr ? 1 : 0);
+  tg_fp8_gemm_blockscaled_wide_kernel<kGrouped>
+      <<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmC != nullptr ? *tmC : tmA, p, tmC != nullptr ? 1 : 0);
   return cudaGetLastError();
+}
+}  // namespace
+
+cudaError_t launch_gemm_blockscaled_wide(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap* tmC,
+                                         const GemmParams& p, int num_sms, cudaStream_t stream) {
+  return launch_wide<false>(tmA, tmB, tmC, p, p.tiles_m * p.tiles_n, num_sms, stream);
+}
+
+// Grouped problem: p.M = total rows, p.m_indptr / num_groups / mtile_bound set, tmB maps B as [G * N, K].
+cudaError_t launch_gemm_blockscaled_grouped(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap* tmC,
+                                            const GemmParams& p, int num_sms, cudaStream_t stream) {
+  return launch_wide<true>(tmA, tmB, tmC, p, p.mtile_bound * p.tiles_n, num_sms, stream);
 }
 
 }  // namespace tg

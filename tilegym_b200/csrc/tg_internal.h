@@ -37,6 +37,10 @@ struct GemmParams {
   int32_t kb_per_split;   // k-blocks per split
   float* ws_partial;      // [splits, tiles..., 128*BN] fp32 partial tiles
   uint32_t* ws_counters;  // one per output tile, zero on entry and on exit
+  // grouped (ragged) block-scaled GEMM: rows [m_indptr[g], m_indptr[g+1]) of A / C use weight g of B [G, N, K]
+  const int32_t* m_indptr;  // device, num_groups + 1 entries
+  int32_t num_groups;
+  int32_t mtile_bound;  // ceil(M / 128) + num_groups >= the number of 128-row tiles of all groups
   // diagnostics
   int32_t* status;  // device status word
   // bit 0 (small-M kernel): the weight operand is not written by the kernel that precedes this one on the
@@ -65,6 +69,10 @@ cudaError_t launch_gemm_blockscaled(const CUtensorMap& tmA, const CUtensorMap& t
 // or nullptr for register -> global stores (fp32 output, unaligned rows).
 cudaError_t launch_gemm_blockscaled_wide(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap* tmC,
                                          const GemmParams& p, int num_sms, cudaStream_t stream);
+// Grouped (ragged) problem on the same kernel: p.M = total rows, p.m_indptr / num_groups / mtile_bound set,
+// tmB maps B [G, N, K] as [G * N, K] with 256-row boxes.
+cudaError_t launch_gemm_blockscaled_grouped(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap* tmC,
+                                            const GemmParams& p, int num_sms, cudaStream_t stream);
 // CTA-pair block-scaled kernel: 256 x 192 tiles, tmA boxes 128 rows and tmB 96, p.tiles_n counts 192-wide tiles, no split-K.
 cudaError_t launch_gemm_blockscaled_2cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
                                          int group_m, int num_sms, cudaStream_t stream);

@@ -119,6 +119,57 @@ def w8a8_block_fp8_matmul(
     return C
 
 
+def ragged_block_scaled_bmm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    a_scale: torch.Tensor,
+    b_scale: torch.Tensor,
+    m_indptr: torch.Tensor,
+    max_m: int,
+    max_m_device: Optional[torch.Tensor] = None,
+    transpose_a: bool = False,
+    transpose_b: bool = True,
+    out_dtype: Optional[torch.dtype] = None,
+    **kwargs,
+) -> torch.Tensor:
+    """Ragged (grouped) block-scaled FP8 GEMM: rows [m_indptr[q], m_indptr[q+1]) of `a` times weight b[q].T.
+
+    Signature and preconditions of src/tilegym/suites/flashinfer/ops.py:126-158 and
+    src/tilegym/suites/flashinfer/cutile/gemm/ragged_block_scaled_bmm.py:497-545: a (total_m, K) e4m3,
+    b (Q, N, K) e4m3, a_scale (total_m, ceil(K/128)) f32, b_scale (Q, ceil(N/128), ceil(K/128)) f32, m_indptr
+    (Q+1,) int32 on the device; returns a new (total_m, N) tensor (bf16 unless out_dtype says otherwise).
+    Differences: segments need no alignment to 128 rows and may be empty; `max_m` / `max_m_device` are accepted
+    and not needed (the kernel reads m_indptr itself, nothing is read back to the host); only 128 x 128 scale
+    blocks and e4m3 inputs are implemented.
+    """
+    assert transpose_a is False and transpose_b is True, "Only NT layout is supported"
+    dev = _need_cuda(a, b, a_scale, b_scale, m_indptr)
+    assert a.is_contiguous(), "A matrix must be contiguous"
+    assert b.is_contiguous(), "B matrix must be contiguous"
+    assert a_scale.is_contiguous(), "A scale matrix must be contiguous"
+    assert b_scale.is_contiguous(), "B scale matrix must be contiguous"
+    assert m_indptr.is_contiguous(), "m_indptr must be contiguous"
+    total_m, K_A = a.shape
+    Q, N, K_B = b.shape
+    assert K_A == K_B, f"K dimensions must match: {K_A} != {K_B}"
+    assert m_indptr.shape[0] == Q + 1, "m_indptr must have Q+1 elements"
+    assert a_scale.shape[0] == total_m, "a_scale total_m dimension mismatch"
+    assert b_scale.shape[0] == Q, "b_scale Q dimension mismatch"
+    if m_indptr.dtype != torch.int32:
+        raise _lib.TileGymB200Error(-2, f"m_indptr must be int32, got {m_indptr.dtype}")
+    if out_dtype is None:
+        out_dtype = torch.bfloat16
+    if out_dtype not in _OUT_DTYPES:
+        raise _lib.TileGymB200Error(-6, f"out_dtype {out_dtype} is not one of f32, f16, bf16")
+    c = torch.empty((total_m, N), device=dev, dtype=out_dtype)
+    rc = _lib.lib().tg_fp8_gemm_blockscaled_grouped(
+        _lib.ref(_lib.desc(c)), _lib.ref(_lib.desc(a)), _lib.ref(_lib.desc(b)), _lib.ref(_lib.desc(a_scale)),
+        _lib.ref(_lib.desc(b_scale)), m_indptr.data_ptr(), 128, 128, dev.index, _stream(dev),
+    )
+    _lib.check_rc(rc)
+    return c
+
+
 def act_quant(x: torch.Tensor, block_size: int = 128) -> Tuple[torch.Tensor, torch.Tensor]:
     """FP8 block-wise activation quantisation: (y e4m3, s f32 per block).
 
