@@ -11,6 +11,7 @@ descriptor structs, a non-zero return code becomes a RuntimeError.
 from __future__ import annotations
 
 import ctypes
+import struct
 import os
 from typing import Optional
 
@@ -63,7 +64,7 @@ class TileGymB200Error(RuntimeError):
 _lib: Optional[ctypes.CDLL] = None
 
 # name -> (restype, argtypes); the list the symbol-export test walks.
-_P = ctypes.POINTER(TensorDesc)
+_P = ctypes.c_char_p  # const TgTensorDesc*, passed as the packed bytes of desc()
 SIGNATURES = {
     "tg_version": (ctypes.c_int32, []),
     "tg_set_static_weights": (ctypes.c_int32, [ctypes.c_int32]),
@@ -126,27 +127,36 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
-def desc(t: Optional[torch.Tensor]) -> Optional[TensorDesc]:
-    """Descriptor of a tensor (None passes through as a NULL pointer)."""
+# The descriptor is marshalled with one struct.pack call (about half the cost of filling a ctypes Structure
+# field by field); the packed bytes have exactly the layout of TensorDesc / TgTensorDesc.
+_DESC = struct.Struct("Qi4x5q5qi4x")
+assert _DESC.size == ctypes.sizeof(TensorDesc)
+_PAD = ((), (0,), (0, 0), (0, 0, 0), (0, 0, 0, 0), (0, 0, 0, 0, 0))
+
+
+def desc(t: Optional[torch.Tensor]) -> Optional[bytes]:
+    """Descriptor of a tensor as the bytes of a TgTensorDesc (None passes through as a NULL pointer)."""
     if t is None:
         return None
-    if t.dim() > 5:
+    nd = t.dim()
+    if nd > 5:
         raise ValueError("tensors of more than 5 dimensions are not supported")
     code = DTYPE_CODES.get(t.dtype)
     if code is None:
         raise TileGymB200Error(-2, f"dtype {t.dtype} has no code in the C ABI")
-    d = TensorDesc()
-    d.ptr = t.data_ptr()
-    d.ndim = t.dim()
-    for i in range(t.dim()):
-        d.shape[i] = t.shape[i]
-        d.strides[i] = t.stride(i)
-    d.dtype = code
+    pad = _PAD[5 - nd]
+    return _DESC.pack(t.data_ptr(), nd, *t.shape, *pad, *t.stride(), *pad, code)
+
+
+def desc2d(ptr: int, rows: int, cols: int, row_stride: int, dtype: torch.dtype) -> bytes:
+    """Descriptor of a row-major 2-D view given by numbers (saves creating the view tensor)."""
+    return _DESC.pack(ptr, 2, rows, cols, 0, 0, 0, row_stride, 1, 0, 0, 0, DTYPE_CODES[dtype])
+
+
+def ref(d: Optional[bytes]):
+    """What is passed for a `const TgTensorDesc*` argument: the packed bytes themselves (ctypes passes a
+    pointer to them and keeps them alive for the call), or None for NULL."""
     return d
-
-
-def ref(d: Optional[TensorDesc]):
-    return ctypes.byref(d) if d is not None else None
 
 
 def check_rc(rc: int) -> None:

@@ -44,7 +44,7 @@ def _need_cuda(*tensors: Optional[torch.Tensor]) -> torch.device:
 
 
 def _stream(dev: torch.device) -> int:
-    return torch.cuda.current_stream(dev).cuda_stream
+    return torch._C._cuda_getCurrentRawStream(dev.index)
 
 
 def _workspace(dev: torch.device) -> torch.Tensor:
@@ -306,7 +306,7 @@ def _pertensor(
 ) -> None:
     ws = _workspace(dev)
     rc = _lib.lib().tg_fp8_gemm_pertensor(
-        _lib.ref(_lib.desc(c2)), _lib.ref(_lib.desc(a2)), _lib.ref(_lib.desc(b2)),
+        c2 if isinstance(c2, bytes) else _lib.desc(c2), a2 if isinstance(a2, bytes) else _lib.desc(a2), _lib.desc(b2),
         scale_a.data_ptr() if scale_a is not None else 0, scale_b.data_ptr() if scale_b is not None else 0,
         float(alpha), _lib.ref(_lib.desc(bias)), float(beta), ws.data_ptr(), ws.numel(), dev.index, _stream(dev),
     )
@@ -322,7 +322,7 @@ def _scalar_f32(s: Optional[torch.Tensor], dev: torch.device, name: str) -> Opti
         raise _lib.TileGymB200Error(-6, f"{name} must hold exactly one element (per-tensor scale)")
     if s.dtype != torch.float32 or s.device != dev:
         s = s.to(device=dev, dtype=torch.float32)
-    return s.reshape(1)
+    return s  # one element: only its address is used
 
 
 def fp8_scaled_mm(
@@ -356,8 +356,9 @@ def fp8_scaled_mm(
         assert out.shape == A.shape[:-1] + (N,) and out.is_contiguous()
     if bias is not None and not bias.is_contiguous():
         bias = bias.contiguous()
-    _pertensor(out.view(M, N), A.view(M, K), B, _scalar_f32(scale_a, dev, "scale_a"),
-               _scalar_f32(scale_b, dev, "scale_b"), 1.0, bias, 0.0, dev)
+    # contiguous (..., N) / (..., K) tensors are (M, N) / (M, K) matrices: describe them without making views
+    _pertensor(_lib.desc2d(out.data_ptr(), M, N, N, out.dtype), _lib.desc2d(A.data_ptr(), M, K, K, A.dtype), B,
+               _scalar_f32(scale_a, dev, "scale_a"), _scalar_f32(scale_b, dev, "scale_b"), 1.0, bias, 0.0, dev)
     return out
 
 
