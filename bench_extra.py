@@ -148,6 +148,41 @@ def grouped_sweep(dev, fp8_peak_tflops: float):
     return rows
 
 
+def swiglu_sweep(dev):
+    """Llama-3.1-8B gate/up projection at M = 4096 with SwiGLU: the fused epilogue against the two-step path
+    (the same GEMM writing [M, 2I] bf16, then silu(gate) * up as a torch elementwise pass)."""
+    import tilegym_b200 as tg
+
+    M, I, K = 4096, 14336, 4096
+    a = torch.randn(M, K, device=dev).to(torch.float8_e4m3fn)
+    w = torch.randn(2 * I, K, device=dev, dtype=torch.bfloat16).mul_(0.02).to(torch.float8_e4m3fn)
+    sa = torch.full((1,), 3e-2, device=dev)
+    sb = torch.full((1,), 2e-4, device=dev)
+    out = torch.empty(M, I, dtype=torch.bfloat16, device=dev)
+    y = torch.empty(M, 2 * I, dtype=torch.bfloat16, device=dev)
+
+    def two_step():
+        tg.fp8_scaled_mm(a, w, sa, sb, None, torch.bfloat16, out=y)
+        torch.mul(torch.nn.functional.silu(y[:, :I]), y[:, I:], out=out)
+
+    res = {}
+    for name, fn in (("fused_us", lambda: tg.fp8_scaled_mm_swiglu(a, w, sa, sb, None, torch.bfloat16, out=out)),
+                     ("gemm_then_silu_mul_us", two_step)):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(20):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        res[name] = round(e0.elapsed_time(e1) * 1e3 / 20, 1)
+    res["shape"] = f"M={M} I={I} K={K}"
+    res["fused_tflops"] = round(2.0 * M * 2 * I * K / res["fused_us"] / 1e6, 1)
+    return res
+
+
 def run(dev, peaks):
     hbm = float(peaks["hbm_gbs"])
     fp8 = 2.0 * float(peaks["bf16_tflops"])  # kernels timed alone: burst figure
@@ -158,4 +193,5 @@ def run(dev, peaks):
         "block_scaled": block_scaled_sweep(dev, fp8, hbm),
         "grouped_block_scaled": grouped_sweep(dev, fp8),
         "quantisers": quantiser_sweep(dev, hbm),
+        "swiglu_gate_up": swiglu_sweep(dev),
     }

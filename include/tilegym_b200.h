@@ -98,6 +98,18 @@ TG_API int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc
                                 int32_t block_k, uint64_t workspace, uint64_t workspace_bytes,
                                 int32_t device_id, uint64_t stream);
 
+/* Per-tensor-scaled FP8 GEMM of a fused gate/up projection with the SwiGLU activation in its epilogue:
+ *     C[m, j] = silu(g) * u,   g = alpha*sa*sb*(A . B[row_g(j)]^T) + bias[row_g(j)],  u likewise with row_u(j)
+ * B: (N, K) e4m3, N = 2 * I a multiple of 128, whose rows alternate 32 gate rows and 32 up rows:
+ * row_g(j) = 64 * (j / 32) + j % 32, row_u(j) = row_g(j) + 32 (bias, if given, in the same order).
+ * C: (M, I) bf16 / f16 with 16-byte aligned rows.  The [M, 2I] intermediate never reaches memory.
+ * The reference computes this as two steps, matmul then silu_and_mul
+ * (src/tilegym/ops/fused_mlp.py:85-107, PartiallyFusedSwiGLUMLP.forward); it has no fused counterpart.
+ */
+TG_API int32_t tg_fp8_gemm_pertensor_swiglu(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
+                                            uint64_t scale_a, uint64_t scale_b, float alpha,
+                                            const TgTensorDesc* bias, int32_t device_id, uint64_t stream);
+
 /* Grouped (ragged, MoE-style) block-scaled GEMM: rows [m_indptr[g], m_indptr[g+1]) of A and C belong to group g
  * and use weight B[g]:
  *     C[m,n] = sum_kb  As[m,kb] * Bs[g, n/128, kb] * (A[m,kb-block] . B[g, n, kb-block])      for m in group g

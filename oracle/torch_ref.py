@@ -238,6 +238,25 @@ def ref_fp8_scaled_mm(
     return C.to(out_dtype).reshape(*A.shape[:-1], B.shape[0])
 
 
+def ref_fp8_scaled_mm_swiglu(
+    A: torch.Tensor,
+    B_interleaved: torch.Tensor,
+    scale_a: torch.Tensor,
+    scale_b: torch.Tensor,
+    bias_interleaved: Optional[torch.Tensor] = None,
+    out_dtype: torch.dtype = torch.bfloat16,
+) -> torch.Tensor:
+    """silu(gate) * up of a fused gate/up projection whose weight rows alternate 32 gate rows and 32 up rows:
+    the fp32 per-tensor GEMM above, then silu_and_mul (src/tilegym/ops/fused_mlp.py:97-102, torch semantics
+    x[..., :I] -> silu, times x[..., I:]) in fp32, one cast at the end."""
+    y = ref_fp8_scaled_mm(A, B_interleaved, scale_a, scale_b, bias_interleaved, torch.float32)
+    N = B_interleaved.shape[0]
+    y = y.reshape(-1, N // 64, 2, 32)
+    gate, up = y[:, :, 0, :], y[:, :, 1, :]
+    out = torch.nn.functional.silu(gate) * up
+    return out.reshape(*A.shape[:-1], N // 2).to(out_dtype)
+
+
 def ref_gemm_alpha_beta(
     a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, alpha: float = 1.0, beta: float = 0.0
 ) -> torch.Tensor:

@@ -53,8 +53,11 @@ def test_linear_helper_caches_quantised_module(dev):
     assert torch.nn.functional.cosine_similarity(y1.float().flatten(), h.q_proj(x).float().flatten(), dim=0) > 0.995
 
 
-def test_apply_to_llama_converts_decoder_linears(dev):
+@pytest.mark.parametrize("swiglu", [True, False])
+def test_apply_to_llama_converts_decoder_linears(dev, swiglu):
     transformers = pytest.importorskip("transformers")
+    from tilegym_b200.linear import FP8SwiGLUMLP
+
     cfg = transformers.LlamaConfig(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
                                    num_key_value_heads=2, vocab_size=320, max_position_embeddings=128)
     torch.manual_seed(0)
@@ -62,9 +65,11 @@ def test_apply_to_llama_converts_decoder_linears(dev):
     ids = torch.randint(0, 320, (2, 24), device=dev)
     with torch.no_grad():
         base = model(ids).logits.float()
-    monkey_patch.apply_tilegym_kernel_to_llama(model=model, fp8_linear=True)
+    monkey_patch.apply_tilegym_kernel_to_llama(model=model, fp8_linear=True, swiglu=swiglu)
     n_fp8 = sum(isinstance(m, FP8Linear) for m in model.modules())
-    assert n_fp8 == 2 * 7 and isinstance(model.lm_head, torch.nn.Linear)
+    n_mlp = sum(isinstance(m, FP8SwiGLUMLP) for m in model.modules())
+    # per layer q, k, v, o and either gate, up, down or one fused MLP (which holds the down projection)
+    assert (n_fp8, n_mlp) == ((2 * 5, 2) if swiglu else (2 * 7, 0)) and isinstance(model.lm_head, torch.nn.Linear)
     with torch.no_grad():
         got = model(ids).logits.float()
     cos = torch.nn.functional.cosine_similarity(base.flatten(), got.flatten(), dim=0)

@@ -14,6 +14,8 @@ from .ops import (  # noqa: F401
     per_token_group_quant_8bit,
     ragged_block_scaled_bmm,
     fp8_scaled_mm_no_alloc,
+    fp8_scaled_mm_swiglu,
+    interleave_gate_up,
     gemm_alpha_beta,
     matmul,
     quant_per_tensor,

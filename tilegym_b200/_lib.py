@@ -90,6 +90,10 @@ SIGNATURES = {
         [_P, _P, _P, _P, _P, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int32,
          ctypes.c_uint64],
     ),
+    "tg_fp8_gemm_pertensor_swiglu": (
+        ctypes.c_int32,
+        [_P, _P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_float, _P, ctypes.c_int32, ctypes.c_uint64],
+    ),
     "tg_fp8_gemm_blockscaled_grouped": (
         ctypes.c_int32,
         [_P, _P, _P, _P, _P, ctypes.c_uint64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64],

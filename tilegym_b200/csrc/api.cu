@@ -266,13 +266,16 @@ uint64_t tg_fp8_gemm_workspace_bytes(int64_t, int64_t, int64_t) { return kWsCoun
 static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B, uint64_t scale_a,
                               uint64_t scale_b, float alpha, const TgTensorDesc* bias, float beta, uint64_t workspace,
                               uint64_t workspace_bytes, const uint64_t* peer_ptrs, int32_t num_peers,
-                              int32_t device_id, uint64_t stream) {
+                              int32_t device_id, uint64_t stream, bool swiglu = false) {
   int32_t rc;
   if ((rc = check_operand(A, "A")) != TG_OK) return rc;
   if ((rc = check_operand(B, "B")) != TG_OK) return rc;
   const int64_t M = A->shape[0], K = A->shape[1], N = B->shape[0];
   if (B->shape[1] != K) return fail(TG_ERR_ARGS, "A is [M,%lld] but B is [N,%lld]: K must match", (long long)K, (long long)B->shape[1]);
-  if ((rc = check_output(C, M, N)) != TG_OK) return rc;
+  if (swiglu && N % 128 != 0) return fail(TG_ERR_ARGS, "the SwiGLU epilogue needs N (gate + up rows) to be a multiple of 128, got %lld", (long long)N);
+  // SwiGLU: every 64 accumulator columns (32 gate, 32 up) become 32 output columns
+  const int64_t N_out = swiglu ? N / 2 : N;
+  if ((rc = check_output(C, M, N_out)) != TG_OK) return rc;
   if (bias != nullptr) {
     if (bias->dtype != TG_F32 && bias->dtype != TG_BF16 && bias->dtype != TG_F16)
       return fail(TG_ERR_DTYPE, "bias must be f32, f16 or bf16");
@@ -321,8 +324,13 @@ static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, cons
   // rows are 16-byte aligned; the fused all-gather needs that path.
   const bool tma_out_ok = (C->dtype == TG_BF16 || C->dtype == TG_F16) && beta == 0.0f && (C->ptr & 15u) == 0 &&
                           ((C->strides[0] * 2) & 15) == 0;
-  const bool pair_kernel = M >= 256 && N >= 256 && env_int("TILEGYM_B200_2CTA", 1) != 0 &&
-                           getenv("TILEGYM_B200_BN") == nullptr && getenv("TILEGYM_B200_SPLITS") == nullptr;
+  const bool pair_kernel = swiglu || (M >= 256 && N >= 256 && env_int("TILEGYM_B200_2CTA", 1) != 0 &&
+                                      getenv("TILEGYM_B200_BN") == nullptr && getenv("TILEGYM_B200_SPLITS") == nullptr);
+  if (swiglu) {
+    if (!tma_out_ok) return fail(TG_ERR_ARGS, "the SwiGLU epilogue needs a bf16 / f16 output with 16-byte aligned rows");
+    small = false;  // only the CTA-pair kernel has this epilogue (it runs any M; rows past M read as zero)
+    p.flags |= 4;
+  }
   if (num_peers > 0 && !(pair_kernel && tma_out_ok))
     return fail(TG_ERR_ARGS, "the fused all-gather needs M, N >= 256, a bf16 / f16 output with 16-byte aligned rows and beta == 0");
 
@@ -374,12 +382,13 @@ static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, cons
     int tail_div = pertensor_2cta_tail_div(p.tiles_m * p.tiles_n, st.num_sms);
     tail_div = env_int("TILEGYM_B200_TAIL_DIV", tail_div);
     if (tail_div != 2 && tail_div != 4) tail_div = 1;
+    if (swiglu && tail_div == 4) tail_div = 2;  // a SwiGLU output box needs 128 accumulator columns
     CUtensorMap tmBt;
     if ((rc = make_map(&tmBt, B->ptr, N, K, B->strides[0], 128 / tail_div)) != TG_OK) return rc;
     CUtensorMap out_maps[8];
     int num_out = 0;
-    if (tma_out_ok && (num_peers > 0 || env_int("TILEGYM_B200_TMA_STORE", 1) != 0)) {
-      if ((rc = make_out_map(&out_maps[num_out++], C->ptr, M, N, C->strides[0] * 2, C->dtype)) != TG_OK) return rc;
+    if (tma_out_ok && (num_peers > 0 || swiglu || env_int("TILEGYM_B200_TMA_STORE", 1) != 0)) {
+      if ((rc = make_out_map(&out_maps[num_out++], C->ptr, M, N_out, C->strides[0] * 2, C->dtype)) != TG_OK) return rc;
       for (int i = 0; i < num_peers; ++i)
         if ((rc = make_out_map(&out_maps[num_out++], peer_ptrs[i], M, N, C->strides[0] * 2, C->dtype)) != TG_OK) return rc;
     }
@@ -426,6 +435,12 @@ int32_t tg_fp8_gemm_pertensor_allgather(const TgTensorDesc* C, const TgTensorDes
     if (peer_ptrs[i] & 15u) return fail(TG_ERR_ALIGN, "peer pointer %d is not 16-byte aligned", i);
   }
   return pertensor_impl(C, A, B, scale_a, scale_b, alpha, bias, 0.0f, 0, 0, peer_ptrs, num_peers, device_id, stream);
+}
+
+int32_t tg_fp8_gemm_pertensor_swiglu(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
+                                     uint64_t scale_a, uint64_t scale_b, float alpha, const TgTensorDesc* bias,
+                                     int32_t device_id, uint64_t stream) {
+  return pertensor_impl(C, A, B, scale_a, scale_b, alpha, bias, 0.0f, 0, 0, nullptr, 0, device_id, stream, true);
 }
 
 int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,

@@ -310,6 +310,71 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         // shared-memory buffer and leave as one bulk tensor store per destination; rows and columns past
         // M / N are clipped by the tensor map.
         const int row0 = tm * 256 + static_cast<int>(rank) * kBM + q * 32;
+        if (p.flags & 4) {
+          // SwiGLU epilogue: the weight rows alternate 32 gate rows / 32 up rows, so every 64 accumulator
+          // columns are (gate, up) for 32 output columns: out = silu(gate) * up.  Two such chunks fill one
+          // 64-column box of the [M, N/2] output.
+#pragma unroll 1
+          for (int c = 0; c < (bn >> 6); ++c) {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(t_addr + c * 64, r0);
+            tmem_ld_32x32(t_addr + c * 64 + 32, r1);
+            tmem_ld_wait();
+            if (c == (bn >> 6) - 1) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive_cluster(leader_tempty + 8 * buf);
+            }
+            if ((c & 1) == 0) {
+              if (lane == 0) tma_store_wait_read<1>();  // the store that last read this buffer has drained it
+              __syncwarp();
+            }
+            const int in_col = tn * kBN + col_off + c * 64;  // first gate column of this chunk
+            uint8_t* dst_row = my_stage + sb * kOutBufBytes + lane * 128;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              float v[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float gate = __uint_as_float(r0[8 * g + j]) * scale;
+                float up = __uint_as_float(r1[8 * g + j]) * scale;
+                if (p.bias != nullptr) {
+                  if (in_col + 8 * g + j < p.N) gate += load_bias(p.bias, p.bias_dtype, in_col + 8 * g + j);
+                  if (in_col + 32 + 8 * g + j < p.N) up += load_bias(p.bias, p.bias_dtype, in_col + 32 + 8 * g + j);
+                }
+                v[j] = __fdividef(gate, 1.0f + __expf(-gate)) * up;
+              }
+              uint4 o;
+              if (p.out_dtype == TG_BF16) {
+                o.x = pack_bf16x2(v[0], v[1]);
+                o.y = pack_bf16x2(v[2], v[3]);
+                o.z = pack_bf16x2(v[4], v[5]);
+                o.w = pack_bf16x2(v[6], v[7]);
+              } else {
+                o.x = pack_f16x2(v[0], v[1]);
+                o.y = pack_f16x2(v[2], v[3]);
+                o.z = pack_f16x2(v[4], v[5]);
+                o.w = pack_f16x2(v[6], v[7]);
+              }
+              const int chunk16 = (c & 1) * 4 + g;  // 16-byte chunk of the 128-byte staging row
+              *reinterpret_cast<uint4*>(dst_row + ((chunk16 ^ (lane & 7)) << 4)) = o;  // 128-byte swizzle
+            }
+            if (c & 1) {
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                const uint32_t src = smem_u32(my_stage + sb * kOutBufBytes);
+                const int out_col = (tn * kBN + col_off + (c - 1) * 64) >> 1;
+                for (int d = 0; d < num_out; ++d) tma_store_2d(&omaps.m[d], src, out_col, row0);
+                tma_store_commit();
+              }
+              sb ^= 1;
+            }
+          }
+          buf ^= 1;
+          if (buf == 0) aph ^= 1u;
+          continue;
+        }
 #pragma unroll 1
         for (int c = 0; c < (bn >> 6); ++c) {
           uint32_t r0[32], r1[32];

@@ -84,6 +84,34 @@ class FP8Linear(nn.Module):
         return f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, mode={self.mode}"
 
 
+class FP8SwiGLUMLP(nn.Module):
+    """down_proj(silu(gate_proj(x)) * up_proj(x)) with e4m3 weights and per-tensor scales: one fused gate/up
+    GEMM whose epilogue applies SwiGLU (the [tokens, 2 * intermediate] tensor of
+    src/tilegym/ops/fused_mlp.py:85-107 is never written), then the down GEMM.  Built from an MLP that has
+    `gate_proj`, `up_proj` and `down_proj` Linear layers (Llama, Mistral, Qwen2, ...)."""
+
+    def __init__(self, gate_proj: nn.Linear, up_proj: nn.Linear, down_proj: nn.Linear):
+        super().__init__()
+        assert gate_proj.weight.shape == up_proj.weight.shape and gate_proj.out_features % 64 == 0
+        assert (gate_proj.bias is None) == (up_proj.bias is None)
+        with torch.no_grad():
+            w = ops.interleave_gate_up(gate_proj.weight.detach(), up_proj.weight.detach())
+            q, s = ops.quant_per_tensor(w)
+            self.register_buffer("gate_up_fp8", q)
+            self.register_buffer("gate_up_scale", s)
+            if gate_proj.bias is not None:
+                self.register_buffer("gate_up_bias", ops.interleave_gate_up(gate_proj.bias.detach(), up_proj.bias.detach()))
+            else:
+                self.gate_up_bias = None
+        self.down = FP8Linear.from_linear(down_proj, "per_tensor")
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        out_dtype = x.dtype if x.dtype in (torch.bfloat16, torch.float16) else torch.bfloat16
+        xq, sx = ops.quant_per_tensor(x)
+        h = ops.fp8_scaled_mm_swiglu(xq, self.gate_up_fp8, sx, self.gate_up_scale, self.gate_up_bias, out_dtype)
+        return self.down(h)
+
+
 def _linear_fp8(self, attr_name: str, x: torch.Tensor) -> torch.Tensor:
     """Counterpart of the reference helper `_linear_cutile(self, attr_name, x)`
     (src/tilegym/transformers/olmoe/modeling_olmoe.py:50-61): runs the Linear stored at `attr_name` of a
@@ -96,16 +124,33 @@ def _linear_fp8(self, attr_name: str, x: torch.Tensor) -> torch.Tensor:
     return mod(x)
 
 
-def convert_linears(module: nn.Module, mode: str = "per_tensor", skip=("lm_head",)) -> int:
+def _is_swiglu_mlp(m: nn.Module) -> bool:
+    """A gate_proj / up_proj / down_proj MLP with a SiLU activation (Llama, Mistral, Qwen2, ...)."""
+    parts = [getattr(m, n, None) for n in ("gate_proj", "up_proj", "down_proj")]
+    if not all(isinstance(x, nn.Linear) for x in parts):
+        return False
+    gate, up, down = parts
+    act = getattr(m, "act_fn", None)
+    silu = isinstance(act, nn.SiLU) or type(act).__name__ in ("SiLUActivation", "SiLU") or act is nn.functional.silu
+    return (silu and gate.weight.shape == up.weight.shape and gate.out_features % 64 == 0
+            and gate.in_features % 16 == 0 and down.in_features % 16 == 0
+            and (gate.bias is None) == (up.bias is None))
+
+
+def convert_linears(module: nn.Module, mode: str = "per_tensor", skip=("lm_head",), fuse_swiglu: bool = False) -> int:
     """Replaces every nn.Linear under `module` (weights already on a CUDA device) by an FP8Linear,
-    except children whose name is in `skip`.  Returns the number of replaced modules."""
+    except children whose name is in `skip`.  With `fuse_swiglu` (per-tensor mode) a gate / up / down MLP
+    with a SiLU activation becomes one FP8SwiGLUMLP instead.  Returns the number of replaced Linear layers."""
     n = 0
     for name, child in list(module.named_children()):
-        if isinstance(child, nn.Linear) and name not in skip:
+        if fuse_swiglu and mode == "per_tensor" and _is_swiglu_mlp(child):
+            setattr(module, name, FP8SwiGLUMLP(child.gate_proj, child.up_proj, child.down_proj))
+            n += 3
+        elif isinstance(child, nn.Linear) and name not in skip:
             ok_block = child.in_features % 128 == 0
             if child.in_features % 16 == 0 and (mode == "per_tensor" or ok_block):
                 setattr(module, name, FP8Linear.from_linear(child, mode))
                 n += 1
         else:
-            n += convert_linears(child, mode, skip)
+            n += convert_linears(child, mode, skip, fuse_swiglu)
     return n

@@ -27,36 +27,37 @@ logger = logging.getLogger("tilegym_b200")
 
 # model_type -> default FP8 mode (DeepSeek checkpoints ship 128x128 block scales)
 _DEFAULT_MODE = {"deepseek_v2": "block"}
-_pending: Dict[str, str] = {}  # model types whose models get converted on first forward
+_pending: Dict[str, tuple] = {}  # model types whose models get converted on first forward
 
 
-def convert_model(model: nn.Module, mode: str = "per_tensor") -> int:
-    """Converts the Linear layers of a loaded model (on a CUDA device); keeps `lm_head` in its dtype."""
-    n = convert_linears(model, mode)
+def convert_model(model: nn.Module, mode: str = "per_tensor", fuse_swiglu: bool = False) -> int:
+    """Converts the Linear layers of a loaded model (on a CUDA device); keeps `lm_head` in its dtype.  With
+    `fuse_swiglu` the SiLU MLPs run their gate / up projection and the activation as one kernel."""
+    n = convert_linears(model, mode, fuse_swiglu=fuse_swiglu)
     logger.info("tilegym_b200: %d nn.Linear modules now run the FP8 GEMM (%s scales)", n, mode)
     return n
 
 
-def _first_forward_hook(mode: str) -> Callable:
+def _first_forward_hook(mode: str, fuse_swiglu: bool = False) -> Callable:
     def hook(module, args, kwargs):
         if not getattr(module, "_tilegym_fp8_done", False):
             object.__setattr__(module, "_tilegym_fp8_done", True)
-            convert_model(module, mode)
+            convert_model(module, mode, fuse_swiglu)
         return None
 
     return hook
 
 
-def _apply(model_type: str, model, fp8_linear: bool, fp8_mode: Optional[str]) -> None:
+def _apply(model_type: str, model, fp8_linear: bool, fp8_mode: Optional[str], fuse_swiglu: bool = False) -> None:
     if not fp8_linear:
         return
     mode = fp8_mode or _DEFAULT_MODE.get(model_type, "per_tensor")
     if model is not None:
-        convert_model(model, mode)
+        convert_model(model, mode, fuse_swiglu)
         return
     # Before model initialisation: convert each model of this type when it first runs (its weights are
     # loaded and placed by then).
-    _pending[model_type] = mode
+    _pending[model_type] = (mode, fuse_swiglu)
     try:
         from transformers import PreTrainedModel
     except Exception as exc:  # transformers is only needed for the pre-initialisation form
@@ -69,7 +70,7 @@ def _apply(model_type: str, model, fp8_linear: bool, fp8_mode: Optional[str]) ->
             mt = getattr(getattr(self, "config", None), "model_type", None)
             if mt in _pending and not getattr(self, "_tilegym_fp8_hooked", False) and hasattr(self, "lm_head"):
                 object.__setattr__(self, "_tilegym_fp8_hooked", True)
-                self.register_forward_pre_hook(_first_forward_hook(_pending[mt]), with_kwargs=True)
+                self.register_forward_pre_hook(_first_forward_hook(*_pending[mt]), with_kwargs=True)
             return out
 
         PreTrainedModel.post_init = post_init
@@ -80,9 +81,11 @@ def _make(model_type: str):
     def apply_fn(rope: bool = True, rms_norm: bool = True, swiglu: bool = True, attn: bool = True, model=None,
                  use_cutile: bool = False, fp8_linear: bool = False, fp8_mode: Optional[str] = None) -> None:
         for flag, on in (("rope", rope), ("rms_norm", rms_norm), ("swiglu", swiglu), ("attn", attn)):
-            if on:
+            if on and not (flag == "swiglu" and fp8_linear):
                 logger.debug("tilegym_b200: %s=True accepted; that kernel is not part of this library", flag)
-        _apply(model_type, model, fp8_linear, fp8_mode)
+        # swiglu=True, the reference's switch for its fused SwiGLU MLP, selects the fused gate/up + SiLU*mul
+        # kernel here when the FP8 path is on
+        _apply(model_type, model, fp8_linear, fp8_mode, fuse_swiglu=swiglu)
 
     apply_fn.__name__ = f"apply_tilegym_kernel_to_{model_type}"
     apply_fn.__doc__ = (

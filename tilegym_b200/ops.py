@@ -362,6 +362,58 @@ def fp8_scaled_mm(
     return out
 
 
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """Stacks a gate and an up projection (weights [I, K] or biases [I], I a multiple of 32) in the row order
+    `fp8_scaled_mm_swiglu` expects: 32 gate rows, 32 up rows, 32 gate rows, ...  Done once, at load time."""
+    assert gate.shape == up.shape and gate.shape[0] % 32 == 0
+    blocks = gate.shape[0] // 32
+    g = gate.reshape(blocks, 32, *gate.shape[1:])
+    u = up.reshape(blocks, 32, *up.shape[1:])
+    return torch.stack((g, u), dim=1).reshape(2 * gate.shape[0], *gate.shape[1:]).contiguous()
+
+
+def fp8_scaled_mm_swiglu(
+    A: torch.Tensor,
+    B: torch.Tensor,
+    scale_a: Optional[torch.Tensor] = None,
+    scale_b: Optional[torch.Tensor] = None,
+    bias: Optional[torch.Tensor] = None,
+    out_dtype: torch.dtype = torch.bfloat16,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """silu(gate) * up of a fused gate/up projection, computed in the GEMM epilogue.
+
+    A (..., K) e4m3; B (2*I, K) e4m3 with rows ordered by `interleave_gate_up`; per-tensor scales as in
+    `fp8_scaled_mm`; bias (2*I,) in the same row order or None.  Returns (..., I) in bf16 / f16: the
+    [..., 2*I] intermediate of matmul + silu_and_mul (src/tilegym/ops/fused_mlp.py:85-107) is never written.
+    """
+    dev = _need_cuda(A, B)
+    assert A.dtype == _FP8 and B.dtype == _FP8, "A and B must be float8_e4m3fn"
+    assert B.ndim == 2 and A.shape[-1] == B.shape[-1] and B.shape[0] % 128 == 0
+    if out_dtype not in (torch.bfloat16, torch.float16):
+        raise _lib.TileGymB200Error(-6, f"out_dtype {out_dtype} is not bf16 or f16")
+    if not A.is_contiguous():
+        A = A.contiguous()
+    if not B.is_contiguous():
+        B = B.contiguous()
+    N, K = B.shape
+    M = A.numel() // K
+    if out is None:
+        out = A.new_empty(A.shape[:-1] + (N // 2,), dtype=out_dtype)
+    else:
+        assert out.shape == A.shape[:-1] + (N // 2,) and out.is_contiguous()
+    if bias is not None and not bias.is_contiguous():
+        bias = bias.contiguous()
+    sa, sb = _scalar_f32(scale_a, dev, "scale_a"), _scalar_f32(scale_b, dev, "scale_b")
+    rc = _lib.lib().tg_fp8_gemm_pertensor_swiglu(
+        _lib.desc2d(out.data_ptr(), M, N // 2, N // 2, out.dtype), _lib.desc2d(A.data_ptr(), M, K, K, A.dtype),
+        _lib.desc(B), sa.data_ptr() if sa is not None else 0, sb.data_ptr() if sb is not None else 0, 1.0,
+        _lib.desc(bias), dev.index, _stream(dev),
+    )
+    _lib.check_rc(rc)
+    return out
+
+
 def fp8_scaled_mm_no_alloc(
     A: torch.Tensor,
     B: torch.Tensor,
