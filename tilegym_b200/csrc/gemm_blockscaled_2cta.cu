@@ -7,7 +7,8 @@
 // warps per CTA (three per TMEM lane quadrant, 64 columns each) with packed fp32x2 FMAs:
 // acc += (As[m,kb] * Bs[nb,kb]) * partial, exact for arbitrary fp32 scales.
 // Roles per CTA: warp 0 TMA producer, warp 1 MMA issuer (leader CTA only) and TMEM owner,
-// warps 2..17 promotion + store.
+// warps 2..13 promotion + store.  Experimental (opt-in, TILEGYM_B200_BS_PAIR=1): two TMEM buffers cannot hide the
+// cross-CTA release chain, so it runs slower than the single-CTA 128 x 256 kernel that is the default.
 #include "tg_gemm_common.cuh"
 
 namespace tg {
