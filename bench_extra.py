@@ -183,6 +183,41 @@ def swiglu_sweep(dev):
     return res
 
 
+def mlp_block_sweep(dev):
+    """One Llama-3.1-8B MLP block (hidden 4096, intermediate 14336) on 4096 tokens, bf16 in and out:
+    FP8SwiGLUMLP (activation quantiser, fused gate/up + SwiGLU GEMM, quantiser, down GEMM) against the same
+    block in bf16 through torch (three cuBLAS GEMMs and an elementwise pass)."""
+    from tilegym_b200.linear import FP8SwiGLUMLP
+
+    H, I, M = 4096, 14336, 4096
+    torch.manual_seed(0)
+    gate, up, down = (torch.nn.Linear(H, I, bias=False), torch.nn.Linear(H, I, bias=False),
+                      torch.nn.Linear(I, H, bias=False))
+    gate, up, down = [m.to(dev).to(torch.bfloat16) for m in (gate, up, down)]
+    x = torch.randn(M, H, device=dev, dtype=torch.bfloat16)
+    mlp = FP8SwiGLUMLP(gate, up, down)
+
+    def ref():
+        return down(torch.nn.functional.silu(gate(x)) * up(x))
+
+    res = {"shape": f"tokens={M} hidden={H} intermediate={I}"}
+    with torch.no_grad():
+        for name, fn in (("fp8_swiglu_mlp_us", lambda: mlp(x)), ("torch_bf16_mlp_us", ref)):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            res[name] = round(e0.elapsed_time(e1) * 1e3 / 10, 1)
+        y, r = mlp(x).float(), ref().float()
+        res["rel_err_vs_bf16"] = round(float((y - r).abs().max() / r.abs().max()), 4)
+    return res
+
+
 def run(dev, peaks):
     hbm = float(peaks["hbm_gbs"])
     fp8 = 2.0 * float(peaks["bf16_tflops"])  # kernels timed alone: burst figure
@@ -194,4 +229,5 @@ def run(dev, peaks):
         "grouped_block_scaled": grouped_sweep(dev, fp8),
         "quantisers": quantiser_sweep(dev, hbm),
         "swiglu_gate_up": swiglu_sweep(dev),
+        "llama8b_mlp_block": mlp_block_sweep(dev),
     }
