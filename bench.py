@@ -435,8 +435,41 @@ def run_one(args):
     kind, dims = args.one.split(":")
     M, N, K = (int(v) for v in dims.split(","))
     dev = torch.device("cuda:0")
+    if kind in ("actquant", "groupquant", "quantpt", "dequant"):
+        # quantisers: M x N elements; K is the group size (groupquant) and ignored otherwise
+        x = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
+        if kind == "actquant":
+            fn, nbytes = (lambda: tg.act_quant(x)), 3 * M * N + 4 * M * N // 128
+        elif kind == "groupquant":
+            fn, nbytes = (lambda: tg.per_token_group_quant_8bit(x, K)), 3 * M * N + 4 * M * N // K
+        elif kind == "quantpt":
+            fn, nbytes = (lambda: tg.quant_per_tensor(x)), 5 * M * N
+        else:
+            q = x.to(torch.float8_e4m3fn)
+            s = torch.rand((M + 127) // 128, (N + 127) // 128, device=dev) + 0.5
+            fn, nbytes = (lambda: tg.weight_dequant(q, s)), 3 * M * N
+        sec = timed(fn, args.steps, args.warmup, dev)
+        print(json.dumps({"one": args.one, "us_per_launch": sec / args.steps * 1e6,
+                          "gbs": nbytes * args.steps / sec / 1e9}), flush=True)
+        return
+    if kind == "grouped":
+        # M rows in 8 equal groups (M a multiple of 8), each with its own [N, K] weight
+        G = 8
+        a8 = torch.randn(M, K, device=dev).to(torch.float8_e4m3fn)
+        b8 = torch.randn(G, N, K, device=dev, dtype=torch.bfloat16).mul_(0.02).to(torch.float8_e4m3fn)
+        As = torch.rand(M, (K + 127) // 128, device=dev) + 0.5
+        Bs = torch.rand(G, (N + 127) // 128, (K + 127) // 128, device=dev) + 0.5
+        ind = (torch.arange(G + 1, device=dev) * (M // G)).to(torch.int32)
+        fn = lambda: tg.ragged_block_scaled_bmm(a8, b8, As, Bs, ind, M // G)  # noqa: E731
+        sec = timed(fn, args.steps, args.warmup, dev)
+        print(json.dumps({"one": args.one, "us_per_launch": sec / args.steps * 1e6,
+                          "tflops": 2.0 * M * N * K * args.steps / sec / 1e12}), flush=True)
+        return
     a8, b8, sa, sb = make_case(M, N, K, dev, 1)
-    if kind == "pertensor":
+    if kind == "swiglu":
+        out = torch.empty(M, N // 2, dtype=torch.bfloat16, device=dev)
+        fn = lambda: tg.fp8_scaled_mm_swiglu(a8, b8, sa, sb, None, torch.bfloat16, out=out)  # noqa: E731
+    elif kind == "pertensor":
         out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
         fn = lambda: tg.fp8_scaled_mm(a8, b8, sa, sb, None, torch.bfloat16, out=out)  # noqa: E731
     elif kind == "blockscaled":
@@ -444,7 +477,7 @@ def run_one(args):
         Bs = torch.rand((N + 127) // 128, (K + 127) // 128, device=dev) + 0.5
         fn = lambda: tg.w8a8_block_fp8_matmul(a8, b8, As, Bs, [128, 128], torch.bfloat16)  # noqa: E731
     else:
-        raise SystemExit("--one KIND must be pertensor or blockscaled")
+        raise SystemExit("--one KIND must be pertensor, swiglu, blockscaled, grouped, actquant, groupquant, quantpt or dequant")
     sec = timed(fn, args.steps, args.warmup, dev)
     print(json.dumps({"one": args.one, "us_per_launch": sec / args.steps * 1e6,
                       "tflops": 2.0 * M * N * K * args.steps / sec / 1e12,
@@ -461,7 +494,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--chunks", type=int, default=8, help="N>1: M-slabs whose all-gather overlaps the next slab's GEMM")
     ap.add_argument("--one", default=None, metavar="KIND:M,N,K",
-                    help="profiling aid: run one GEMM (pertensor or blockscaled) of the given size steps+warmup times")
+                    help="profiling aid: run one kernel steps+warmup times. GEMMs pertensor / swiglu / blockscaled / "
+                         "grouped (M rows in 8 groups); quantisers actquant / groupquant (K = group size) / quantpt / "
+                         "dequant on an M x N tensor")
     args = ap.parse_args()
     if args.one:
         run_one(args)
