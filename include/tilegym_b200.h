@@ -110,6 +110,15 @@ TG_API int32_t tg_fp8_gemm_pertensor_swiglu(const TgTensorDesc* C, const TgTenso
                                             uint64_t scale_a, uint64_t scale_b, float alpha,
                                             const TgTensorDesc* bias, int32_t device_id, uint64_t stream);
 
+/* Dense bf16 / f16 GEMM (no quantisation), fp32 accumulation on the same CTA-pair tcgen05 kernel (kind::f16):
+ *     C[M,N] = alpha * (A[M,K] . B[N,K]^T) + bias[N] + beta * C[M,N]
+ * A, B: both bf16 or both f16, row-major, contiguous rows, 16-byte aligned base and row pitch (K % 8 == 0);
+ * C: bf16 / f16 / f32.  The unquantised path of tilegym.ops.matmul (src/tilegym/ops/ops.py:715-741,
+ * src/tilegym/ops/cutile/matmul.py:421-455) with B given K-major ([N, K], i.e. trans_b).
+ */
+TG_API int32_t tg_gemm_dense16(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B, float alpha,
+                               const TgTensorDesc* bias, float beta, int32_t device_id, uint64_t stream);
+
 /* Grouped (ragged, MoE-style) block-scaled GEMM: rows [m_indptr[g], m_indptr[g+1]) of A and C belong to group g
  * and use weight B[g]:
  *     C[m,n] = sum_kb  As[m,kb] * Bs[g, n/128, kb] * (A[m,kb-block] . B[g, n, kb-block])      for m in group g

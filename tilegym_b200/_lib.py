@@ -94,6 +94,10 @@ SIGNATURES = {
         ctypes.c_int32,
         [_P, _P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_float, _P, ctypes.c_int32, ctypes.c_uint64],
     ),
+    "tg_gemm_dense16": (
+        ctypes.c_int32,
+        [_P, _P, _P, ctypes.c_float, _P, ctypes.c_float, ctypes.c_int32, ctypes.c_uint64],
+    ),
     "tg_fp8_gemm_blockscaled_grouped": (
         ctypes.c_int32,
         [_P, _P, _P, _P, _P, ctypes.c_uint64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64],

@@ -443,6 +443,88 @@ int32_t tg_fp8_gemm_pertensor_swiglu(const TgTensorDesc* C, const TgTensorDesc* 
   return pertensor_impl(C, A, B, scale_a, scale_b, alpha, bias, 0.0f, 0, 0, nullptr, 0, device_id, stream, true);
 }
 
+// Dense bf16 / f16 GEMM on the CTA-pair kernel (tcgen05 kind::f16): the unquantised path of `matmul`.
+int32_t tg_gemm_dense16(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B, float alpha,
+                        const TgTensorDesc* bias, float beta, int32_t device_id, uint64_t stream) {
+  int32_t rc;
+  if (A == nullptr || B == nullptr) return fail(TG_ERR_NULL, "a descriptor is null");
+  if ((A->dtype != TG_BF16 && A->dtype != TG_F16) || B->dtype != A->dtype)
+    return fail(TG_ERR_DTYPE, "A and B must both be bf16 or both f16");
+  if (A->ndim != 2 || B->ndim != 2) return fail(TG_ERR_ARGS, "A and B must be 2-D");
+  const int64_t M = A->shape[0], K = A->shape[1], N = B->shape[0];
+  if (K <= 0 || B->shape[1] != K) return fail(TG_ERR_ARGS, "A is [M,%lld] but B is [N,%lld]: K must match", (long long)K, (long long)B->shape[1]);
+  if (A->strides[1] != 1 || B->strides[1] != 1 || A->strides[0] < K || B->strides[0] < K)
+    return fail(TG_ERR_ARGS, "A and B rows must be contiguous");
+  if ((M > 0 && A->ptr == 0) || (N > 0 && B->ptr == 0)) return fail(TG_ERR_NULL, "data pointer is null");
+  if ((A->ptr & 15u) || (B->ptr & 15u) || ((A->strides[0] * 2) & 15) || ((B->strides[0] * 2) & 15))
+    return fail(TG_ERR_ALIGN, "A and B need 16-byte aligned bases and row pitches (K %% 8 == 0) for TMA");
+  if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) return fail(TG_ERR_ARGS, "problem is too large");
+  if ((rc = check_output(C, M, N)) != TG_OK) return rc;
+  if (bias != nullptr) {
+    if (bias->dtype != TG_F32 && bias->dtype != TG_BF16 && bias->dtype != TG_F16) return fail(TG_ERR_DTYPE, "bias must be f32, f16 or bf16");
+    if (bias->ndim != 1 || bias->shape[0] != N || bias->strides[0] != 1) return fail(TG_ERR_ARGS, "bias must be a contiguous vector of N elements");
+    if (bias->ptr == 0 && N > 0) return fail(TG_ERR_NULL, "bias data pointer is null");
+  }
+  if (M == 0 || N == 0) return TG_OK;
+
+  DeviceGuard guard(device_id);
+  if (guard.err != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TG_ERR_DEVICE, "cannot select CUDA device %d", device_id);
+  }
+  if ((rc = init_device(device_id)) != TG_OK) return rc;
+  const DeviceState& st = g_dev[device_id];
+  cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = static_cast<int32_t>(M);
+  p.N = static_cast<int32_t>(N);
+  p.K = static_cast<int32_t>(K);
+  p.num_kb = static_cast<int32_t>((K + 63) / 64);  // a k-block is one 128-byte row of 64 elements
+  p.tiles_m = static_cast<int32_t>((M + 255) / 256);
+  p.tiles_n = static_cast<int32_t>((N + 255) / 256);
+  p.C = reinterpret_cast<void*>(C->ptr);
+  p.ldc = C->strides[0];
+  p.out_dtype = C->dtype;
+  p.alpha = alpha;
+  p.beta = beta;
+  p.bias = bias ? reinterpret_cast<const void*>(bias->ptr) : nullptr;
+  p.bias_dtype = bias ? bias->dtype : TG_F32;
+  p.splits = 1;
+  p.kb_per_split = p.num_kb;
+  p.status = st.status;
+  p.flags = (A->dtype == TG_BF16) ? 8 : 16;
+
+  auto map16 = [&](CUtensorMap* map, const TgTensorDesc* t, int64_t rows, int box_rows) -> int32_t {
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(t->strides[0] * 2)};
+    cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = g_encode(map, t->dtype == TG_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                          reinterpret_cast<void*>(t->ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? TG_OK : fail(TG_ERR_ARGS, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  };
+  int group_m = static_cast<int>((24ll << 20) / (512ll * K));
+  if (group_m < 2) group_m = 2;
+  if (group_m > p.tiles_m) group_m = p.tiles_m;
+  int tail_div = pertensor_2cta_tail_div(p.tiles_m * p.tiles_n, st.num_sms);
+  if (tail_div != 2 && tail_div != 4) tail_div = 1;
+  CUtensorMap tmA, tmB, tmBt;
+  if ((rc = map16(&tmA, A, M, 128)) != TG_OK) return rc;
+  if ((rc = map16(&tmB, B, N, 128)) != TG_OK) return rc;
+  if ((rc = map16(&tmBt, B, N, 128 / tail_div)) != TG_OK) return rc;
+  const bool tma_out_ok = (C->dtype == TG_BF16 || C->dtype == TG_F16) && beta == 0.0f && (C->ptr & 15u) == 0 &&
+                          ((C->strides[0] * 2) & 15) == 0;
+  CUtensorMap out_maps[8];
+  int num_out = 0;
+  if (tma_out_ok && (rc = make_out_map(&out_maps[num_out++], C->ptr, M, N, C->strides[0] * 2, C->dtype)) != TG_OK) return rc;
+  cudaError_t e = launch_gemm_pertensor_2cta(tmA, tmB, tmBt, out_maps, num_out, p, group_m, tail_div, st.num_sms, cs);
+  if (e != cudaSuccess) return fail(TG_ERR_LAUNCH, "dense GEMM launch failed: %s", cudaGetErrorString(e));
+  return TG_OK;
+}
+
 int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
                                         const TgTensorDesc* As, const TgTensorDesc* Bs, uint64_t m_indptr,
                                         int32_t block_n, int32_t block_k, int32_t device_id, uint64_t stream) {

@@ -84,6 +84,18 @@ __device__ __forceinline__ void mma_f8f6f4_pair(uint32_t d_tmem, uint64_t adesc,
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// 16-bit operands (bf16 / f16, K = 16 per instruction): the dense, unquantised GEMM runs the same kernel
+__device__ __forceinline__ void mma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive (count 1) on the barrier at `bar_cluster_addr` once all tcgen05 operations issued so far by
 // this thread, for the CTA pair, have completed.
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster_addr) {
@@ -132,6 +144,9 @@ __device__ __forceinline__ void decode_unit(int u, const GemmParams& p, const Pa
   pair_tile_coords(t, p.tiles_m, p.tiles_n, plan.group_m, tm, tn);
 }
 
+// kDense16: bf16 / f16 operands (kind::f16) instead of e4m3 (kind::f8f6f4); a compile-time switch, because the
+// MMA warp's issue loop is sensitive to any extra control flow.
+template <bool kDense16>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     tg_fp8_gemm_pertensor_2cta_kernel(const __grid_constant__ CUtensorMap tmA,
                                       const __grid_constant__ CUtensorMap tmB,
@@ -206,6 +221,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         const int b_row = tn * kBN + col_off + static_cast<int>(rank) * (bn >> 1);
         const CUtensorMap* mapB = (bn == kBN) ? &tmB : &tmBt;  // the slice map boxes bn / 2 rows
         const uint32_t pair_tx = 2u * static_cast<uint32_t>(kABytes + (bn >> 1) * kBK);
+        // a k-block is one 128-byte swizzle row: 128 e4m3 or 64 bf16 / f16 elements (flags bits 3, 4)
+        constexpr int kb_elems = kDense16 ? kBK / 2 : kBK;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag))) {
             report_timeout(p.status, kRoleProducer * 1000 + 31);
@@ -214,8 +231,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
           }
           if (elected) {
             if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, pair_tx);  // both CTAs' bytes
-            tma_load_2d_pair(a_base + s * kABytes, &tmA, leader_full + 8 * s, kb * kBK, a_row);
-            tma_load_2d_pair(b_base + s * kBBytes, mapB, leader_full + 8 * s, kb * kBK, b_row);
+            tma_load_2d_pair(a_base + s * kABytes, &tmA, leader_full + 8 * s, kb * kb_elems, a_row);
+            tma_load_2d_pair(b_base + s * kBBytes, mapB, leader_full + 8 * s, kb * kb_elems, b_row);
           }
           __syncwarp();
           if (++s == S) {
@@ -240,7 +257,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       bool ok = true;
       for (int u = pair_id; u < num_units && ok; u += num_pairs) {
         const int bn = (u < plan.full_tiles) ? kBN : kBN / plan.tail_div;
-        const uint32_t idesc = make_idesc_e4m3_f32(256, bn);
+        // e4m3: A / B format fields 0; 16-bit operands: format 0 = f16, 1 = bf16 in bits [7,10) and [10,13)
+        const uint32_t fmt16 = (kDense16 && (p.flags & 8)) ? ((1u << 7) | (1u << 10)) : 0u;
+        constexpr bool dense16 = kDense16;
+        const uint32_t idesc = make_idesc_e4m3_f32(256, bn) | fmt16;
         if (!__all_sync(0xffffffffu, mbar_wait(bar_tempty + 8 * buf, aph ^ 1u, abort_flag))) {
           report_timeout(p.status, kRoleMma * 1000 + 31);
           break;
@@ -258,8 +278,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
           const uint64_t bdesc = make_kmajor_sw128_desc(b_base + s * kBBytes);
           if (elected) {
 #pragma unroll
-            for (int k = 0; k < kBK / kUmmaK; ++k) {
-              mma_f8f6f4_pair(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < kBK / kUmmaK; ++k) {  // four 32-byte K steps either way
+              if (dense16)
+                mma_f16_pair(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+              else
+                mma_f8f6f4_pair(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
             }
             tc_commit_pair(bar_empty + 8 * s);   // this CTA's stage is free again ...
             tc_commit_pair(peer_empty + 8 * s);  // ... and so is the peer's
@@ -484,8 +507,11 @@ cudaError_t launch_gemm_pertensor_2cta(const CUtensorMap& tmA, const CUtensorMap
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(tg_fp8_gemm_pertensor_2cta_kernel,
+    cudaError_t e = cudaFuncSetAttribute(tg_fp8_gemm_pertensor_2cta_kernel<false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(tg_fp8_gemm_pertensor_2cta_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               kSmemBytes);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
@@ -497,8 +523,12 @@ cudaError_t launch_gemm_pertensor_2cta(const CUtensorMap& tmA, const CUtensorMap
   plan.full_tiles = (plan.tail_div == 1) ? tiles : tiles - tiles % pairs;
   plan.num_units = plan.full_tiles + (tiles - plan.full_tiles) * plan.tail_div;
   if (plan.num_units < pairs) pairs = plan.num_units;
-  tg_fp8_gemm_pertensor_2cta_kernel<<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmBt, omaps, num_out, p,
-                                                                                  plan);
+  if (p.flags & 24)  // bf16 / f16 operands
+    tg_fp8_gemm_pertensor_2cta_kernel<true><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmBt, omaps, num_out,
+                                                                                         p, plan);
+  else
+    tg_fp8_gemm_pertensor_2cta_kernel<false><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmBt, omaps,
+                                                                                          num_out, p, plan);
   return cudaGetLastError();
 }
 

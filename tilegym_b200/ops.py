@@ -496,8 +496,9 @@ def matmul(
     Tuning kwargs and `backend=` are accepted and ignored.
     """
     dev = _need_cuda(a, b)
-    if a.dtype != _FP8 or b.dtype != _FP8:
-        raise NotImplementedError("tilegym_b200.matmul implements the float8_e4m3fn path only")
+    dense16 = a.dtype in (torch.bfloat16, torch.float16) and b.dtype == a.dtype
+    if not dense16 and (a.dtype != _FP8 or b.dtype != _FP8):
+        raise NotImplementedError("tilegym_b200.matmul implements float8_e4m3fn, bfloat16 and float16 inputs")
     if trans_a:
         a = a.t()
     if not a.is_contiguous():
@@ -509,6 +510,14 @@ def matmul(
     N = bt.shape[0]
     assert bt.shape[1] == K, "incompatible dimensions"
     out_dtype = kwargs.pop("out_dtype", None)
+    if dense16:
+        # unquantised path (what the reference's Linear patch calls today): tcgen05 kind::f16, fp32 accumulate,
+        # output in the input dtype (src/tilegym/ops/cutile/matmul.py:446)
+        c = torch.empty((M, N), dtype=a.dtype if out_dtype is None else out_dtype, device=dev)
+        rc = _lib.lib().tg_gemm_dense16(_lib.desc(c), _lib.desc(a), _lib.desc(bt), 1.0, None, 0.0, dev.index,
+                                        _stream(dev))
+        _lib.check_rc(rc)
+        return c
     c = torch.empty((M, N), dtype=torch.float32 if out_dtype is None else out_dtype, device=dev)
     _pertensor(c, a, bt, None, None, 1.0, None, 0.0, dev)
     if out_dtype is None:
