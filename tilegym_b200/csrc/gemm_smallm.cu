@@ -71,6 +71,68 @@ __device__ __forceinline__ void smallm_store(const GemmParams& p, int m, int64_t
   }
 }
 
+// With four epilogue warps per CTA nothing hides a branch: the per-element dispatch of smallm_store costs about a
+// hundred cycles per stored value.  The helpers below decide output type and beta once per thread and leave
+// straight-line convert + store sequences.
+template <typename T>
+__device__ __forceinline__ T smallm_cast(float v);
+template <>
+__device__ __forceinline__ __nv_bfloat16 smallm_cast<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+template <>
+__device__ __forceinline__ __half smallm_cast<__half>(float v) {
+  return __float2half_rn(v);
+}
+template <>
+__device__ __forceinline__ float smallm_cast<float>(float v) {
+  return v;
+}
+
+// Column n of the output (one value per activation row m < mv) from this thread's accumulators.
+template <int MP, typename T>
+__device__ __forceinline__ void smallm_store_column_as(T* c, int64_t ldc, const float (&acc)[MP], int mv, float scale,
+                                                       float bias) {
+#pragma unroll
+  for (int m = 0; m < MP; ++m)
+    if (m < mv) c[m * ldc] = smallm_cast<T>(fmaf(acc[m], scale, bias));
+}
+
+template <int MP>
+__device__ __forceinline__ void smallm_store_column(const GemmParams& p, int64_t n, const float (&acc)[MP], int mv,
+                                                    float scale, float bias) {
+  if (p.beta != 0.f) {
+#pragma unroll
+    for (int m = 0; m < MP; ++m)
+      if (m < mv) smallm_store(p, m, n, fmaf(acc[m], scale, bias));
+  } else if (p.out_dtype == TG_BF16) {
+    smallm_store_column_as<MP>(reinterpret_cast<__nv_bfloat16*>(p.C) + n, p.ldc, acc, mv, scale, bias);
+  } else if (p.out_dtype == TG_F16) {
+    smallm_store_column_as<MP>(reinterpret_cast<__half*>(p.C) + n, p.ldc, acc, mv, scale, bias);
+  } else {
+    smallm_store_column_as<MP>(reinterpret_cast<float*>(p.C) + n, p.ldc, acc, mv, scale, bias);
+  }
+}
+
+// Cluster reduction, owner side: rows rank, rank + splits, ... of the output, each the sum in split order of the
+// partial rows the peers pushed into `inbox` (slot [split][j], 128 floats per row).  The loads of one row are
+// issued together.
+template <typename T>
+__device__ __forceinline__ void smallm_reduce_rows_as(T* c, int64_t ldc, const float* inbox_col, int rank, int splits,
+                                                      int rpr, int mv, float scale, float bias) {
+  for (int j = 0; j * splits + rank < mv; ++j) {
+    const float* src = inbox_col + j * kBM;
+    float v[8];
+#pragma unroll
+    for (int s2 = 0; s2 < 8; ++s2) v[s2] = (s2 < splits) ? src[s2 * rpr * kBM] : 0.f;
+    float sum = v[0];
+#pragma unroll
+    for (int s2 = 1; s2 < 8; ++s2)
+      if (s2 < splits) sum += v[s2];  // split order: bit-stable
+    c[static_cast<int64_t>(j * splits + rank) * ldc] = smallm_cast<T>(fmaf(sum, scale, bias));
+  }
+}
+
 __device__ __forceinline__ uint32_t sm_cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -275,11 +337,7 @@ __global__ void __launch_bounds__(kThreads, 2)
   }
 
   if (p.splits == 1) {
-    if (have_acc && n_ok) {
-#pragma unroll
-      for (int m = 0; m < MP; ++m)
-        if (m < mv) smallm_store(p, m, n, fmaf(acc[m], scale, bias));
-    }
+    if (have_acc && n_ok) smallm_store_column<MP>(p, n, acc, mv, scale, bias);
   } else if constexpr (CLUSTER) {
     // Output row m is finished by the CTA of rank m % splits; partial row m of split sp goes to slot
     // [sp][m / splits] of that CTA's inbox.  rows_per_rank = ceil(mv / splits).
@@ -288,20 +346,14 @@ __global__ void __launch_bounds__(kThreads, 2)
     sm_cluster_wait();  // every CTA of the cluster has started: its shared memory may be written
     if (have_acc && n_local < p.tile_rows) {
       const uint32_t inbox_addr = smem_u32(inbox) + static_cast<uint32_t>((sp * rpr) * kBM + n_local) * 4u;
-      uint32_t peer[8];
-#pragma unroll
-      for (int r = 0; r < 8; ++r) peer[r] = sm_map_to_cta(inbox_addr, r < p.splits ? r : 0);
-      int r = 0, j = 0;  // m = j * splits + r
+      uint32_t r = 0, row_addr = inbox_addr;  // m = j * splits + r; row_addr = slot [sp][j] in the owner's inbox
 #pragma unroll
       for (int m = 0; m < MP; ++m) {
         if (m < mv) {
-          uint32_t dst = peer[0];
-#pragma unroll
-          for (int t = 1; t < 8; ++t) dst = (r == t) ? peer[t] : dst;
-          sm_st_cluster_f32(dst + static_cast<uint32_t>(j) * (kBM * 4u), acc[m]);
-          if (++r == p.splits) {
+          sm_st_cluster_f32(sm_map_to_cta(row_addr, r), acc[m]);
+          if (++r == static_cast<uint32_t>(p.splits)) {
             r = 0;
-            ++j;
+            row_addr += kBM * 4u;
           }
         }
       }
@@ -313,11 +365,20 @@ __global__ void __launch_bounds__(kThreads, 2)
     if (threadIdx.x == 64) TG_STAMP(7);
     if (n_ok) {
       const int rank = static_cast<int>(sm_cluster_ctarank());
-      for (int j = 0; j * p.splits + rank < mv; ++j) {
-        const float* src = inbox + j * kBM + n_local;
-        float sum = src[0];
-        for (int s2 = 1; s2 < p.splits; ++s2) sum += src[s2 * rpr * kBM];  // split order: bit-stable
-        smallm_store(p, j * p.splits + rank, n, fmaf(sum, scale, bias));
+      const float* col = inbox + n_local;
+      if (p.beta != 0.f) {
+        for (int j = 0; j * p.splits + rank < mv; ++j) {
+          const float* src = col + j * kBM;
+          float sum = src[0];
+          for (int s2 = 1; s2 < p.splits; ++s2) sum += src[s2 * rpr * kBM];  // split order: bit-stable
+          smallm_store(p, j * p.splits + rank, n, fmaf(sum, scale, bias));
+        }
+      } else if (p.out_dtype == TG_BF16) {
+        smallm_reduce_rows_as(reinterpret_cast<__nv_bfloat16*>(p.C) + n, p.ldc, col, rank, p.splits, rpr, mv, scale, bias);
+      } else if (p.out_dtype == TG_F16) {
+        smallm_reduce_rows_as(reinterpret_cast<__half*>(p.C) + n, p.ldc, col, rank, p.splits, rpr, mv, scale, bias);
+      } else {
+        smallm_reduce_rows_as(reinterpret_cast<float*>(p.C) + n, p.ldc, col, rank, p.splits, rpr, mv, scale, bias);
       }
     }
     if (threadIdx.x == 64) TG_STAMP(8);
@@ -339,11 +400,7 @@ __global__ void __launch_bounds__(kThreads, 2)
           for (int m = 0; m < MP; ++m)  // MP independent loads in flight
             if (m < mv) acc[m] += __ldcg(src + m * kBM);
         }
-        if (n_ok) {
-#pragma unroll
-          for (int m = 0; m < MP; ++m)
-            if (m < mv) smallm_store(p, m, n, fmaf(acc[m], scale, bias));
-        }
+        if (n_ok) smallm_store_column<MP>(p, n, acc, mv, scale, bias);
       }
     }
   }
