@@ -114,6 +114,34 @@ __device__ __forceinline__ void smallm_store_column(const GemmParams& p, int64_t
   }
 }
 
+// The whole [mv, 128] output tile of a CTA that owns its tile alone (no K split): the four epilogue warps
+// transpose it through shared memory (`tile`, MP rows of 128 elements) and store 16 bytes per lane, so that a
+// warp writes whole 128-byte lines of the row-major output instead of 64-byte pieces of 32 different rows.
+// Needs 16-byte aligned output rows; `cols` (a multiple of 16 / sizeof(T)) columns of the tile exist.
+template <int MP, typename T>
+__device__ __forceinline__ void smallm_store_tile_as(T* c_tile, int64_t ldc, T* tile, const float (&acc)[MP],
+                                                     bool have_acc, int n_local, int mv, int cols, float scale,
+                                                     float bias) {
+  if (have_acc) {
+#pragma unroll
+    for (int m = 0; m < MP; ++m) tile[m * kBM + n_local] = smallm_cast<T>(fmaf(acc[m], scale, bias));
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+  constexpr int kVec = 16 / static_cast<int>(sizeof(T));
+  constexpr int kChunks = kBM / kVec;          // 16-byte chunks per row
+  constexpr int kRowsPerPass = 128 / kChunks;  // rows the 128 threads cover at once
+  const int chunk = n_local % kChunks, r0 = n_local / kChunks;
+  if (have_acc && chunk * kVec < cols) {
+#pragma unroll
+    for (int i = 0; i < (MP + kRowsPerPass - 1) / kRowsPerPass; ++i) {
+      const int m = r0 + i * kRowsPerPass;
+      if (m < mv)
+        *reinterpret_cast<uint4*>(c_tile + m * ldc + chunk * kVec) =
+            *reinterpret_cast<const uint4*>(tile + m * kBM + chunk * kVec);
+    }
+  }
+}
+
 // Cluster reduction, owner side: rows rank, rank + splits, ... of the output, each the sum in split order of the
 // partial rows the peers pushed into `inbox` (slot [split][j], 128 floats per row).  The loads of one row are
 // issued together.
@@ -337,7 +365,27 @@ __global__ void __launch_bounds__(kThreads, 2)
   }
 
   if (p.splits == 1) {
-    if (have_acc && n_ok) smallm_store_column<MP>(p, n, acc, mv, scale, bias);
+    bool done = false;
+    if constexpr (!CLUSTER) {
+      const int vec = (p.out_dtype == TG_F32) ? 4 : 8;
+      if (p.beta == 0.f && c_rows_aligned(p) && p.N % vec == 0) {  // the same answer in every thread
+        done = true;
+        if (warp >= 2) {
+          const int left = static_cast<int>(p.N - row0);
+          const int cols = left < p.tile_rows ? left : p.tile_rows;
+          if (p.out_dtype == TG_BF16)
+            smallm_store_tile_as<MP>(reinterpret_cast<__nv_bfloat16*>(p.C) + row0, p.ldc,
+                                     reinterpret_cast<__nv_bfloat16*>(inbox), acc, have_acc, n_local, mv, cols, scale, bias);
+          else if (p.out_dtype == TG_F16)
+            smallm_store_tile_as<MP>(reinterpret_cast<__half*>(p.C) + row0, p.ldc, reinterpret_cast<__half*>(inbox), acc,
+                                     have_acc, n_local, mv, cols, scale, bias);
+          else
+            smallm_store_tile_as<MP>(reinterpret_cast<float*>(p.C) + row0, p.ldc, inbox, acc, have_acc, n_local, mv, cols,
+                                     scale, bias);
+        }
+      }
+    }
+    if (!done && have_acc && n_ok) smallm_store_column<MP>(p, n, acc, mv, scale, bias);
   } else if constexpr (CLUSTER) {
     // Output row m is finished by the CTA of rank m % splits; partial row m of split sp goes to slot
     // [sp][m / splits] of that CTA's inbox.  rows_per_rank = ceil(mv / splits).
