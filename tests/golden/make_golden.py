@@ -133,4 +133,6 @@ def main(ref_root: str, only=()) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", tuple(sys.argv[2:]))
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <path of a TileGym checkout> [fixture family ...]")
+    main(sys.argv[1], tuple(sys.argv[2:]))
