@@ -159,9 +159,11 @@ constexpr uint64_t kWsPartialBytes = 48ull << 20;
 
 // Split K only when the tiles alone leave most SMs idle.
 void choose_splits(int tiles, int num_kb, int num_sms, int64_t tile_floats, int target_ctas, int min_kb, int* splits,
-                   int* kbps) {
+                   int* kbps, int suggested = 0) {
   int s = 1;
-  if (tiles * 2 <= target_ctas && num_kb >= 2 * min_kb) {
+  if (suggested > 0) {
+    s = suggested;
+  } else if (tiles * 2 <= target_ctas && num_kb >= 2 * min_kb) {
     s = target_ctas / tiles;
     const int max_by_k = num_kb / min_kb;
     if (s > max_by_k) s = max_by_k;
@@ -205,6 +207,26 @@ void choose_smallm_config(int64_t N, int num_kb, int num_sms, int mp, int32_t* t
   *tile_rows = tr;
   *splits = s;
   *kbps = per;
+}
+
+// K split of the block-scaled 128 x 128 kernel (one persistent CTA per SM), by a cost model in k-block times:
+// waves x (k-blocks per unit + tail), where a split unit's tail (partial tile written, fence and counter, the last
+// arriver adding s partial tiles) costs about 6 + 1.5 s k-block times; fitted to sweeps of the split count at
+// M = 128 and 256 on the DeepSeek-V2 shapes.  Ties go to the smaller split count.
+int suggest_splits_blockscaled(int64_t tiles, int num_kb, int num_sms, int min_kb) {
+  int best = 1;
+  double best_cost = 1e300;
+  const int max_s = num_kb / min_kb < 16 ? num_kb / min_kb : 16;
+  for (int s = 1; s <= max_s; ++s) {
+    const int per = (num_kb + s - 1) / s;
+    const int64_t waves = (tiles * s + num_sms - 1) / num_sms;
+    const double cost = static_cast<double>(waves) * (per + (s > 1 ? 6.0 + 1.5 * s : 0.0));
+    if (cost < best_cost * 0.97) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return best;
 }
 
 int choose_bn(int64_t M, int64_t N, int num_sms) {
@@ -654,9 +676,14 @@ int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, co
   const bool have_ws = workspace != 0 && workspace_bytes >= kWsCounterBytes + kWsPartialBytes;
   const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
   if (tiles > 0x3fffffff) return fail(TG_ERR_ARGS, "problem has too many tiles");
-  if (have_ws && tiles * 16 <= static_cast<int64_t>(kWsCounterBytes / 4))
-    choose_splits(static_cast<int>(tiles), p.num_kb, st.num_sms, 128ll * 128, st.num_sms, 4, &p.splits, &p.kb_per_split);
-  else {
+  if (have_ws && tiles * 16 <= static_cast<int64_t>(kWsCounterBytes / 4)) {
+    // a problem that fills half a wave of 128 x 256 tiles goes to the wide kernel, which has no K split
+    const bool wide_unsplit = static_cast<int64_t>(p.tiles_m) * ((N + 255) / 256) >=
+                                  env_int("TILEGYM_B200_BS_WIDE_MIN", (st.num_sms + 1) / 2) &&
+                              env_int("TILEGYM_B200_BS_WIDE", 1) != 0;
+    choose_splits(static_cast<int>(tiles), p.num_kb, st.num_sms, 128ll * 128, st.num_sms, 4, &p.splits, &p.kb_per_split,
+                  wide_unsplit ? 1 : suggest_splits_blockscaled(tiles, p.num_kb, st.num_sms, 4));
+  } else {
     p.splits = 1;
     p.kb_per_split = p.num_kb;
   }
