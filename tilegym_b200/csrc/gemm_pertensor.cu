@@ -181,9 +181,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int row_in_tile = q * 32 + lane;
       const int64_t row = static_cast<int64_t>(tm) * kBM + row_in_tile;
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * BN);
-      float* part = nullptr;
+      // partial tile of (tile, split): per 32-column chunk and lane quadrant 8 float4 per thread, lane-contiguous,
+      // so that every store and load instruction of a warp covers 512 consecutive bytes
+      float4* part = nullptr;
       if (p.splits > 1)
-        part = p.ws_partial + (static_cast<int64_t>(t) * p.splits + sp) * (kBM * BN) + row_in_tile * 32;
+        part = reinterpret_cast<float4*>(p.ws_partial) + (static_cast<int64_t>(t) * p.splits + sp) * (kBM * BN / 4) +
+               q * 256 + lane;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -199,25 +202,26 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (p.splits == 1) {
           if (row < p.M) epilogue_store32(p, row, tn * BN + c * 32, acc, scale, vec_ok);
         } else {
-          float4* dst = reinterpret_cast<float4*>(part + c * (kBM * 32));
+          float4* dst = part + c * 1024;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) dst[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+          for (int j = 0; j < 8; ++j)
+            __stcg(dst + j * 32, make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]));
         }
       }
       if (p.splits > 1) {
         if (splitk_arrive_is_last(p.ws_counters + t * 4 + q, p.splits)) {
-          const float* tile_part = p.ws_partial + static_cast<int64_t>(t) * p.splits * (kBM * BN) + row_in_tile * 32;
+          const float4* tile_part = reinterpret_cast<const float4*>(p.ws_partial) +
+                                    static_cast<int64_t>(t) * p.splits * (kBM * BN / 4) + q * 256 + lane;
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
             float acc[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) acc[j] = 0.f;
             for (int s2 = 0; s2 < p.splits; ++s2) {  // fixed order: bit-stable result
-              const float4* src =
-                  reinterpret_cast<const float4*>(tile_part + static_cast<int64_t>(s2) * (kBM * BN) + c * (kBM * 32));
+              const float4* src = tile_part + static_cast<int64_t>(s2) * (kBM * BN / 4) + c * 1024;
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
-                float4 v = __ldcg(src + j);
+                float4 v = __ldcg(src + j * 32);
                 acc[4 * j] += v.x;
                 acc[4 * j + 1] += v.y;
                 acc[4 * j + 2] += v.z;
