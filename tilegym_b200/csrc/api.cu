@@ -229,6 +229,37 @@ int suggest_splits_blockscaled(int64_t tiles, int num_kb, int num_sms, int min_k
   return best;
 }
 
+// Tile width and K split of the single-CTA per-tensor kernel (65 <= M < 256 in practice), by a cost model in
+// microseconds fitted to sweeps over (width, split) on the Llama-3.1-8B shapes at M = 96 ... 256:
+// waves x (k-blocks per unit x time per k-block + split tail).  A k-block takes 0.19 / 0.24 / 0.42 us for 64 /
+// 128 / 256 columns; a split unit's tail (partial tile out, fence and counter, the last arriver adding s partial
+// tiles) about 2.5 + (width / 64) (0.5 + 0.9 s) us.  Ties go to the narrower tile and the smaller split count.
+void choose_bn_splits_pertensor(int64_t M, int64_t N, int num_kb, int num_sms, int forced_bn, bool may_split, int* bn_out,
+                                int* splits_out) {
+  const int cand[3] = {64, 128, 256};
+  const double t_kb[3] = {0.19, 0.24, 0.42};
+  const int64_t tm = (M + 127) / 128;
+  double best_cost = 1e300;
+  *bn_out = forced_bn > 0 ? forced_bn : 128;
+  *splits_out = 1;
+  for (int i = 0; i < 3; ++i) {
+    if (forced_bn > 0 && cand[i] != forced_bn) continue;
+    const int64_t tiles = tm * ((N + cand[i] - 1) / cand[i]);
+    const int max_s = !may_split ? 1 : (num_kb / 4 < 8 ? (num_kb / 4 > 1 ? num_kb / 4 : 1) : 8);
+    for (int s = 1; s <= max_s; ++s) {
+      const int per = (num_kb + s - 1) / s;
+      const int64_t waves = (tiles * s + num_sms - 1) / num_sms;
+      const double tail = s > 1 ? 2.5 + (cand[i] / 64.0) * (0.5 + 0.9 * s) : 0.0;
+      const double cost = static_cast<double>(waves) * (per * t_kb[i] + tail);
+      if (cost < best_cost * 0.97) {
+        best_cost = cost;
+        *bn_out = cand[i];
+        *splits_out = s;
+      }
+    }
+  }
+}
+
 int choose_bn(int64_t M, int64_t N, int num_sms) {
   // Estimated time = waves x tile width x a per-width efficiency factor
   // (narrow tiles re-read A from shared memory more often per flop).
@@ -419,15 +450,21 @@ static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, cons
     return TG_OK;
   }
 
-  int bn = choose_bn(M, N, st.num_sms);
-  bn = env_int("TILEGYM_B200_BN", bn);
-  if (bn != 256 && bn != 128 && bn != 64) return fail(TG_ERR_ARGS, "TILEGYM_B200_BN must be 64, 128 or 256");
+  const int forced_bn = env_int("TILEGYM_B200_BN", 0);
+  if (forced_bn != 0 && forced_bn != 256 && forced_bn != 128 && forced_bn != 64)
+    return fail(TG_ERR_ARGS, "TILEGYM_B200_BN must be 64, 128 or 256");
+  int bn = 128, suggested = 1;
+  if (M < 256)
+    choose_bn_splits_pertensor(M, N, p.num_kb, st.num_sms, forced_bn, have_ws, &bn, &suggested);
+  else
+    bn = forced_bn != 0 ? forced_bn : choose_bn(M, N, st.num_sms);  // larger M gets here only with the pair kernel off
   p.tiles_m = static_cast<int32_t>((M + 127) / 128);
   p.tiles_n = static_cast<int32_t>((N + bn - 1) / bn);
   const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
   if (tiles > 0x3fffffff) return fail(TG_ERR_ARGS, "problem has too many tiles");
   if (have_ws && tiles * 4 <= static_cast<int64_t>(kWsCounterBytes / 4))
-    choose_splits(static_cast<int>(tiles), p.num_kb, st.num_sms, 128ll * bn, st.num_sms, 4, &p.splits, &p.kb_per_split);
+    choose_splits(static_cast<int>(tiles), p.num_kb, st.num_sms, 128ll * bn, st.num_sms, 4, &p.splits, &p.kb_per_split,
+                  M < 256 ? suggested : 0);
   else {
     p.splits = 1;
     p.kb_per_split = p.num_kb;
