@@ -450,6 +450,8 @@ static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, cons
     return TG_OK;
   }
 
+  // programmatic dependent launch: this kernel's set-up overlaps the tail of the previous kernel on the stream
+  if (env_int("TILEGYM_B200_PDL", 1) != 0) p.flags |= 2;
   const int forced_bn = env_int("TILEGYM_B200_BN", 0);
   if (forced_bn != 0 && forced_bn != 256 && forced_bn != 128 && forced_bn != 64)
     return fail(TG_ERR_ARGS, "TILEGYM_B200_BN must be 64, 128 or 256");
