@@ -419,6 +419,7 @@ static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, cons
 
   // Large problems: CTA-pair kernel (256 x 256 tiles, half the L2 traffic per SM).
   if (pair_kernel) {
+    if (env_int("TILEGYM_B200_PDL", 1) != 0) p.flags |= 2;  // programmatic dependent launch
     p.tiles_m = static_cast<int32_t>((M + 255) / 256);
     p.tiles_n = static_cast<int32_t>((N + 255) / 256);
     p.splits = 1;
@@ -555,7 +556,7 @@ int32_t tg_gemm_dense16(const TgTensorDesc* C, const TgTensorDesc* A, const TgTe
   p.splits = 1;
   p.kb_per_split = p.num_kb;
   p.status = st.status;
-  p.flags = (A->dtype == TG_BF16) ? 8 : 16;
+  p.flags = ((A->dtype == TG_BF16) ? 8 : 16) | (env_int("TILEGYM_B200_PDL", 1) != 0 ? 2 : 0);
 
   auto map16 = [&](CUtensorMap* map, const TgTensorDesc* t, int64_t rows, int box_rows) -> int32_t {
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
@@ -644,6 +645,7 @@ int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDes
   p.splits = 1;
   p.kb_per_split = p.num_kb;
   p.status = st.status;
+  if (env_int("TILEGYM_B200_PDL", 1) != 0) p.flags |= 2;  // programmatic dependent launch
   p.m_indptr = reinterpret_cast<const int32_t*>(m_indptr);
   p.num_groups = static_cast<int32_t>(G);
   // every group adds at most one partly filled 128-row tile to the ceil(M / 128) a dense problem would have
@@ -710,6 +712,7 @@ int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, co
   p.ldas = As->strides[0];
   p.ldbs = Bs->strides[0];
   p.status = st.status;
+  if (env_int("TILEGYM_B200_PDL", 1) != 0) p.flags |= 2;  // programmatic dependent launch
   p.ws_counters = reinterpret_cast<uint32_t*>(workspace);
   p.ws_partial = reinterpret_cast<float*>(workspace + kWsCounterBytes);
   const bool have_ws = workspace != 0 && workspace_bytes >= kWsCounterBytes + kWsPartialBytes;

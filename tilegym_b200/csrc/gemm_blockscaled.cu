@@ -76,6 +76,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  griddep_launch_dependents();  // the next kernel's CTAs may take the place of ours as we finish
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) {
@@ -97,6 +98,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Programmatic dependent launch: the set-up above may have run while the previous kernel on the stream was
+  // finishing; nothing below may touch global memory before that kernel has completed.
+  griddep_wait();
 
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int num_units = num_tiles * p.splits;
@@ -330,9 +334,17 @@ cudaError_t launch_gemm_blockscaled(const CUtensorMap& tmA, const CUtensorMap& t
   const int units = p.tiles_m * p.tiles_n * p.splits;
   const int grid = units < num_sms ? units : num_sms;
   // tmC == nullptr selects the register -> global store epilogue (fp32 output or unaligned rows)
-  tg_fp8_gemm_blockscaled_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmC != nullptr ? *tmC : tmA, p,
-                                                                         tmC != nullptr ? 1 : 0);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (p.flags & 2) ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, tg_fp8_gemm_blockscaled_kernel, tmA, tmB, tmC != nullptr ? *tmC : tmA, p, tmC != nullptr ? 1 : 0);
 }
 
 }  // namespace tg

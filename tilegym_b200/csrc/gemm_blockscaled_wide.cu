@@ -180,6 +180,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  griddep_launch_dependents();  // the next kernel's CTAs may take the place of ours as we finish
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) {
@@ -201,6 +202,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Programmatic dependent launch: the set-up above may have run while the previous kernel on the stream was
+  // finishing; nothing below may touch global memory before that kernel has completed.
+  griddep_wait();
 
   // 128 x 256 tiles; grouped: every warp counts the groups' 128-row tiles itself (warp 0..11 all need it)
   const int mtiles = kGrouped ? count_group_mtiles(p, lane) : 0;
@@ -441,9 +445,17 @@ cudaError_t launch_wide(const CUtensorMap& tmA, const CUtensorMap& tmB, const CU
   }
   const int grid = tiles < num_sms ? tiles : num_sms;
   // tmC == nullptr selects the register -> global store epilogue (fp32 output or unaligned rows)
-  tg_fp8_gemm_blockscaled_wide_kernel<kGrouped>
-      <<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmC != nullptr ? *tmC : tmA, p, tmC != nullptr ? 1 : 0);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (p.flags & 2) ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, tg_fp8_gemm_blockscaled_wide_kernel<kGrouped>, tmA, tmB, tmC != nullptr ? *tmC : tmA, p, tmC != nullptr ? 1 : 0);
 }
 }  // namespace
 

@@ -170,6 +170,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
+  griddep_launch_dependents();  // the next kernel's CTAs may take the place of ours as we finish
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader
   const bool leader = (rank == 0);
@@ -195,6 +196,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   cluster_sync_all();  // both CTAs' barriers are initialised before anyone signals across the pair
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Programmatic dependent launch: the set-up above may have run while the previous kernel on the stream was
+  // finishing; nothing below may touch global memory before that kernel has completed.
+  griddep_wait();
 
   const int num_units = plan.num_units;
   const int pair_id = blockIdx.x >> 1;
@@ -523,13 +527,19 @@ cudaError_t launch_gemm_pertensor_2cta(const CUtensorMap& tmA, const CUtensorMap
   plan.full_tiles = (plan.tail_div == 1) ? tiles : tiles - tiles % pairs;
   plan.num_units = plan.full_tiles + (tiles - plan.full_tiles) * plan.tail_div;
   if (plan.num_units < pairs) pairs = plan.num_units;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);  // the pair is the kernel's compile-time cluster
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (p.flags & 2) ? 1 : 0;
   if (p.flags & 24)  // bf16 / f16 operands
-    tg_fp8_gemm_pertensor_2cta_kernel<true><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmBt, omaps, num_out,
-                                                                                         p, plan);
-  else
-    tg_fp8_gemm_pertensor_2cta_kernel<false><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmBt, omaps,
-                                                                                          num_out, p, plan);
-  return cudaGetLastError();
+    return cudaLaunchKernelEx(&cfg, tg_fp8_gemm_pertensor_2cta_kernel<true>, tmA, tmB, tmBt, omaps, num_out, p, plan);
+  return cudaLaunchKernelEx(&cfg, tg_fp8_gemm_pertensor_2cta_kernel<false>, tmA, tmB, tmBt, omaps, num_out, p, plan);
 }
 
 }  // namespace tg
