@@ -229,7 +229,7 @@ int suggest_splits_blockscaled(int64_t tiles, int num_kb, int num_sms, int min_k
   return best;
 }
 
-// Tile width and K split of the single-CTA per-tensor kernel (65 <= M < 256 in practice), by a cost model in
+// Tile width and K split of the single-CTA per-tensor kernel (65 <= M < 512 in practice), by a cost model in
 // microseconds fitted to sweeps over (width, split) on the Llama-3.1-8B shapes at M = 96 ... 256:
 // waves x (k-blocks per unit x time per k-block + split tail).  A k-block takes 0.19 / 0.24 / 0.42 us for 64 /
 // 128 / 256 columns; a split unit's tail (partial tile out, fence and counter, the last arriver adding s partial
@@ -377,7 +377,12 @@ static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, cons
   // rows are 16-byte aligned; the fused all-gather needs that path.
   const bool tma_out_ok = (C->dtype == TG_BF16 || C->dtype == TG_F16) && beta == 0.0f && (C->ptr & 15u) == 0 &&
                           ((C->strides[0] * 2) & 15) == 0;
-  const bool pair_kernel = swiglu || (M >= 256 && N >= 256 && env_int("TILEGYM_B200_2CTA", 1) != 0 &&
+  // The CTA-pair kernel needs enough 256 x 256 tiles to occupy the GPU: below TILEGYM_B200_PAIR_MIN_TILES (24)
+  // of them and M < 512, single-CTA tiles (64 ... 256 columns, optional K split) finish sooner; measured at
+  // M = 256: N = K = 4096 11.6 against 12.4 us, N = 4096 K = 14336 25.5 against 29.1 us.
+  const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  const bool pair_fills = M >= 512 || num_peers > 0 || pair_tiles >= env_int("TILEGYM_B200_PAIR_MIN_TILES", 24);
+  const bool pair_kernel = swiglu || (M >= 256 && N >= 256 && pair_fills && env_int("TILEGYM_B200_2CTA", 1) != 0 &&
                                       getenv("TILEGYM_B200_BN") == nullptr && getenv("TILEGYM_B200_SPLITS") == nullptr);
   if (swiglu) {
     if (!tma_out_ok) return fail(TG_ERR_ARGS, "the SwiGLU epilogue needs a bf16 / f16 output with 16-byte aligned rows");
@@ -457,7 +462,7 @@ static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, cons
   if (forced_bn != 0 && forced_bn != 256 && forced_bn != 128 && forced_bn != 64)
     return fail(TG_ERR_ARGS, "TILEGYM_B200_BN must be 64, 128 or 256");
   int bn = 128, suggested = 1;
-  if (M < 256)
+  if (M < 512)
     choose_bn_splits_pertensor(M, N, p.num_kb, st.num_sms, forced_bn, have_ws, &bn, &suggested);
   else
     bn = forced_bn != 0 ? forced_bn : choose_bn(M, N, st.num_sms);  // larger M gets here only with the pair kernel off
@@ -467,7 +472,7 @@ static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, cons
   if (tiles > 0x3fffffff) return fail(TG_ERR_ARGS, "problem has too many tiles");
   if (have_ws && tiles * 4 <= static_cast<int64_t>(kWsCounterBytes / 4))
     choose_splits(static_cast<int>(tiles), p.num_kb, st.num_sms, 128ll * bn, st.num_sms, 4, &p.splits, &p.kb_per_split,
-                  M < 256 ? suggested : 0);
+                  M < 512 ? suggested : 0);
   else {
     p.splits = 1;
     p.kb_per_split = p.num_kb;
