@@ -221,7 +221,25 @@ __global__ void __launch_bounds__(kThreads, 1)
             float acc[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) acc[j] = 0.f;
-            for (int s2 = 0; s2 < p.splits; ++s2) {  // fixed order: bit-stable result
+            // fixed order (bit-stable result); two splits' loads are in flight together
+            int s2 = 0;
+#pragma unroll 1
+            for (; s2 + 1 < p.splits; s2 += 2) {
+              const float4* src = tile_part + static_cast<int64_t>(s2) * (kBM * BN / 4) + c * 1024;
+              float4 v0[8], v1[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v0[j] = __ldcg(src + j * 32);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v1[j] = __ldcg(src + (kBM * BN / 4) + j * 32);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                acc[4 * j] = (acc[4 * j] + v0[j].x) + v1[j].x;
+                acc[4 * j + 1] = (acc[4 * j + 1] + v0[j].y) + v1[j].y;
+                acc[4 * j + 2] = (acc[4 * j + 2] + v0[j].z) + v1[j].z;
+                acc[4 * j + 3] = (acc[4 * j + 3] + v0[j].w) + v1[j].w;
+              }
+            }
+            if (s2 < p.splits) {
               const float4* src = tile_part + static_cast<int64_t>(s2) * (kBM * BN / 4) + c * 1024;
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
