@@ -240,6 +240,14 @@ TG_API int32_t tg_device_status(int32_t device_id, int32_t* detail);
 /* Message of the last failing call made by this thread ("" if none). */
 TG_API const char* tg_last_error_string(void);
 
+/* Host-only (no CUDA call): the tile width and K-split count the library would pick on a GPU with num_sms SMs.
+ * kind 0: per-tensor GEMM on single-CTA tiles (64 < M < 512 where the CTA-pair kernel would not fill the GPU);
+ * kind 1: block-scaled GEMM on 128 x 128 tiles.  The counterpart of the launch-shape choice in the reference's
+ * wrapper (src/tilegym/suites/unsloth/cutile/fp8.py:417-420: BLOCK_SIZE_M from M, one program per tile); here
+ * the choice is a cost model, waves x (k-blocks per unit + split tail), exposed for inspection and tests. */
+TG_API int32_t tg_plan_splits(int32_t kind, int64_t M, int64_t N, int64_t K, int32_t num_sms, int32_t* tile_cols,
+                              int32_t* splits);
+
 /* Library version, e.g. 100 for 0.1.0. */
 TG_API int32_t tg_version(void);
 

@@ -148,3 +148,40 @@ def test_signatures_match_the_reference_entry_points():
     assert list(inspect.signature(ops.per_token_group_quant_8bit).parameters) == [
         "x", "group_size", "eps", "dst_dtype", "column_major_scales", "scale_tma_aligned", "scale_ue8m0"]
     assert list(inspect.signature(ops.matmul).parameters)[:6] == ["a", "b", "trans_a", "trans_b", "static_persistent", "use_tma"]
+
+
+def _plan(kind, M, N, K, sms=148):
+    cols, splits = ctypes.c_int32(0), ctypes.c_int32(0)
+    rc = _lib.lib().tg_plan_splits(kind, M, N, K, sms, ctypes.byref(cols), ctypes.byref(splits))
+    assert rc == 0
+    return cols.value, splits.value
+
+
+def test_plan_splits_follows_the_measured_optima():
+    """Tile width / K split of the mid-M kernels (a host-side cost model): the choices that won the split sweeps
+    on B200 (148 SMs) for the Llama-3.1-8B and DeepSeek-V2 weight shapes."""
+    # per-tensor, single-CTA tiles, M = 128: one wave of narrow tiles unsplit, the long-K shape split in two
+    assert _plan(0, 128, 6144, 4096) == (64, 1)     # qkv
+    assert _plan(0, 128, 4096, 4096) == (64, 1)     # o_proj
+    assert _plan(0, 128, 4096, 14336) == (64, 2)    # down
+    assert _plan(0, 128, 28672, 4096)[1] == 1       # gate_up: many tiles, never split
+    assert _plan(0, 255, 4096, 14336) == (128, 2)   # two tile rows: wider tiles
+    # block-scaled, 128 x 128 tiles
+    assert _plan(1, 128, 24576, 1536) == (128, 1)   # more tiles than SMs
+    assert _plan(1, 128, 5120, 12288) == (128, 3)
+    assert 3 <= _plan(1, 128, 3072, 5120)[1] <= 6   # flat optimum between 3 and 6
+    assert _plan(1, 256, 5120, 12288) == (128, 3)
+    assert _plan(1, 4096, 5120, 12288) == (128, 1)
+    # a split never leaves a unit with fewer than four k-blocks, and a GPU with few SMs splits less
+    for K in (512, 1024, 4096, 14336):
+        _, s = _plan(1, 128, 1024, K)
+        assert s >= 1 and (K // 128) // s >= 4 or s == 1
+    assert _plan(1, 128, 5120, 12288, sms=40)[1] == 1
+
+
+def test_plan_splits_rejects_bad_arguments():
+    cols, splits = ctypes.c_int32(0), ctypes.c_int32(0)
+    lib = _lib.lib()
+    assert lib.tg_plan_splits(2, 128, 128, 128, 148, ctypes.byref(cols), ctypes.byref(splits)) == -6
+    assert lib.tg_plan_splits(0, 0, 128, 128, 148, ctypes.byref(cols), ctypes.byref(splits)) == -6
+    assert lib.tg_plan_splits(0, 128, 128, 128, 148, None, ctypes.byref(splits)) == -5

@@ -67,6 +67,11 @@ _lib: Optional[ctypes.CDLL] = None
 _P = ctypes.c_char_p  # const TgTensorDesc*, passed as the packed bytes of desc()
 SIGNATURES = {
     "tg_version": (ctypes.c_int32, []),
+    "tg_plan_splits": (
+        ctypes.c_int32,
+        [ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32,
+         ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)],
+    ),
     "tg_set_static_weights": (ctypes.c_int32, [ctypes.c_int32]),
     "tg_last_error_string": (ctypes.c_char_p, []),
     "tg_fp8_gemm_workspace_bytes": (ctypes.c_uint64, [ctypes.c_int64] * 3),

@@ -304,6 +304,26 @@ extern "C" {
 
 int32_t tg_version(void) { return 100; }
 
+int32_t tg_plan_splits(int32_t kind, int64_t M, int64_t N, int64_t K, int32_t num_sms, int32_t* tile_cols,
+                       int32_t* splits) {
+  if (tile_cols == nullptr || splits == nullptr) return fail(TG_ERR_NULL, "tile_cols / splits is null");
+  if (M <= 0 || N <= 0 || K <= 0 || num_sms <= 0) return fail(TG_ERR_ARGS, "M, N, K and num_sms must be positive");
+  const int num_kb = static_cast<int>((K + 127) / 128);
+  if (kind == 0) {
+    int bn = 128, s = 1;
+    choose_bn_splits_pertensor(M, N, num_kb, num_sms, 0, true, &bn, &s);
+    *tile_cols = bn;
+    *splits = s;
+  } else if (kind == 1) {
+    const int64_t tiles = ((M + 127) / 128) * ((N + 127) / 128);
+    *tile_cols = 128;
+    *splits = suggest_splits_blockscaled(tiles, num_kb, num_sms, 4);
+  } else {
+    return fail(TG_ERR_ARGS, "kind must be 0 (per-tensor, single-CTA tiles) or 1 (block-scaled, 128 x 128 tiles)");
+  }
+  return TG_OK;
+}
+
 int32_t tg_set_static_weights(int32_t on) {
   const int32_t old = g_static_weights;
   g_static_weights = on ? 1 : 0;
