@@ -1,6 +1,11 @@
-"""Shape sweeps that accompany the headline number of bench.py (`--extra`):
-the decode (M <= 64, HBM-bound) GEMMs of the Llama-3.1-8B linears and the
-DeepSeek-V2-style block-scaled GEMMs.
+"""Shape sweeps that accompany the headline number of bench.py.
+
+`run_configs` (part of the default N = 1 run) covers the other benchmark
+configurations in bounded form: the 1024-cube GEMM, the decode (M <= 64,
+HBM-bound) GEMMs of the Llama-3.1-8B linears, the DeepSeek-V2-style
+block-scaled GEMMs and the Llama-3.1-70B gate_up GEMM on one GPU.  `run`
+(`--extra`) adds the grouped GEMM, the quantisers, the SwiGLU epilogue and a
+whole MLP block.
 
 Timing method for the small kernels: R launches are captured into one CUDA
 graph, each reading a different copy of the weight (the copies together are
@@ -56,11 +61,11 @@ def decode_sweep(dev, hbm_peak_gbs: float):
             outs = [torch.empty(M, N, dtype=torch.bfloat16, device=dev) for _ in range(copies)]
             launch = lambda i: tg.fp8_scaled_mm(a, w[i], sa, sb, None, torch.bfloat16, out=outs[i])  # noqa: E731
             us_default = graph_time_us(launch, copies)
-            # decode loop mode: the weights are constants, so consecutive GEMMs may overlap their weight
+            # as FP8Linear calls it: the weights are constants, so consecutive GEMMs may overlap their weight
             # streaming with the previous kernel's tail (programmatic dependent launch)
-            prev = tg.set_static_weights(True)
-            us = graph_time_us(launch, copies)
-            tg.set_static_weights(prev)
+            launch_static = lambda i: tg.fp8_scaled_mm(a, w[i], sa, sb, None, torch.bfloat16, out=outs[i],  # noqa: E731
+                                                       static_weights=True)
+            us = graph_time_us(launch_static, copies)
             nbytes = N * K + M * K + 2 * M * N + 8
             gbs = nbytes / us / 1e3
             rows.append({"shape": name, "M": M, "N": N, "K": K, "us": round(us, 2), "gbs": round(gbs, 1),
@@ -218,14 +223,75 @@ def mlp_block_sweep(dev):
     return res
 
 
+def cube_1024(dev, fp8_peak_tflops: float):
+    """Benchmark configuration 1: one 1024 x 1024 x 1024 per-tensor GEMM (2.1 GFLOP, 4 MB: launch-bound)."""
+    import tilegym_b200 as tg
+
+    copies = 8
+    a = [torch.randn(1024, 1024, device=dev).to(torch.float8_e4m3fn) for _ in range(copies)]
+    b = [torch.randn(1024, 1024, device=dev).to(torch.float8_e4m3fn) for _ in range(copies)]
+    out = [torch.empty(1024, 1024, dtype=torch.bfloat16, device=dev) for _ in range(copies)]
+    sa = torch.full((1,), 1e-2, device=dev)
+    us = graph_time_us(lambda i: tg.fp8_scaled_mm(a[i], b[i], sa, sa, None, torch.bfloat16, out=out[i]), copies, replays=20)
+    tflops = 2.0 * 1024 ** 3 / us / 1e6
+    return {"M": 1024, "N": 1024, "K": 1024, "us": round(us, 2), "tflops": round(tflops, 1),
+            "frac_of_burst_peak": round(tflops / fp8_peak_tflops, 3),
+            "note": "16 CTA-pair tiles on 148 SMs: bounded by launch and fill / drain, not by the tensor pipe"}
+
+
+def llama70b_one_gpu(dev, fp8_peak_tflops: float):
+    """The multi-GPU workload (M = 8192, N = 57344, K = 8192) on ONE GPU: the same-workload base of the
+    strong-scaling curve."""
+    import tilegym_b200 as tg
+
+    M, N, K = 8192, 57344, 8192
+    a = torch.randn(M, K, device=dev, dtype=torch.bfloat16).to(torch.float8_e4m3fn)
+    b = torch.empty(N, K, device=dev, dtype=torch.float8_e4m3fn)
+    for i in range(0, N, 8192):  # in slabs: the bf16 source of the whole weight would be 0.9 GB
+        b[i:i + 8192] = torch.randn(min(8192, N - i), K, device=dev, dtype=torch.bfloat16).mul_(0.02).to(torch.float8_e4m3fn)
+    sa = torch.full((1,), 3e-2, device=dev)
+    sb = torch.full((1,), 2e-4, device=dev)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    for _ in range(2):
+        tg.fp8_scaled_mm(a, b, sa, sb, None, torch.bfloat16, out=out)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 5
+    e0.record()
+    for _ in range(reps):
+        tg.fp8_scaled_mm(a, b, sa, sb, None, torch.bfloat16, out=out)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    tflops = 2.0 * M * N * K / ms / 1e9
+    return {"M": M, "N": N, "K": K, "ms": round(ms, 4), "tflops": round(tflops, 1),
+            "frac_of_burst_peak": round(tflops / fp8_peak_tflops, 3)}
+
+
+def run_configs(dev, peaks):
+    """Bounded sweeps of the benchmark configurations the headline number does not cover."""
+    hbm = float(peaks["hbm_gbs"])
+    fp8 = 2.0 * float(peaks["bf16_tflops"])  # kernels timed alone, in short loops: burst figure
+    return {
+        "method": "CUDA-graph replay over rotating weight copies (> 3x L2), time per launch (the 70B GEMM: CUDA "
+                  "events around 5 launches); fractions are of the measured HBM copy bandwidth "
+                  f"({hbm:.0f} GB/s) / of 2 x measured bf16 burst ({fp8:.0f} TFLOP/s)",
+        "config1_cube_1024": cube_1024(dev, fp8),
+        "config3_decode_per_tensor": decode_sweep(dev, hbm),
+        "config3_default": "FP8Linear passes static_weights=True (its weight is a constant of the layer), so `us` / "
+                           "`gbs` are what a decode loop through FP8Linear gets; a bare fp8_scaled_mm call, whose "
+                           "default makes no such promise, takes `us_without_static_weight_promise`",
+        "config4_block_scaled": block_scaled_sweep(dev, fp8, hbm),
+        "config5_one_gpu": llama70b_one_gpu(dev, fp8),
+    }
+
+
 def run(dev, peaks):
     hbm = float(peaks["hbm_gbs"])
     fp8 = 2.0 * float(peaks["bf16_tflops"])  # kernels timed alone: burst figure
     return {
         "method": "CUDA-graph replay over rotating weight copies (> 3x L2), time per launch; fractions are of the "
                   "measured HBM copy bandwidth / of 2 x measured bf16 burst",
-        "decode_per_tensor": decode_sweep(dev, hbm),
-        "block_scaled": block_scaled_sweep(dev, fp8, hbm),
         "grouped_block_scaled": grouped_sweep(dev, fp8),
         "quantisers": quantiser_sweep(dev, hbm),
         "swiglu_gate_up": swiglu_sweep(dev),

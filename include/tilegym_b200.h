@@ -65,7 +65,7 @@ typedef struct TgTensorDesc {
 
 /* Per-tensor-scaled FP8 GEMM with a fused epilogue:
  *     C[M,N] = alpha * sa * sb * (A[M,K] . B[N,K]^T) + bias[N] + beta * C[M,N]
- * A, B: e4m3, row-major, contiguous rows (K % 16 == 0, 16-byte aligned base).
+ * A, B: both e4m3 or both e5m2, row-major, contiguous rows (K % 16 == 0, 16-byte aligned base).
  * C: bf16 / f16 / f32, row-major, written in place (read first only if beta != 0).
  * scale_a, scale_b: device pointers to one fp32 each, or 0 for 1.0.
  * bias: f32 or bf16 vector of N elements, or NULL.
@@ -80,23 +80,33 @@ typedef struct TgTensorDesc {
  */
 TG_API int32_t tg_fp8_gemm_pertensor(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
                               uint64_t scale_a, uint64_t scale_b, float alpha, const TgTensorDesc* bias,
-                              float beta, uint64_t workspace, uint64_t workspace_bytes, int32_t device_id,
-                              uint64_t stream);
+                              float beta, uint64_t workspace, uint64_t workspace_bytes, uint32_t flags,
+                              int32_t device_id, uint64_t stream);
+
+/* flags of tg_fp8_gemm_pertensor.
+ * TG_GEMM_STATIC_B: B (the weights) is not written by the kernel that precedes this call on the stream - true
+ * for the parameters of a Linear layer.  Small-M (M <= 64) launches then start streaming B while that kernel's
+ * last thread blocks are still finishing (programmatic dependent launch); A, the scales, the bias and C are
+ * still touched only after it has completed.  Worth 0.7-1.7 us on a 5-20 us decode GEMM. */
+#define TG_GEMM_STATIC_B 1u
 
 /* Block-scaled W8A8 GEMM (1 x block_k activation scales, block_n x block_k
  * weight scales; only 128 x 128 is implemented, anything else is -6):
- *     C[m,n] = sum_kb  As[m,kb] * Bs[n/128,kb] * (A[m,kb-block] . B[n,kb-block])
+ *     C[m,n] = sum_kb  As[m,kb] * Bs[n/128,kb] * (A[m,kb-block] . B[n,kb-block]) + bias[n] + beta * C[m,n]
  * A: (M,K) e4m3; B: (N,K) e4m3; As: (M, ceil(K/128)) f32; Bs: (ceil(N/128),
- * ceil(K/128)) f32; C: (M,N) f32 / f16 / bf16.  Rows past M, N and columns
+ * ceil(K/128)) f32; C: (M,N) f32 / f16 / bf16, written in place (read first only
+ * if beta != 0).  bias: f32 / f16 / bf16 vector of N elements, or NULL; it is added
+ * in fp32 before the one rounding to C's dtype.  Rows past M, N and columns
  * past K read as zero.  workspace as above (used when K is split).
  * Replaces tilegym.suites.unsloth.ops.w8a8_block_fp8_matmul
  * (src/tilegym/suites/unsloth/ops.py:240-265; host wrapper and kernel
- * src/tilegym/suites/unsloth/cutile/fp8.py:388-446 and :243-334).
+ * src/tilegym/suites/unsloth/cutile/fp8.py:388-446 and :243-334), which has
+ * neither bias nor beta (pass NULL and 0).
  */
 TG_API int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
                                 const TgTensorDesc* As, const TgTensorDesc* Bs, int32_t block_n,
-                                int32_t block_k, uint64_t workspace, uint64_t workspace_bytes,
-                                int32_t device_id, uint64_t stream);
+                                int32_t block_k, const TgTensorDesc* bias, float beta, uint64_t workspace,
+                                uint64_t workspace_bytes, int32_t device_id, uint64_t stream);
 
 /* Per-tensor-scaled FP8 GEMM of a fused gate/up projection with the SwiGLU activation in its epilogue:
  *     C[m, j] = silu(g) * u,   g = alpha*sa*sb*(A . B[row_g(j)]^T) + bias[row_g(j)],  u likewise with row_u(j)
@@ -127,14 +137,15 @@ TG_API int32_t tg_gemm_dense16(const TgTensorDesc* C, const TgTensorDesc* A, con
  * m_indptr: DEVICE pointer to G+1 int32 offsets, non-decreasing, never read on the host (so the call can be
  * captured in a CUDA graph whose routing changes between replays); groups may be empty and need no alignment;
  * rows outside every group are left untouched; offsets are clamped to [0, M] on the device.
+ * bias: NULL or a contiguous (G, N) f32 / f16 / bf16 matrix, row g added to the rows of group g; beta as above.
  * Replaces tilegym.suites.flashinfer.ops.ragged_block_scaled_bmm for e4m3 inputs in the NT layout
  * (src/tilegym/suites/flashinfer/ops.py:126-158, kernel
  * src/tilegym/suites/flashinfer/cutile/gemm/ragged_block_scaled_bmm.py:497-616).
  */
 TG_API int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
                                                const TgTensorDesc* As, const TgTensorDesc* Bs, uint64_t m_indptr,
-                                               int32_t block_n, int32_t block_k, int32_t device_id,
-                                               uint64_t stream);
+                                               int32_t block_n, int32_t block_k, const TgTensorDesc* bias,
+                                               float beta, int32_t device_id, uint64_t stream);
 
 /* Column-parallel GEMM fused with the all-gather of its output (multi-GPU, one
  * process per GPU).  This rank computes its slab C[M, n] = alpha*sa*sb*(A . B_shard^T)
@@ -223,7 +234,8 @@ TG_API int32_t tg_quant_pertensor(const TgTensorDesc* Y, uint64_t scale_out, con
 TG_API int32_t tg_weight_quant_block(const TgTensorDesc* Y, const TgTensorDesc* S, const TgTensorDesc* X,
                               int32_t block, int32_t device_id, uint64_t stream);
 
-/* Process-wide promise that the B operand (weights) of small-M GEMMs (M <= 64) is
+/* Process-wide form of TG_GEMM_STATIC_B, for callers that cannot pass the flag per call: a promise that the B
+ * operand (weights) of small-M GEMMs (M <= 64) is
  * never written by the kernel that precedes the GEMM on its stream.  The small-M
  * kernel is launched with programmatic dependent launch; with this promise it
  * starts streaming weights while the previous kernel's last CTAs are still
@@ -231,6 +243,26 @@ TG_API int32_t tg_weight_quant_block(const TgTensorDesc* Y, const TgTensorDesc* 
  * previous kernel has completed either way).  Returns the previous setting.
  * No reference counterpart. */
 TG_API int32_t tg_set_static_weights(int32_t on);
+
+/* Re-reads the TILEGYM_B200_* tuning / debug variables from the environment.  They are otherwise read once,
+ * by the first call that needs one (a launch does not scan the environment).  No reference counterpart. */
+TG_API void tg_reload_env(void);
+
+/* Bound of every wait inside the kernels (on an mbarrier: a TMA copy landing, the tensor core finishing, a
+ * buffer being released), in microseconds; 0 restores the default of 2 s.  A wait that runs out makes its
+ * kernel record a code, leave its loops, free its TMEM and return; tg_device_status() then reports
+ * TG_ERR_TIMEOUT.  After such a report the output of that launch is undefined and the split-K arrival
+ * counters at the start of the workspace it used may be non-zero: clear the first 64 KiB of that workspace
+ * before using it again.  Returns the previous setting.  No reference counterpart (its kernels
+ * contain no device-side waits of their own). */
+TG_API uint32_t tg_set_wait_limit_us(uint32_t limit_us);
+
+/* Runs the bounded-wait give-up path once, safely: one thread block with the kernels' role layout allocates
+ * TMEM and waits, with the kernels' own wait code, for a barrier nothing arrives on; after limit_us
+ * (1 .. 1000000) the wait gives up, the block frees its TMEM and returns normally, and tg_device_status()
+ * reports TG_ERR_TIMEOUT (detail = role * 1000 + 99) once.  Nothing faults or hangs and the context stays
+ * usable.  No reference counterpart. */
+TG_API int32_t tg_selftest_wait_timeout(uint32_t limit_us, int32_t device_id, uint64_t stream);
 
 /* Reads (and clears) the device-side status word of `device_id` after
  * synchronising the device: 0, or TG_ERR_TIMEOUT with *detail set to a code

@@ -186,6 +186,29 @@ def ref_w8a8_block_fp8_matmul(
     return C.to(output_dtype).reshape(*A.shape[:-1], B.shape[0])
 
 
+def ref_fp8_block_scaled_mm(
+    A: torch.Tensor,
+    B: torch.Tensor,
+    As: torch.Tensor,
+    Bs: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    out_dtype: torch.dtype = torch.bfloat16,
+    c: Optional[torch.Tensor] = None,
+    beta: float = 0.0,
+) -> torch.Tensor:
+    """The block-scaled GEMM above with the epilogue of a Linear layer: the fp32 product of
+    tests/suites/unsloth/test_fp8.py:158-191 plus bias[n] (and beta * c) in fp32, ONE cast at the end.
+    The reference operator has no bias; this is the form the benchmark description states
+    (fp32 accumulate, optional bias, one rounding to bf16)."""
+    A_deq, B_deq = dequant_block_scaled(A, B, As, Bs, 128, 128)
+    C = A_deq @ B_deq.T
+    if bias is not None:
+        C = C + bias.float()
+    if beta != 0.0:
+        C = C + beta * c.float().reshape(C.shape)
+    return C.to(out_dtype).reshape(*A.shape[:-1], B.shape[0])
+
+
 def ref_ragged_block_scaled_bmm(
     a: torch.Tensor,
     b: torch.Tensor,
@@ -287,6 +310,22 @@ def ref_matmul(a: torch.Tensor, b: torch.Tensor, trans_b: bool = False) -> torch
     out = a.float() @ bb
     if a.dtype == torch.float8_e4m3fn:
         return out.clamp(-E4M3_MAX, E4M3_MAX).to(a.dtype)
+    if a.dtype == torch.float8_e5m2:
+        return out.clamp(-57344.0, 57344.0).to(a.dtype)
+    return out.to(a.dtype)
+
+
+def ref_bmm(a: torch.Tensor, b: torch.Tensor, transpose_a: bool = False, transpose_b: bool = False) -> torch.Tensor:
+    """Batched matmul, output in the input dtype (tests/ops/test_bmm.py:17-23: transpose, torch.bmm).  Computed
+    in fp32 with one cast at the end (torch.bmm on f16 CPU tensors accumulates in fp32 as well); 8-bit inputs
+    are clamped to the format's range before the cast back, as ref_matmul does."""
+    af = (a.transpose(1, 2) if transpose_a else a).float()
+    bf = (b.transpose(1, 2) if transpose_b else b).float()
+    out = torch.bmm(af, bf)
+    if a.dtype == torch.float8_e4m3fn:
+        return out.clamp(-E4M3_MAX, E4M3_MAX).to(a.dtype)
+    if a.dtype == torch.float8_e5m2:
+        return out.clamp(-57344.0, 57344.0).to(a.dtype)
     return out.to(a.dtype)
 
 

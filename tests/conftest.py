@@ -33,6 +33,14 @@ def load_golden(name: str) -> dict:
     return out
 
 
+def load_golden16(name: str, dtype: torch.dtype):
+    """A gemm_alpha_beta fixture whose a, b, c and out are all stored as raw 16-bit patterns of `dtype`
+    (float16 or bfloat16): returns (a, b, c, out, alpha, beta)."""
+    z = np.load(os.path.join(GOLDEN, name))
+    t = [torch.from_numpy(z[k].view(np.int16).copy()).view(dtype) for k in ("a", "b", "c", "out")]
+    return (*t, float(z["alpha"]), float(z["beta"]))
+
+
 @pytest.fixture(scope="session")
 def dev():
     if not torch.cuda.is_available():

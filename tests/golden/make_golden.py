@@ -92,6 +92,21 @@ def main(ref_root: str, only=()) -> None:
             os.path.join(HERE, f"gemm_alpha_beta_{m}_{alpha}_{beta}.npz"),
             a=bits(a), b=bits(b), c=bits(c), out=bits(out), alpha=np.float32(alpha), beta=np.float32(beta),
         )
+    # --- the same operator on 16-bit operands (the test's (float16 -> float16) and (bfloat16 -> bfloat16) rows,
+    # test_flashinfer_gemm_alpha_beta.py:44-53), same recipe, through the same reference ------------------
+    for dt, tag in ([(torch.float16, "f16"), (torch.bfloat16, "bf16")] if want("gemm_alpha_beta16") else []):
+        m = n = k = 256
+        alpha, beta = 1.5, 2.0
+        torch.manual_seed(0)
+        a = torch.rand(m * k, dtype=torch.float16).to(dt).view(m, k)
+        b = torch.rand(k * n, dtype=torch.float16).to(dt).view(n, k)
+        c = torch.rand((m, n), dtype=dt)
+        out = G.reference(a, b, c.clone(), False, True, alpha, beta, dt)
+        as16 = lambda t: t.view(torch.int16).numpy().view(np.uint16)  # noqa: E731  raw bits of either 16-bit type
+        np.savez_compressed(
+            os.path.join(HERE, f"gemm_alpha_beta_{tag}_{m}_{alpha}_{beta}.npz"),
+            a=as16(a), b=as16(b), c=as16(c), out=as16(out), alpha=np.float32(alpha), beta=np.float32(beta),
+        )
     # --- per_token_group_quant_8bit: recipe of test_per_token_group_quant_8bit.py:119-133 (seed 0, bf16
     # randn, eps 1e-10) through that file's torch reference; one all-zero group exercises the eps clamp -----
     if want("group_quant"):

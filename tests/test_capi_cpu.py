@@ -48,7 +48,7 @@ def test_pertensor_argument_checks():
     c = torch.zeros(128, 128, dtype=torch.bfloat16)
 
     def call(C, A, B, bias=None):
-        return L.tg_fp8_gemm_pertensor(_d(C), _d(A), _d(B), 0, 0, 1.0, _d(bias), 0.0, 0, 0, 0, 0)
+        return L.tg_fp8_gemm_pertensor(_d(C), _d(A), _d(B), 0, 0, 1.0, _d(bias), 0.0, 0, 0, 0, 0, 0)
 
     assert call(c, a, None) == -5 and b"null" in L.tg_last_error_string()
     assert call(c, a.view(torch.uint8), a) == -2
@@ -57,6 +57,9 @@ def test_pertensor_argument_checks():
     assert call(torch.zeros(64, 128, dtype=torch.bfloat16), a, a) == -6  # C shape
     assert call(c, torch.zeros(128, 136, dtype=torch.float8_e4m3fn), torch.zeros(128, 136, dtype=torch.float8_e4m3fn)) == -8  # K % 16
     assert call(c, a, a, torch.zeros(64)) == -6  # bias length
+    e5 = torch.zeros(128, 128, dtype=torch.float8_e5m2)
+    assert call(c, a, e5) == -2 and b"same 8-bit format" in L.tg_last_error_string()
+    assert L.tg_fp8_gemm_pertensor(_d(c), _d(a), _d(a), 0, 0, 1.0, None, 0.0, 0, 0, 6, 0, 0) == -6  # unknown flags
     # empty problems are accepted without a device
     e = torch.zeros(0, 128, dtype=torch.float8_e4m3fn)
     assert call(torch.zeros(0, 128, dtype=torch.bfloat16), e, a) == 0
@@ -69,13 +72,15 @@ def test_blockscaled_argument_checks():
     b = torch.zeros(128, 256, dtype=torch.float8_e4m3fn)
     As, Bs = torch.ones(128, 2), torch.ones(1, 2)
 
-    def call(As_, Bs_, bn=128, bk=128):
-        return L.tg_fp8_gemm_blockscaled(_d(c), _d(a), _d(b), _d(As_), _d(Bs_), bn, bk, 0, 0, 0, 0)
+    def call(As_, Bs_, bn=128, bk=128, bias=None):
+        return L.tg_fp8_gemm_blockscaled(_d(c), _d(a), _d(b), _d(As_), _d(Bs_), bn, bk, _d(bias), 0.0, 0, 0, 0, 0)
 
     assert call(As, Bs, 64, 128) == -6 and b"128" in L.tg_last_error_string()
     assert call(torch.ones(128, 3), Bs) == -6
     assert call(As, torch.ones(2, 2)) == -6
     assert call(As.half(), Bs) == -2
+    assert call(As, Bs, bias=torch.zeros(64)) == -6  # bias length
+    assert call(As, Bs, bias=torch.zeros(128, dtype=torch.int32)) == -2
 
 
 def test_grouped_blockscaled_argument_checks():
@@ -86,9 +91,11 @@ def test_grouped_blockscaled_argument_checks():
     As, Bs = torch.zeros(256, 2), torch.zeros(2, 1, 2)
     ind = torch.zeros(3, dtype=torch.int32)
 
-    def call(c=C, a=A, b=B, sa=As, sb=Bs, ptr=None, bn=128):
+    def call(c=C, a=A, b=B, sa=As, sb=Bs, ptr=None, bn=128, bias=None):
         return L.tg_fp8_gemm_blockscaled_grouped(_d(c), _d(a), _d(b), _d(sa), _d(sb),
-                                                 ind.data_ptr() if ptr is None else ptr, bn, 128, 0, 0)
+                                                 ind.data_ptr() if ptr is None else ptr, bn, 128, _d(bias), 0.0, 0, 0)
+
+    assert call(bias=torch.zeros(128)) == -6  # a grouped bias is [groups, N]
 
     assert call(b=B[0]) == -6  # B must be 3-D
     assert call(b=torch.zeros(2, 128, 128, dtype=torch.float8_e4m3fn)) == -6  # K mismatch
@@ -120,6 +127,15 @@ def test_quantiser_argument_checks():
     assert L.tg_per_token_group_quant(_d(y), _d(sg.half()), _d(x), 16, 1e-10, 0, 0, 0) == -2
     assert L.tg_per_token_group_quant(_d(y), _d(sg), None, 16, 1e-10, 0, 0, 0) == -5
     assert b"group_size" in L.tg_last_error_string() or True
+
+
+def test_wait_limit_setter_and_selftest_argument_checks():
+    L = _lib.lib()
+    prev = L.tg_set_wait_limit_us(1500)
+    assert L.tg_set_wait_limit_us(prev) == 1500
+    assert L.tg_selftest_wait_timeout(0, 0, 0) == -6          # a limit is required ...
+    assert L.tg_selftest_wait_timeout(5_000_000, 0, 0) == -6  # ... and it must be short
+    L.tg_reload_env()  # no device needed
 
 
 def test_ops_refuse_cpu_tensors_instead_of_falling_back():

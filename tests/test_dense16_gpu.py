@@ -24,7 +24,7 @@ def test_dense_matmul_matches_oracle(dev, M, N, K, dtype):
     assert out.dtype == dtype and out.shape == (M, N)
     scale = float(ref.float().abs().max())
     torch.testing.assert_close(out.float().cpu(), ref.float(), rtol=1e-2, atol=1e-2 * scale / 8)
-    _lib.device_status(0)
+    _lib.device_status(dev.index)
 
 
 def test_dense_matmul_kn_layout_and_fp32_out(dev):

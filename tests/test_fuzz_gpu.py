@@ -75,4 +75,4 @@ def test_grouped_random_routing(dev, seed):
     out = tg.ragged_block_scaled_bmm(a.to(dev), b.to(dev), As.to(dev), Bs.to(dev), ind.to(dev), max(sizes))
     res = R.check_tolerance(out.float(), ref.float())
     assert res["ok"], (sizes, N, K, res)
-    _lib.device_status(0)
+    _lib.device_status(dev.index)

@@ -26,11 +26,11 @@ KNOBS = ("TILEGYM_B200_BN", "TILEGYM_B200_SPLITS", "TILEGYM_B200_FORCE_PATH", "T
 @pytest.fixture(autouse=True)
 def clean_env_and_status(dev):
     for k in KNOBS:
-        os.environ.pop(k, None)
+        _lib.set_knob(k, None)
     yield
     for k in KNOBS:
-        os.environ.pop(k, None)
-    _lib.device_status(0)  # raises if any bounded device-side wait expired
+        _lib.set_knob(k, None)
+    _lib.device_status(dev.index)  # raises if any bounded device-side wait expired
 
 
 def run_pt(dev, M, N, K, seed, bias=False, out_dtype=torch.bfloat16, outliers=True):
@@ -60,6 +60,28 @@ def test_llama8b_prefill_shapes(dev, N, K):
     run_pt(dev, 4096, N, K, seed=2000 + N + K)
 
 
+@pytest.mark.parametrize("N", [7168, 28672])
+def test_llama70b_gate_up_shard_shapes(dev, N):
+    """BASELINE config 5, the GEMM one rank runs when the 57344 weight rows are sharded 8 or 2 ways
+    (M = 8192, K = 8192): operands drawn and quantised on the GPU with the configuration's distributions,
+    64 sampled rows of the result (all N columns) against the CPU oracle on the same bits."""
+    M, K = 8192, 8192
+    g = torch.Generator(device=dev).manual_seed(5000 + N)
+    x = torch.randn(M, K, generator=g, device=dev, dtype=torch.bfloat16)
+    cols = torch.randperm(K, generator=g, device=dev)[: max(1, round(0.001 * K))]
+    x[:, cols] *= 20.0
+    a8, sa = tg.quant_per_tensor(x)
+    del x
+    w = torch.randn(N, K, generator=g, device=dev, dtype=torch.bfloat16) * 0.02
+    b8, sb = tg.quant_per_tensor(w)
+    del w
+    out = tg.fp8_scaled_mm(a8, b8, sa, sb)
+    rows = torch.randperm(M, generator=torch.Generator().manual_seed(N))[:64].sort().values
+    ref = R.ref_fp8_scaled_mm(a8[rows.to(dev)].cpu(), b8.cpu(), sa.cpu(), sb.cpu())
+    res = R.check_tolerance(out[rows.to(dev)], ref)
+    assert res["ok"], res
+
+
 @pytest.mark.parametrize("M", [1, 8, 16, 64])
 @pytest.mark.parametrize("N,K", [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)])
 def test_llama8b_decode_shapes(dev, M, N, K):
@@ -70,8 +92,8 @@ def test_llama8b_decode_shapes(dev, M, N, K):
 @pytest.mark.parametrize("bn", ["256", "128", "64"])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 128), (300, 520, 1040), (1, 16, 16), (129, 257 * 8, 144)])
 def test_tile_widths_and_tails(dev, bn, M, N, K):
-    os.environ["TILEGYM_B200_BN"] = bn
-    os.environ["TILEGYM_B200_FORCE_PATH"] = "gemm"
+    _lib.set_knob("TILEGYM_B200_BN", bn)
+    _lib.set_knob("TILEGYM_B200_FORCE_PATH", "gemm")
     run_pt(dev, M, N, K, seed=11, bias=True)
 
 
@@ -90,7 +112,7 @@ def test_output_dtypes_and_unaligned_n(dev, out_dtype, M):
 @pytest.mark.parametrize("splits", ["1", "2", "5"])
 @pytest.mark.parametrize("M", [16, 256])
 def test_split_k_matches_unsplit(dev, splits, M):
-    os.environ["TILEGYM_B200_SPLITS"] = splits
+    _lib.set_knob("TILEGYM_B200_SPLITS", splits)
     run_pt(dev, M, 512, 4096, seed=5)
 
 
@@ -100,10 +122,10 @@ def test_small_m_cluster_and_workspace_reductions_agree(dev, M, ws):
     """The K splits are reduced either through distributed shared memory (cluster, default) or through
     the global workspace; both add the partial sums in split order, so the bits are identical."""
     a8, b8, sa, sb = (t.to(dev) for t in R.gen_per_tensor_case(M, 1024, 8192, 60 + M))
-    os.environ["TILEGYM_B200_SPLITS"] = "4"  # same split count on both paths
-    os.environ["TILEGYM_B200_SMALLM_WS"] = ws
+    _lib.set_knob("TILEGYM_B200_SPLITS", "4")  # same split count on both paths
+    _lib.set_knob("TILEGYM_B200_SMALLM_WS", ws)
     out = tg.fp8_scaled_mm(a8, b8, sa, sb)
-    os.environ["TILEGYM_B200_SMALLM_WS"] = "1" if ws == "0" else "0"
+    _lib.set_knob("TILEGYM_B200_SMALLM_WS", "1" if ws == "0" else "0")
     other = tg.fp8_scaled_mm(a8, b8, sa, sb)
     assert R.check_tolerance(out, R.ref_fp8_scaled_mm(a8.cpu(), b8.cpu(), sa.cpu(), sb.cpu()))["ok"]
     assert torch.equal(out, other)
@@ -111,7 +133,7 @@ def test_small_m_cluster_and_workspace_reductions_agree(dev, M, ws):
 
 @pytest.mark.parametrize("group_m", ["1", "3", "64"])
 def test_cta_pair_kernel_raster_groups(dev, group_m):
-    os.environ["TILEGYM_B200_GROUP_M"] = group_m
+    _lib.set_knob("TILEGYM_B200_GROUP_M", group_m)
     run_pt(dev, 1280, 1536, 512, seed=12, bias=True)
 
 
@@ -119,9 +141,9 @@ def test_cta_pair_kernel_raster_groups(dev, group_m):
 @pytest.mark.parametrize("M,N,K", [(512, 768, 1024), (1000, 1100, 400), (4096, 6144, 512)])
 def test_cta_pair_kernel_tail_slices(dev, tail_div, M, N, K):
     """The tiles of the last wave are cut into 1, 2 or 4 column slices; the result does not change."""
-    os.environ["TILEGYM_B200_TAIL_DIV"] = tail_div
+    _lib.set_knob("TILEGYM_B200_TAIL_DIV", tail_div)
     out = run_pt(dev, M, N, K, seed=14, bias=True)
-    os.environ["TILEGYM_B200_TAIL_DIV"] = "1"
+    _lib.set_knob("TILEGYM_B200_TAIL_DIV", "1")
     a8, b8, sa, sb = (t.to(dev) for t in R.gen_per_tensor_case(M, N, K, 14))
     bvec = torch.randn(N, generator=torch.Generator().manual_seed(21)).to(dev)
     assert torch.equal(out, tg.fp8_scaled_mm(a8, b8, sa, sb, bvec))
@@ -130,7 +152,7 @@ def test_cta_pair_kernel_tail_slices(dev, tail_div, M, N, K):
 def test_cta_pair_and_single_cta_kernels_agree(dev):
     a8, b8, sa, sb = (t.to(dev) for t in R.gen_per_tensor_case(1024, 768, 2048, 13))
     pair = tg.fp8_scaled_mm(a8, b8, sa, sb)
-    os.environ["TILEGYM_B200_2CTA"] = "0"
+    _lib.set_knob("TILEGYM_B200_2CTA", "0")
     single = tg.fp8_scaled_mm(a8, b8, sa, sb)
     assert torch.equal(pair, single)  # same fp32 accumulation order inside the tensor core, same epilogue
 
@@ -306,10 +328,10 @@ def test_block_scaled_cta_pair_kernel_tails_and_agreement(dev, M, N, K):
     Bs = torch.rand(-(-N // 128), -(-K // 128), generator=g) + 0.1
     ref = R.ref_w8a8_block_fp8_matmul(A, B, As, Bs, [128, 128])
     args = [t.to(dev) for t in (A, B, As, Bs)]
-    os.environ["TILEGYM_B200_BS_PAIR"] = "1"  # the CTA-pair kernel is opt-in
+    _lib.set_knob("TILEGYM_B200_BS_PAIR", "1")  # the CTA-pair kernel is opt-in
     pair = tg.w8a8_block_fp8_matmul(*args, [128, 128])
     torch.testing.assert_close(pair.cpu(), ref, rtol=1e-4, atol=1e-4)
-    os.environ["TILEGYM_B200_BS_PAIR"] = "0"
+    _lib.set_knob("TILEGYM_B200_BS_PAIR", "0")
     single = tg.w8a8_block_fp8_matmul(*args, [128, 128])
     torch.testing.assert_close(single, pair, rtol=1e-5, atol=1e-5)  # the 128 x 128 kernel may split K here
 
@@ -326,20 +348,20 @@ def test_block_scaled_wide_tile_kernel_tails_and_agreement(dev, M, N, K, dtype):
     Bs = torch.rand(-(-N // 128), -(-K // 128), generator=g) + 0.1
     ref = R.ref_w8a8_block_fp8_matmul(A, B, As, Bs, [128, 128], dtype)
     args = [t.to(dev) for t in (A, B, As, Bs)]
-    os.environ["TILEGYM_B200_SPLITS"] = "1"
-    os.environ["TILEGYM_B200_BS_WIDE"] = "1"
+    _lib.set_knob("TILEGYM_B200_SPLITS", "1")
+    _lib.set_knob("TILEGYM_B200_BS_WIDE", "1")
     wide = tg.w8a8_block_fp8_matmul(*args, [128, 128], dtype)
     if dtype == torch.float32:
         torch.testing.assert_close(wide.cpu(), ref, rtol=1e-4, atol=1e-4)
     else:
         assert R.check_tolerance(wide, ref)["ok"]
-    os.environ["TILEGYM_B200_BS_WIDE"] = "0"
+    _lib.set_knob("TILEGYM_B200_BS_WIDE", "0")
     narrow = tg.w8a8_block_fp8_matmul(*args, [128, 128], dtype)
     assert torch.equal(wide, narrow)
 
 
 def test_block_scaled_split_k_and_leading_dims(dev):
-    os.environ["TILEGYM_B200_SPLITS"] = "3"
+    _lib.set_knob("TILEGYM_B200_SPLITS", "3")
     a8, b8, As, Bs = R.gen_block_scaled_case(2 * 70, 256, 2048, seed=9)
     ref = R.ref_w8a8_block_fp8_matmul(a8, b8, As, Bs, None, torch.bfloat16).view(2, 70, 256)
     out = tg.w8a8_block_fp8_matmul(a8.view(2, 70, 2048).to(dev), b8.to(dev), As.view(2, 70, 16).to(dev), Bs.to(dev),
@@ -350,14 +372,14 @@ def test_block_scaled_split_k_and_leading_dims(dev):
 def test_block_scaled_forced_split_count_is_clamped_to_the_workspace(dev):
     """A split count whose partial tiles would not fit the workspace (here 192 tiles x 12 splits x 64 KiB) is
     reduced by the library instead of being taken literally."""
-    os.environ["TILEGYM_B200_SPLITS"] = "12"
-    os.environ["TILEGYM_B200_BS_WIDE"] = "0"
+    _lib.set_knob("TILEGYM_B200_SPLITS", "12")
+    _lib.set_knob("TILEGYM_B200_BS_WIDE", "0")
     a8, b8, As, Bs = R.gen_block_scaled_case(128, 24576, 1536, seed=77)
     ref = R.ref_w8a8_block_fp8_matmul(a8, b8, As, Bs, [128, 128], torch.bfloat16)
     out = tg.w8a8_block_fp8_matmul(a8.to(dev), b8.to(dev), As.to(dev), Bs.to(dev), [128, 128], torch.bfloat16)
     res = R.check_tolerance(out, ref)
     assert res["ok"], res
-    _lib.device_status(0)  # no fault, no expired wait
+    _lib.device_status(dev.index)  # no fault, no expired wait
 
 
 def test_block_scaled_rejects_other_blocks_and_dtypes(dev):

@@ -58,7 +58,7 @@ def test_ragged_unaligned_and_empty_groups(dev, out_dtype):
     else:
         res = R.check_tolerance(out.float(), ref.float())
         assert res["ok"], res
-    _lib.device_status(0)
+    _lib.device_status(dev.index)
 
 
 def test_each_group_equals_the_dense_kernel(dev):
@@ -70,7 +70,7 @@ def test_each_group_equals_the_dense_kernel(dev):
     a8, b, As, bs, ind = make_case(sizes, 512, 1024, seed=9)
     args = [t.to(dev) for t in (a8, b, As, bs, ind)]
     out = tg.ragged_block_scaled_bmm(*args, 384)
-    os.environ["TILEGYM_B200_SPLITS"] = "1"  # the dense kernel would split K on problems this small
+    _lib.set_knob("TILEGYM_B200_SPLITS", "1")  # the dense kernel would split K on problems this small
     try:
         lo = 0
         for q, sz in enumerate(sizes):
@@ -79,7 +79,7 @@ def test_each_group_equals_the_dense_kernel(dev):
             assert torch.equal(out[lo:lo + sz], dense)
             lo += sz
     finally:
-        os.environ.pop("TILEGYM_B200_SPLITS", None)
+        _lib.set_knob("TILEGYM_B200_SPLITS", None)
 
 
 def test_rows_outside_every_group_are_left_alone_and_bad_offsets_are_clamped(dev):
@@ -90,9 +90,10 @@ def test_rows_outside_every_group_are_left_alone_and_bad_offsets_are_clamped(dev
     c = torch.full((256, 256), 7.0, dtype=torch.bfloat16, device=dev)
     args = [t.to(dev) for t in (a8, b, As, bs, ind)]
     rc = L.tg_fp8_gemm_blockscaled_grouped(_lib.ref(_lib.desc(c)), *[_lib.ref(_lib.desc(t)) for t in args[:4]],
-                                            args[4].data_ptr(), 128, 128, 0, torch.cuda.current_stream().cuda_stream)
+                                            args[4].data_ptr(), 128, 128, None, 0.0, dev.index,
+                                           torch.cuda.current_stream().cuda_stream)
     _lib.check_rc(rc)
-    _lib.device_status(0)
+    _lib.device_status(dev.index)
     assert bool((c[:64] == 7.0).all())
     res = R.check_tolerance(c[64:], ref[64:])
     assert res["ok"], res

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import GOLDEN, load_golden
+from conftest import GOLDEN, load_golden, load_golden16
 from oracle import torch_ref as R
 
 
@@ -98,6 +98,33 @@ def test_gemm_alpha_beta_matches_reference_fixture(name):
     # the fp32-accumulate form the kernels follow agrees within the reference test's tolerance
     f32 = R.ref_gemm_alpha_beta(g["a"], g["b"], g["c"], g["alpha"], g["beta"])
     torch.testing.assert_close(f32.float(), g["out"].float(), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("tag,dt", [("f16", torch.float16), ("bf16", torch.bfloat16)])
+def test_gemm_alpha_beta_16bit_matches_reference_fixture(tag, dt):
+    """The (float16 -> float16) and (bfloat16 -> bfloat16) rows of the reference test, its tolerance."""
+    a, b, c, out, alpha, beta = load_golden16(f"gemm_alpha_beta_{tag}_256_1.5_2.0.npz", dt)
+    f32 = R.ref_gemm_alpha_beta(a, b, c, alpha, beta)
+    assert f32.dtype == dt
+    torch.testing.assert_close(f32.float(), out.float(), rtol=1e-2, atol=1e-2)
+
+
+def test_block_scaled_bias_form_reduces_to_the_reference_form():
+    a8, b8, As, Bs = R.gen_block_scaled_case(40, 256, 384, seed=2)
+    plain = R.ref_w8a8_block_fp8_matmul(a8, b8, As, Bs, None, torch.float32)
+    assert torch.equal(R.ref_fp8_block_scaled_mm(a8, b8, As, Bs, None, torch.float32), plain)
+    bias = torch.randn(256)
+    c = torch.randn(40, 256)
+    full = R.ref_fp8_block_scaled_mm(a8, b8, As, Bs, bias, torch.float32, c, 0.5)
+    torch.testing.assert_close(full, plain + bias + 0.5 * c, rtol=1e-6, atol=1e-6)
+
+
+def test_ref_bmm_follows_torch_bmm():
+    torch.manual_seed(1)
+    a, b = torch.rand(3, 20, 33, dtype=torch.float16), torch.rand(3, 40, 33, dtype=torch.float16)
+    torch.testing.assert_close(R.ref_bmm(a, b, False, True), torch.bmm(a, b.transpose(1, 2)), rtol=1e-3, atol=1e-3)
+    at = a.transpose(1, 2).contiguous()
+    assert torch.equal(R.ref_bmm(at, b, True, True), R.ref_bmm(a, b, False, True))
 
 
 def test_per_tensor_forms_agree():

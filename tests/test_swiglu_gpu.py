@@ -41,7 +41,7 @@ def test_swiglu_epilogue_matches_oracle(dev, M, I, K, bias, dtype):
     assert out.shape == (M, I) and out.dtype == dtype
     res = R.check_tolerance(out.float(), ref.float())
     assert res["ok"], res
-    _lib.device_status(0)
+    _lib.device_status(dev.index)
 
 
 def test_swiglu_equals_two_step_path_within_rounding(dev):

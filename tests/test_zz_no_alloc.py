@@ -44,7 +44,7 @@ def test_two_calls_in_a_row_match_the_regular_entry_point(dev):
         _static_call(a8, b8, sa, sb, out, bias)
         res = R.check_tolerance(out, expect)
         assert res["ok"], (M, N, K, res)
-    _lib.device_status(0)
+    _lib.device_status(dev.index)
 
 
 def test_same_call_twice_gives_identical_bits(dev):

@@ -3,13 +3,15 @@
 Public surface (same names and signatures as the reference operators):
     w8a8_block_fp8_matmul, act_quant, weight_dequant   (tilegym.suites.unsloth.ops)
     gemm_alpha_beta                                    (tilegym.suites.flashinfer.ops)
-    matmul                                             (tilegym.ops)
-plus the per-tensor pieces the reference lacks (fp8_scaled_mm, quant_per_tensor,
+    matmul, bmm                                        (tilegym.ops)
+plus the per-tensor pieces the reference lacks (fp8_scaled_mm, fp8_block_scaled_mm, quant_per_tensor,
 weight_quant_block, FP8Linear) and apply_tilegym_kernel_to_llama / _deepseek_v2.
 """
 
 from .ops import (  # noqa: F401
     act_quant,
+    bmm,
+    fp8_block_scaled_mm,
     fp8_scaled_mm,
     per_token_group_quant_8bit,
     ragged_block_scaled_bmm,
@@ -19,6 +21,7 @@ from .ops import (  # noqa: F401
     gemm_alpha_beta,
     matmul,
     quant_per_tensor,
+    reset_workspaces,
     set_static_weights,
     w8a8_block_fp8_matmul,
     weight_dequant,

@@ -78,7 +78,7 @@ SIGNATURES = {
     "tg_fp8_gemm_pertensor": (
         ctypes.c_int32,
         [_P, _P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_float, _P, ctypes.c_float, ctypes.c_uint64,
-         ctypes.c_uint64, ctypes.c_int32, ctypes.c_uint64],
+         ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int32, ctypes.c_uint64],
     ),
     "tg_fp8_gemm_pertensor_allgather": (
         ctypes.c_int32,
@@ -92,8 +92,8 @@ SIGNATURES = {
     ),
     "tg_fp8_gemm_blockscaled": (
         ctypes.c_int32,
-        [_P, _P, _P, _P, _P, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int32,
-         ctypes.c_uint64],
+        [_P, _P, _P, _P, _P, ctypes.c_int32, ctypes.c_int32, _P, ctypes.c_float, ctypes.c_uint64, ctypes.c_uint64,
+         ctypes.c_int32, ctypes.c_uint64],
     ),
     "tg_fp8_gemm_pertensor_swiglu": (
         ctypes.c_int32,
@@ -105,7 +105,8 @@ SIGNATURES = {
     ),
     "tg_fp8_gemm_blockscaled_grouped": (
         ctypes.c_int32,
-        [_P, _P, _P, _P, _P, ctypes.c_uint64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64],
+        [_P, _P, _P, _P, _P, ctypes.c_uint64, ctypes.c_int32, ctypes.c_int32, _P, ctypes.c_float, ctypes.c_int32,
+         ctypes.c_uint64],
     ),
     "tg_act_quant": (ctypes.c_int32, [_P, _P, _P, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64]),
     "tg_per_token_group_quant": (
@@ -119,6 +120,9 @@ SIGNATURES = {
     ),
     "tg_weight_quant_block": (ctypes.c_int32, [_P, _P, _P, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64]),
     "tg_device_status": (ctypes.c_int32, [ctypes.c_int32, ctypes.POINTER(ctypes.c_int32)]),
+    "tg_reload_env": (None, []),
+    "tg_set_wait_limit_us": (ctypes.c_uint32, [ctypes.c_uint32]),
+    "tg_selftest_wait_timeout": (ctypes.c_int32, [ctypes.c_uint32, ctypes.c_int32, ctypes.c_uint64]),
 }
 
 
@@ -181,3 +185,13 @@ def device_status(device_index: int) -> None:
     """Synchronises the device and raises if a kernel's bounded wait expired."""
     detail = ctypes.c_int32(0)
     check_rc(lib().tg_device_status(device_index, ctypes.byref(detail)))
+
+
+def set_knob(name: str, value) -> None:
+    """Sets (value) or removes (None) a TILEGYM_B200_* tuning variable and makes the library re-read them
+    (it reads the environment once, not per launch)."""
+    if value is None:
+        os.environ.pop(name, None)
+    else:
+        os.environ[name] = str(value)
+    lib().tg_reload_env()

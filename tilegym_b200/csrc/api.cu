@@ -88,10 +88,42 @@ int32_t init_device(int dev) {
   return TG_OK;
 }
 
-int env_int(const char* name, int dflt) {
-  const char* v = getenv(name);
-  return (v && *v) ? atoi(v) : dflt;
+// Tuning / debug knobs come from TILEGYM_B200_* environment variables.  They are read ONCE, on the first call that
+// needs one (a dozen getenv scans per GEMM launch cost more than a decode kernel's set-up), and again whenever
+// tg_reload_env() is called (tests flip knobs between calls).
+enum Knob : int {
+  kKnobSplits, kKnobTileRows, kKnobForcePath, kKnobPairMinTiles, kKnob2Cta, kKnobBn, kKnobSmallmWs, kKnobPdl,
+  kKnobStaticWeights, kKnobGroupM, kKnobTailDiv, kKnobTmaStore, kKnobBsWideMin, kKnobBsWide, kKnobBsPair,
+  kKnobBsSmallm, kKnobCount
+};
+const char* const kKnobNames[kKnobCount] = {
+    "TILEGYM_B200_SPLITS", "TILEGYM_B200_TILE_ROWS", "TILEGYM_B200_FORCE_PATH", "TILEGYM_B200_PAIR_MIN_TILES",
+    "TILEGYM_B200_2CTA", "TILEGYM_B200_BN", "TILEGYM_B200_SMALLM_WS", "TILEGYM_B200_PDL",
+    "TILEGYM_B200_STATIC_WEIGHTS", "TILEGYM_B200_GROUP_M", "TILEGYM_B200_TAIL_DIV", "TILEGYM_B200_TMA_STORE",
+    "TILEGYM_B200_BS_WIDE_MIN", "TILEGYM_B200_BS_WIDE", "TILEGYM_B200_BS_PAIR", "TILEGYM_B200_BS_SMALLM"};
+struct KnobTable {
+  bool loaded = false;
+  bool present[kKnobCount] = {};
+  int value[kKnobCount] = {};
+  int force_path = 0;  // TILEGYM_B200_FORCE_PATH: 0 unset, 1 "gemm", 2 "smallm"
+};
+KnobTable g_knobs;
+
+void load_knobs() {
+  for (int i = 0; i < kKnobCount; ++i) {
+    const char* v = getenv(kKnobNames[i]);
+    g_knobs.present[i] = v != nullptr && *v != 0;
+    g_knobs.value[i] = g_knobs.present[i] ? atoi(v) : 0;
+  }
+  const char* f = getenv(kKnobNames[kKnobForcePath]);
+  g_knobs.force_path = (f && !strcmp(f, "gemm")) ? 1 : (f && !strcmp(f, "smallm")) ? 2 : 0;
+  g_knobs.loaded = true;
 }
+inline bool knob_set(Knob k) {
+  if (!g_knobs.loaded) load_knobs();
+  return g_knobs.present[k];
+}
+inline int knob(Knob k, int dflt) { return knob_set(k) ? g_knobs.value[k] : dflt; }
 
 // 2-D map over a row-major e4m3 matrix [rows, K] with row pitch `pitch` bytes;
 // boxes of 128 bytes (one swizzle row) x box_rows rows; out-of-range elements read as zero.
@@ -125,10 +157,12 @@ int32_t make_out_map(CUtensorMap* map, uint64_t ptr, int64_t rows, int64_t cols,
 bool is_out_dtype(int32_t d) { return d == TG_F32 || d == TG_F16 || d == TG_BF16; }
 int esize(int32_t d) { return d == TG_F32 ? 4 : (d == TG_F16 || d == TG_BF16) ? 2 : 1; }
 
-// A 2-D e4m3 operand with unit inner stride, 16-byte aligned base and pitch.
-int32_t check_operand(const TgTensorDesc* t, const char* name) {
+// A 2-D e4m3 (or, where the entry point takes it, e5m2) operand with unit inner stride, 16-byte aligned base and pitch.
+int32_t check_operand(const TgTensorDesc* t, const char* name, bool allow_e5m2 = false) {
   if (t == nullptr) return fail(TG_ERR_NULL, "%s descriptor is null", name);
-  if (t->dtype != TG_F8E4M3) return fail(TG_ERR_DTYPE, "%s must be float8_e4m3fn (dtype code 7), got %d", name, t->dtype);
+  if (t->dtype != TG_F8E4M3 && !(allow_e5m2 && t->dtype == TG_F8E5M2))
+    return fail(TG_ERR_DTYPE, "%s must be float8_e4m3fn (dtype code 7)%s, got %d", name,
+                allow_e5m2 ? " or float8_e5m2 (5)" : "", t->dtype);
   if (t->ndim != 2) return fail(TG_ERR_ARGS, "%s must be 2-D, got %d-D", name, t->ndim);
   if (t->shape[0] < 0 || t->shape[1] <= 0) return fail(TG_ERR_ARGS, "%s has a bad shape", name);
   if (t->strides[1] != 1 || t->strides[0] < t->shape[1]) return fail(TG_ERR_ARGS, "%s rows must be contiguous", name);
@@ -150,9 +184,29 @@ int32_t check_output(const TgTensorDesc* C, int64_t M, int64_t N) {
   return TG_OK;
 }
 
+// A bias (f32 / f16 / bf16, or NULL): groups == 0 wants a contiguous [N] vector, groups > 0 a contiguous
+// [groups, N] matrix (one bias row per weight of a grouped GEMM).
+int32_t check_bias(const TgTensorDesc* bias, int64_t groups, int64_t N) {
+  if (bias == nullptr) return TG_OK;
+  if (bias->dtype != TG_F32 && bias->dtype != TG_BF16 && bias->dtype != TG_F16)
+    return fail(TG_ERR_DTYPE, "bias must be f32, f16 or bf16");
+  if (groups == 0) {
+    if (bias->ndim != 1 || bias->shape[0] != N || bias->strides[0] != 1)
+      return fail(TG_ERR_ARGS, "bias must be a contiguous vector of N elements");
+  } else if (bias->ndim != 2 || bias->shape[0] != groups || bias->shape[1] != N || bias->strides[1] != 1 ||
+             bias->strides[0] != N) {
+    return fail(TG_ERR_ARGS, "bias must be a contiguous [groups, N] matrix");
+  }
+  if (bias->ptr == 0 && N > 0) return fail(TG_ERR_NULL, "bias data pointer is null");
+  return TG_OK;
+}
+
 // Process-wide promise (tg_set_static_weights): the B operand of small-M GEMMs is never written by the
 // kernel that precedes the GEMM on its stream (weights of a Linear layer), see GemmParams::flags.
 int32_t g_static_weights = 0;
+
+// Bound of every device-side wait, microseconds (tg_set_wait_limit_us); 0 = the kernels' 2 s default.
+uint32_t g_wait_limit_us = 0;
 
 constexpr uint64_t kWsCounterBytes = 64ull << 10;
 constexpr uint64_t kWsPartialBytes = 48ull << 20;
@@ -168,7 +222,7 @@ void choose_splits(int tiles, int num_kb, int num_sms, int64_t tile_floats, int 
     const int max_by_k = num_kb / min_kb;
     if (s > max_by_k) s = max_by_k;
   }
-  s = env_int("TILEGYM_B200_SPLITS", s);
+  s = knob(kKnobSplits, s);
   if (s < 1) s = 1;
   if (s > num_kb) s = num_kb;
   // the partial tiles of all splits must fit the workspace, whoever chose the split count
@@ -194,13 +248,13 @@ void choose_smallm_config(int64_t N, int num_kb, int num_sms, int mp, int32_t* t
     if (tiles * s > 2ll * num_sms || num_kb / s < 2) break;
     best_s = s;
   }
-  int s = env_int("TILEGYM_B200_SPLITS", best_s);
+  int s = knob(kKnobSplits, best_s);
   if (s < 1) s = 1;
   if (s > 8) s = 8;
   if (s > num_kb) s = num_kb;
   int per = (num_kb + s - 1) / s;
   s = (num_kb + per - 1) / per;
-  int tr = env_int("TILEGYM_B200_TILE_ROWS", best_tr);
+  int tr = knob(kKnobTileRows, best_tr);
   tr = (tr / 8) * 8;
   if (tr < 16) tr = 16;
   if (tr > 128) tr = 128;
@@ -289,6 +343,7 @@ int32_t api_check_output(const TgTensorDesc* C, int64_t M, int64_t N) { return c
 int32_t api_make_map(CUtensorMap* map, uint64_t ptr, int64_t rows, int64_t K, int64_t pitch, int box_rows) {
   return make_map(map, ptr, rows, K, pitch, box_rows);
 }
+uint32_t api_wait_limit_us() { return g_wait_limit_us; }
 int32_t api_init_device(int dev, int* num_sms, int32_t** status) {
   int32_t rc = init_device(dev);
   if (rc != TG_OK) return rc;
@@ -324,6 +379,14 @@ int32_t tg_plan_splits(int32_t kind, int64_t M, int64_t N, int64_t K, int32_t nu
   return TG_OK;
 }
 
+void tg_reload_env(void) { load_knobs(); }
+
+uint32_t tg_set_wait_limit_us(uint32_t limit_us) {
+  const uint32_t old = g_wait_limit_us;
+  g_wait_limit_us = limit_us;
+  return old;
+}
+
 int32_t tg_set_static_weights(int32_t on) {
   const int32_t old = g_static_weights;
   g_static_weights = on ? 1 : 0;
@@ -339,23 +402,19 @@ uint64_t tg_fp8_gemm_workspace_bytes(int64_t, int64_t, int64_t) { return kWsCoun
 static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B, uint64_t scale_a,
                               uint64_t scale_b, float alpha, const TgTensorDesc* bias, float beta, uint64_t workspace,
                               uint64_t workspace_bytes, const uint64_t* peer_ptrs, int32_t num_peers,
-                              int32_t device_id, uint64_t stream, bool swiglu = false) {
+                              int32_t device_id, uint64_t stream, bool swiglu = false, uint32_t call_flags = 0) {
   int32_t rc;
-  if ((rc = check_operand(A, "A")) != TG_OK) return rc;
-  if ((rc = check_operand(B, "B")) != TG_OK) return rc;
+  if ((rc = check_operand(A, "A", true)) != TG_OK) return rc;
+  if ((rc = check_operand(B, "B", true)) != TG_OK) return rc;
+  if (A->dtype != B->dtype) return fail(TG_ERR_DTYPE, "A and B must have the same 8-bit format (both e4m3 or both e5m2)");
+  const int32_t fmt_flag = A->dtype == TG_F8E5M2 ? 32 : 0;  // GemmParams::flags bit 5: e5m2 operands
   const int64_t M = A->shape[0], K = A->shape[1], N = B->shape[0];
   if (B->shape[1] != K) return fail(TG_ERR_ARGS, "A is [M,%lld] but B is [N,%lld]: K must match", (long long)K, (long long)B->shape[1]);
   if (swiglu && N % 128 != 0) return fail(TG_ERR_ARGS, "the SwiGLU epilogue needs N (gate + up rows) to be a multiple of 128, got %lld", (long long)N);
   // SwiGLU: every 64 accumulator columns (32 gate, 32 up) become 32 output columns
   const int64_t N_out = swiglu ? N / 2 : N;
   if ((rc = check_output(C, M, N_out)) != TG_OK) return rc;
-  if (bias != nullptr) {
-    if (bias->dtype != TG_F32 && bias->dtype != TG_BF16 && bias->dtype != TG_F16)
-      return fail(TG_ERR_DTYPE, "bias must be f32, f16 or bf16");
-    if (bias->ndim != 1 || bias->shape[0] != N || bias->strides[0] != 1)
-      return fail(TG_ERR_ARGS, "bias must be a contiguous vector of N elements");
-    if (bias->ptr == 0 && N > 0) return fail(TG_ERR_NULL, "bias data pointer is null");
-  }
+  if ((rc = check_bias(bias, 0, N)) != TG_OK) return rc;
   if ((scale_a & 3u) || (scale_b & 3u)) return fail(TG_ERR_ALIGN, "scale pointers must be 4-byte aligned");
   if (M == 0 || N == 0) return TG_OK;
 
@@ -370,6 +429,7 @@ static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, cons
 
   GemmParams p;
   memset(&p, 0, sizeof(p));
+  p.wait_limit_us = g_wait_limit_us;
   p.M = static_cast<int32_t>(M);
   p.N = static_cast<int32_t>(N);
   p.K = static_cast<int32_t>(K);
@@ -386,12 +446,11 @@ static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, cons
   p.status = st.status;
   p.ws_counters = reinterpret_cast<uint32_t*>(workspace);
   p.ws_partial = reinterpret_cast<float*>(workspace + kWsCounterBytes);
+  p.flags = fmt_flag;
   const bool have_ws = workspace != 0 && workspace_bytes >= kWsCounterBytes + kWsPartialBytes;
 
-  const char* force = getenv("TILEGYM_B200_FORCE_PATH");
   bool small = M <= 64;
-  if (force && !strcmp(force, "gemm")) small = false;
-  if (force && !strcmp(force, "smallm") && M <= 64) small = true;
+  if (knob_set(kKnobForcePath) && g_knobs.force_path == 1) small = false;
 
   // The output leaves through bulk tensor stores when it is two bytes wide, not accumulated into, and its
   // rows are 16-byte aligned; the fused all-gather needs that path.
@@ -401,9 +460,9 @@ static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, cons
   // of them and M < 512, single-CTA tiles (64 ... 256 columns, optional K split) finish sooner; measured at
   // M = 256: N = K = 4096 11.6 against 12.4 us, N = 4096 K = 14336 25.5 against 29.1 us.
   const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
-  const bool pair_fills = M >= 512 || num_peers > 0 || pair_tiles >= env_int("TILEGYM_B200_PAIR_MIN_TILES", 24);
-  const bool pair_kernel = swiglu || (M >= 256 && N >= 256 && pair_fills && env_int("TILEGYM_B200_2CTA", 1) != 0 &&
-                                      getenv("TILEGYM_B200_BN") == nullptr && getenv("TILEGYM_B200_SPLITS") == nullptr);
+  const bool pair_fills = M >= 512 || num_peers > 0 || pair_tiles >= knob(kKnobPairMinTiles, 24);
+  const bool pair_kernel = swiglu || (M >= 256 && N >= 256 && pair_fills && knob(kKnob2Cta, 1) != 0 &&
+                                      !knob_set(kKnobBn) && !knob_set(kKnobSplits));
   if (swiglu) {
     if (!tma_out_ok) return fail(TG_ERR_ARGS, "the SwiGLU epilogue needs a bf16 / f16 output with 16-byte aligned rows");
     small = false;  // only the CTA-pair kernel has this epilogue (it runs any M; rows past M read as zero)
@@ -419,12 +478,12 @@ static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, cons
     p.tiles_n = static_cast<int32_t>((N + 127) / 128);
     // Default: the K splits of a tile form a thread-block cluster (1, 2, 4 or 8 CTAs) and reduce through
     // distributed shared memory; TILEGYM_B200_SMALLM_WS=1 selects the global-workspace reduction.
-    const bool use_ws = env_int("TILEGYM_B200_SMALLM_WS", 0) != 0;
+    const bool use_ws = knob(kKnobSmallmWs, 0) != 0;
     const bool ws_ok = have_ws;
     // bit 1: launch with programmatic stream serialization (the kernel waits before touching global memory);
     // bit 0: the caller promised static weights, whose loads may then start before that wait
-    p.flags = (env_int("TILEGYM_B200_PDL", 1) != 0 ? 2 : 0) |
-              ((g_static_weights != 0 || env_int("TILEGYM_B200_STATIC_WEIGHTS", 0) != 0) ? 1 : 0);
+    p.flags = fmt_flag | (knob(kKnobPdl, 1) != 0 ? 2 : 0) |
+              (((call_flags & TG_GEMM_STATIC_B) || g_static_weights != 0 || knob(kKnobStaticWeights, 0) != 0) ? 1 : 0);
     choose_smallm_config(N, p.num_kb, st.num_sms, mp, &p.tile_rows, &p.splits, &p.kb_per_split);
     if (use_ws && !ws_ok) {
       p.splits = 1;
@@ -444,7 +503,7 @@ static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, cons
 
   // Large problems: CTA-pair kernel (256 x 256 tiles, half the L2 traffic per SM).
   if (pair_kernel) {
-    if (env_int("TILEGYM_B200_PDL", 1) != 0) p.flags |= 2;  // programmatic dependent launch
+    if (knob(kKnobPdl, 1) != 0) p.flags |= 2;  // programmatic dependent launch
     p.tiles_m = static_cast<int32_t>((M + 255) / 256);
     p.tiles_n = static_cast<int32_t>((N + 255) / 256);
     p.splits = 1;
@@ -453,20 +512,20 @@ static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, cons
     int group_m = static_cast<int>((24ll << 20) / (256ll * K));
     if (group_m < 2) group_m = 2;
     if (group_m > p.tiles_m) group_m = p.tiles_m;
-    group_m = env_int("TILEGYM_B200_GROUP_M", group_m);
+    group_m = knob(kKnobGroupM, group_m);
     if (group_m < 1) group_m = 1;
     if ((rc = make_map(&tmA, A->ptr, M, K, A->strides[0], 128)) != TG_OK) return rc;
     if ((rc = make_map(&tmB, B->ptr, N, K, B->strides[0], 128)) != TG_OK) return rc;
     // tiles of a partly filled last wave are cut into column slices (TILEGYM_B200_TAIL_DIV overrides: 1, 2, 4)
     int tail_div = pertensor_2cta_tail_div(p.tiles_m * p.tiles_n, st.num_sms);
-    tail_div = env_int("TILEGYM_B200_TAIL_DIV", tail_div);
+    tail_div = knob(kKnobTailDiv, tail_div);
     if (tail_div != 2 && tail_div != 4) tail_div = 1;
     if (swiglu && tail_div == 4) tail_div = 2;  // a SwiGLU output box needs 128 accumulator columns
     CUtensorMap tmBt;
     if ((rc = make_map(&tmBt, B->ptr, N, K, B->strides[0], 128 / tail_div)) != TG_OK) return rc;
     CUtensorMap out_maps[8];
     int num_out = 0;
-    if (tma_out_ok && (num_peers > 0 || swiglu || env_int("TILEGYM_B200_TMA_STORE", 1) != 0)) {
+    if (tma_out_ok && (num_peers > 0 || swiglu || knob(kKnobTmaStore, 1) != 0)) {
       if ((rc = make_out_map(&out_maps[num_out++], C->ptr, M, N_out, C->strides[0] * 2, C->dtype)) != TG_OK) return rc;
       for (int i = 0; i < num_peers; ++i)
         if ((rc = make_out_map(&out_maps[num_out++], peer_ptrs[i], M, N, C->strides[0] * 2, C->dtype)) != TG_OK) return rc;
@@ -477,8 +536,8 @@ static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, cons
   }
 
   // programmatic dependent launch: this kernel's set-up overlaps the tail of the previous kernel on the stream
-  if (env_int("TILEGYM_B200_PDL", 1) != 0) p.flags |= 2;
-  const int forced_bn = env_int("TILEGYM_B200_BN", 0);
+  if (knob(kKnobPdl, 1) != 0) p.flags |= 2;
+  const int forced_bn = knob(kKnobBn, 0);
   if (forced_bn != 0 && forced_bn != 256 && forced_bn != 128 && forced_bn != 64)
     return fail(TG_ERR_ARGS, "TILEGYM_B200_BN must be 64, 128 or 256");
   int bn = 128, suggested = 1;
@@ -506,9 +565,10 @@ static int32_t pertensor_impl(const TgTensorDesc* C, const TgTensorDesc* A, cons
 
 int32_t tg_fp8_gemm_pertensor(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B, uint64_t scale_a,
                               uint64_t scale_b, float alpha, const TgTensorDesc* bias, float beta, uint64_t workspace,
-                              uint64_t workspace_bytes, int32_t device_id, uint64_t stream) {
+                              uint64_t workspace_bytes, uint32_t flags, int32_t device_id, uint64_t stream) {
+  if (flags & ~TG_GEMM_STATIC_B) return fail(TG_ERR_ARGS, "unknown flag bits 0x%x", flags & ~TG_GEMM_STATIC_B);
   return pertensor_impl(C, A, B, scale_a, scale_b, alpha, bias, beta, workspace, workspace_bytes, nullptr, 0,
-                        device_id, stream);
+                        device_id, stream, false, flags);
 }
 
 int32_t tg_fp8_gemm_pertensor_allgather(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
@@ -547,11 +607,7 @@ int32_t tg_gemm_dense16(const TgTensorDesc* C, const TgTensorDesc* A, const TgTe
     return fail(TG_ERR_ALIGN, "A and B need 16-byte aligned bases and row pitches (K %% 8 == 0) for TMA");
   if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) return fail(TG_ERR_ARGS, "problem is too large");
   if ((rc = check_output(C, M, N)) != TG_OK) return rc;
-  if (bias != nullptr) {
-    if (bias->dtype != TG_F32 && bias->dtype != TG_BF16 && bias->dtype != TG_F16) return fail(TG_ERR_DTYPE, "bias must be f32, f16 or bf16");
-    if (bias->ndim != 1 || bias->shape[0] != N || bias->strides[0] != 1) return fail(TG_ERR_ARGS, "bias must be a contiguous vector of N elements");
-    if (bias->ptr == 0 && N > 0) return fail(TG_ERR_NULL, "bias data pointer is null");
-  }
+  if ((rc = check_bias(bias, 0, N)) != TG_OK) return rc;
   if (M == 0 || N == 0) return TG_OK;
 
   DeviceGuard guard(device_id);
@@ -565,6 +621,7 @@ int32_t tg_gemm_dense16(const TgTensorDesc* C, const TgTensorDesc* A, const TgTe
 
   GemmParams p;
   memset(&p, 0, sizeof(p));
+  p.wait_limit_us = g_wait_limit_us;
   p.M = static_cast<int32_t>(M);
   p.N = static_cast<int32_t>(N);
   p.K = static_cast<int32_t>(K);
@@ -581,7 +638,7 @@ int32_t tg_gemm_dense16(const TgTensorDesc* C, const TgTensorDesc* A, const TgTe
   p.splits = 1;
   p.kb_per_split = p.num_kb;
   p.status = st.status;
-  p.flags = ((A->dtype == TG_BF16) ? 8 : 16) | (env_int("TILEGYM_B200_PDL", 1) != 0 ? 2 : 0);
+  p.flags = ((A->dtype == TG_BF16) ? 8 : 16) | (knob(kKnobPdl, 1) != 0 ? 2 : 0);
 
   auto map16 = [&](CUtensorMap* map, const TgTensorDesc* t, int64_t rows, int box_rows) -> int32_t {
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
@@ -614,7 +671,8 @@ int32_t tg_gemm_dense16(const TgTensorDesc* C, const TgTensorDesc* A, const TgTe
 
 int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
                                         const TgTensorDesc* As, const TgTensorDesc* Bs, uint64_t m_indptr,
-                                        int32_t block_n, int32_t block_k, int32_t device_id, uint64_t stream) {
+                                        int32_t block_n, int32_t block_k, const TgTensorDesc* bias, float beta,
+                                        int32_t device_id, uint64_t stream) {
   int32_t rc;
   if ((rc = check_operand(A, "A")) != TG_OK) return rc;
   if (B == nullptr || As == nullptr || Bs == nullptr) return fail(TG_ERR_NULL, "a descriptor is null");
@@ -641,6 +699,7 @@ int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDes
   if ((As->ptr & 3u) || (Bs->ptr & 3u)) return fail(TG_ERR_ALIGN, "scale pointers must be 4-byte aligned");
   if (m_indptr == 0) return fail(TG_ERR_NULL, "m_indptr is null");
   if (m_indptr & 3u) return fail(TG_ERR_ALIGN, "m_indptr must be 4-byte aligned");
+  if ((rc = check_bias(bias, G, N)) != TG_OK) return rc;
   if (M == 0) return TG_OK;
 
   DeviceGuard guard(device_id);
@@ -654,6 +713,7 @@ int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDes
 
   GemmParams p;
   memset(&p, 0, sizeof(p));
+  p.wait_limit_us = g_wait_limit_us;
   p.M = static_cast<int32_t>(M);
   p.N = static_cast<int32_t>(N);
   p.K = static_cast<int32_t>(K);
@@ -663,6 +723,9 @@ int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDes
   p.ldc = C->strides[0];
   p.out_dtype = C->dtype;
   p.alpha = 1.0f;
+  p.beta = beta;
+  p.bias = bias ? reinterpret_cast<const void*>(bias->ptr) : nullptr;
+  p.bias_dtype = bias ? bias->dtype : TG_F32;
   p.As = reinterpret_cast<const float*>(As->ptr);
   p.Bs = reinterpret_cast<const float*>(Bs->ptr);
   p.ldas = As->strides[0];
@@ -670,7 +733,7 @@ int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDes
   p.splits = 1;
   p.kb_per_split = p.num_kb;
   p.status = st.status;
-  if (env_int("TILEGYM_B200_PDL", 1) != 0) p.flags |= 2;  // programmatic dependent launch
+  if (knob(kKnobPdl, 1) != 0) p.flags |= 2;  // programmatic dependent launch
   p.m_indptr = reinterpret_cast<const int32_t*>(m_indptr);
   p.num_groups = static_cast<int32_t>(G);
   // every group adds at most one partly filled 128-row tile to the ceil(M / 128) a dense problem would have
@@ -680,8 +743,8 @@ int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDes
   CUtensorMap tmA, tmB, tmC;
   if ((rc = make_map(&tmA, A->ptr, M, K, A->strides[0], 128)) != TG_OK) return rc;
   if ((rc = make_map(&tmB, B->ptr, G * N, K, K, 256)) != TG_OK) return rc;  // B viewed as [G * N, K]
-  const bool tma_out = (C->dtype == TG_BF16 || C->dtype == TG_F16) && (C->ptr & 15u) == 0 &&
-                       ((C->strides[0] * 2) & 15) == 0 && env_int("TILEGYM_B200_TMA_STORE", 1) != 0;
+  const bool tma_out = (C->dtype == TG_BF16 || C->dtype == TG_F16) && beta == 0.0f && (C->ptr & 15u) == 0 &&
+                       ((C->strides[0] * 2) & 15) == 0 && knob(kKnobTmaStore, 1) != 0;
   if (tma_out && (rc = make_out_map(&tmC, C->ptr, M, N, C->strides[0] * 2, C->dtype)) != TG_OK) return rc;
   cudaError_t e = launch_gemm_blockscaled_grouped(tmA, tmB, tma_out ? &tmC : nullptr, p, st.num_sms, cs);
   if (e != cudaSuccess) return fail(TG_ERR_LAUNCH, "grouped block-scaled GEMM launch failed: %s", cudaGetErrorString(e));
@@ -690,7 +753,8 @@ int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDes
 
 int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
                                 const TgTensorDesc* As, const TgTensorDesc* Bs, int32_t block_n, int32_t block_k,
-                                uint64_t workspace, uint64_t workspace_bytes, int32_t device_id, uint64_t stream) {
+                                const TgTensorDesc* bias, float beta, uint64_t workspace, uint64_t workspace_bytes,
+                                int32_t device_id, uint64_t stream) {
   int32_t rc;
   if ((rc = check_operand(A, "A")) != TG_OK) return rc;
   if ((rc = check_operand(B, "B")) != TG_OK) return rc;
@@ -708,6 +772,7 @@ int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, co
     return fail(TG_ERR_ARGS, "Bs must be [ceil(N/128), ceil(K/128)] = [%lld, %lld] with contiguous rows", (long long)NB, (long long)KB);
   if ((M > 0 && As->ptr == 0) || (N > 0 && Bs->ptr == 0)) return fail(TG_ERR_NULL, "scale data pointer is null");
   if ((As->ptr & 3u) || (Bs->ptr & 3u)) return fail(TG_ERR_ALIGN, "scale pointers must be 4-byte aligned");
+  if ((rc = check_bias(bias, 0, N)) != TG_OK) return rc;
   if (M == 0 || N == 0) return TG_OK;
 
   DeviceGuard guard(device_id);
@@ -721,6 +786,7 @@ int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, co
 
   GemmParams p;
   memset(&p, 0, sizeof(p));
+  p.wait_limit_us = g_wait_limit_us;
   p.M = static_cast<int32_t>(M);
   p.N = static_cast<int32_t>(N);
   p.K = static_cast<int32_t>(K);
@@ -731,13 +797,15 @@ int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, co
   p.ldc = C->strides[0];
   p.out_dtype = C->dtype;
   p.alpha = 1.0f;
-  p.beta = 0.0f;
+  p.beta = beta;
+  p.bias = bias ? reinterpret_cast<const void*>(bias->ptr) : nullptr;
+  p.bias_dtype = bias ? bias->dtype : TG_F32;
   p.As = reinterpret_cast<const float*>(As->ptr);
   p.Bs = reinterpret_cast<const float*>(Bs->ptr);
   p.ldas = As->strides[0];
   p.ldbs = Bs->strides[0];
   p.status = st.status;
-  if (env_int("TILEGYM_B200_PDL", 1) != 0) p.flags |= 2;  // programmatic dependent launch
+  if (knob(kKnobPdl, 1) != 0) p.flags |= 2;  // programmatic dependent launch
   p.ws_counters = reinterpret_cast<uint32_t*>(workspace);
   p.ws_partial = reinterpret_cast<float*>(workspace + kWsCounterBytes);
   const bool have_ws = workspace != 0 && workspace_bytes >= kWsCounterBytes + kWsPartialBytes;
@@ -746,8 +814,8 @@ int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, co
   if (have_ws && tiles * 16 <= static_cast<int64_t>(kWsCounterBytes / 4)) {
     // a problem that fills half a wave of 128 x 256 tiles goes to the wide kernel, which has no K split
     const bool wide_unsplit = static_cast<int64_t>(p.tiles_m) * ((N + 255) / 256) >=
-                                  env_int("TILEGYM_B200_BS_WIDE_MIN", (st.num_sms + 1) / 2) &&
-                              env_int("TILEGYM_B200_BS_WIDE", 1) != 0;
+                                  knob(kKnobBsWideMin, (st.num_sms + 1) / 2) &&
+                              knob(kKnobBsWide, 1) != 0;
     choose_splits(static_cast<int>(tiles), p.num_kb, st.num_sms, 128ll * 128, st.num_sms, 4, &p.splits, &p.kb_per_split,
                   wide_unsplit ? 1 : suggest_splits_blockscaled(tiles, p.num_kb, st.num_sms, 4));
   } else {
@@ -757,37 +825,18 @@ int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, co
   CUtensorMap tmA, tmB;
   if ((rc = make_map(&tmA, A->ptr, M, K, A->strides[0], 128)) != TG_OK) return rc;
   if ((rc = make_map(&tmB, B->ptr, N, K, B->strides[0], 128)) != TG_OK) return rc;
-  // Experimental, opt-in (TILEGYM_B200_BS_PAIR=1): CTA-pair kernel (256 x 192 tiles, each CTA loads 96 rows
-  // of B).  It halves the L2 traffic per flop but its two-buffer promotion chain currently runs slower than
-  // the 128 x 128 kernel with four TMEM buffers, which stays the default.
-  if (M >= 256 && N >= 256 && env_int("TILEGYM_B200_BS_PAIR", 0) != 0 && getenv("TILEGYM_B200_SPLITS") == nullptr) {
-    if ((rc = make_map(&tmB, B->ptr, N, K, B->strides[0], 96)) != TG_OK) return rc;
-    p.tiles_m = static_cast<int32_t>((M + 255) / 256);
-    p.tiles_n = static_cast<int32_t>((N + 191) / 192);
-    p.splits = 1;
-    p.kb_per_split = p.num_kb;
-    int group_m = static_cast<int>((24ll << 20) / (256ll * K));
-    if (group_m < 2) group_m = 2;
-    if (group_m > p.tiles_m) group_m = p.tiles_m;
-    group_m = env_int("TILEGYM_B200_GROUP_M", group_m);
-    if (group_m < 1) group_m = 1;
-    cudaError_t e2 = launch_gemm_blockscaled_2cta(tmA, tmB, p, group_m, st.num_sms, cs);
-    if (e2 != cudaSuccess)
-      return fail(TG_ERR_LAUNCH, "block-scaled GEMM (CTA pair) launch failed: %s", cudaGetErrorString(e2));
-    return TG_OK;
-  }
   // Problems with at least half a wave of 128 x 256 tiles (and no K split) take the wide-tile kernel (a third
   // less shared-memory traffic per flop than 128 x 128 tiles); TILEGYM_B200_BS_WIDE=0 keeps them on the
   // 128 x 128 kernel.
   const int64_t wide_tiles = static_cast<int64_t>(p.tiles_m) * ((N + 255) / 256);
   // two-byte outputs with 16-byte aligned rows leave through shared memory and bulk tensor stores
   CUtensorMap tmC;
-  const bool tma_out = (C->dtype == TG_BF16 || C->dtype == TG_F16) && (C->ptr & 15u) == 0 &&
-                       ((C->strides[0] * 2) & 15) == 0 && env_int("TILEGYM_B200_TMA_STORE", 1) != 0;
+  const bool tma_out = (C->dtype == TG_BF16 || C->dtype == TG_F16) && beta == 0.0f && (C->ptr & 15u) == 0 &&
+                       ((C->strides[0] * 2) & 15) == 0 && knob(kKnobTmaStore, 1) != 0;
   if (tma_out && (rc = make_out_map(&tmC, C->ptr, M, N, C->strides[0] * 2, C->dtype)) != TG_OK) return rc;
   // (measured: from half a wave of wide tiles on, the wide kernel also streams a small-M problem faster)
-  if (p.splits == 1 && wide_tiles >= env_int("TILEGYM_B200_BS_WIDE_MIN", (st.num_sms + 1) / 2) &&
-      env_int("TILEGYM_B200_BS_WIDE", 1) != 0) {
+  if (p.splits == 1 && wide_tiles >= knob(kKnobBsWideMin, (st.num_sms + 1) / 2) &&
+      knob(kKnobBsWide, 1) != 0) {
     if ((rc = make_map(&tmB, B->ptr, N, K, B->strides[0], 256)) != TG_OK) return rc;
     p.tiles_n = static_cast<int32_t>((N + 255) / 256);
     cudaError_t e3 = launch_gemm_blockscaled_wide(tmA, tmB, tma_out ? &tmC : nullptr, p, st.num_sms, cs);

@@ -1,5 +1,5 @@
 // Block-scaled W8A8 FP8 GEMM for sm_100a (1x128 activation scales, 128x128 weight scales):
-//   C[m,n] = sum_kb As[m,kb] * Bs[n/128,kb] * (A[m, kb*128 .. +128) . B[n, kb*128 .. +128))
+//   C[m,n] = sum_kb As[m,kb] * Bs[n/128,kb] * (A[m, kb*128 .. +128) . B[n, kb*128 .. +128)) + bias[n] + beta*C[m,n]
 // The fp32 scales are arbitrary (amax/448), so they cannot ride inside the MMA
 // (hardware block scaling takes power-of-two scales); instead every 128-deep
 // k-block is accumulated by the tensor core into its own TMEM buffer and
@@ -53,7 +53,7 @@ constexpr int kOutBufBytes = 32 * 128;  // per promotion warp: 32 rows x 64 two-
 constexpr int kOutStageBytes = kEpiWarps * kOutBufBytes;
 constexpr int kSmemBytes = kStages * kStageBytes + kOutStageBytes + kCtrlBytes + 1024;
 static_assert(kSmemBytes <= 227 * 1024, "shared memory per CTA");
-static_assert((2 * kStages + 2 * kAccBufs) * 8 + 8 <= kCtrlBytes, "control block");
+static_assert((2 * kStages + 2 * kAccBufs) * 8 + 12 <= kCtrlBytes, "control block");
 
 __global__ void __launch_bounds__(kThreads, 1)
     tg_fp8_gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(bar_tfull + 8 * i, 1);
       mbar_init(bar_tempty + 8 * i, kEpiWarps);
     }
-    *abort_flag = 0u;
+    init_abort_flag(abort_flag, p.wait_limit_us);
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -260,9 +260,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int row0 = tm * kBM + q * 32;
       if (p.splits == 1) {
         if (tma_out) {
+          add_bias_cols<64>(p, acc, col0, 0);
           stage_and_store64(&tmC, my_stage, lane, acc, p.out_dtype, col0, row0, p.M, p.N);
         } else if (row_ok) {
-          epilogue_store32(p, row, col0, acc, 1.0f, vec_ok);
+          epilogue_store32(p, row, col0, acc, 1.0f, vec_ok);  // adds the bias and beta * C itself
           epilogue_store32(p, row, col0 + 32, acc + 32, 1.0f, vec_ok);
         }
       } else {
@@ -294,6 +295,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           TG_BS_STAMP2(4);
           if (tma_out) {
+            add_bias_cols<64>(p, acc, col0, 0);
             stage_and_store64(&tmC, my_stage, lane, acc, p.out_dtype, col0, row0, p.M, p.N);
           } else if (row_ok) {
             epilogue_store32(p, row, col0, acc, 1.0f, vec_ok);

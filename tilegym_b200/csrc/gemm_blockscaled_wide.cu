@@ -1,5 +1,5 @@
 // Block-scaled W8A8 FP8 GEMM for sm_100a, wide-tile version for problems that fill the GPU (no split-K):
-//   C[m,n] = sum_kb As[m,kb] * Bs[n/128,kb] * (A[m, kb-block] . B[n, kb-block])
+//   C[m,n] = sum_kb As[m,kb] * Bs[n/128,kb] * (A[m, kb-block] . B[n, kb-block]) + bias[n] + beta * C[m,n]
 // A 128 x 128 tile moves 64 KB through shared memory per 128-deep k-block (32 KB written by TMA, 32 KB read
 // by the tensor core) for 256 clocks of math, and the shared-memory pipe (about 110 B/clk/SM) caps the tensor
 // pipe near 50 %.  Here the tile is 128 x 256: 96 KB per 512 clocks of math.  Each k-block is accumulated into
@@ -45,7 +45,7 @@ constexpr int kCtrlBytes = 256;
 constexpr int kOutBufBytes = 32 * 128;  // per promotion warp: 32 rows x 64 two-byte columns, 128-byte swizzle
 constexpr int kOutStageBytes = kEpiWarps * kOutBufBytes;
 constexpr int kSmemBytes = kStages * kStageBytes + kOutStageBytes + kCtrlBytes + 1024;
-static_assert((2 * kStages + 2 * kAccBufs) * 8 + 8 <= kCtrlBytes, "control block");
+static_assert((2 * kStages + 2 * kAccBufs) * 8 + 12 <= kCtrlBytes, "control block");
 static_assert(kSmemBytes <= 227 * 1024, "shared memory per CTA");
 
 // 384 threads x 168 registers fill the register file; 128 threads give up 128 each, 256 threads take 64 each.
@@ -191,7 +191,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(bar_tfull + 8 * i, 1);
       mbar_init(bar_tempty + 8 * i, kEpiWarps);
     }
-    *abort_flag = 0u;
+    init_abort_flag(abort_flag, p.wait_limit_us);
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -369,6 +369,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (!ok) break;
       const int row0 = tile.row0 + q * 32;
+      // bias row of a [groups, N] bias: the tile's weight rows start at b_row0 = group * N + col0 in the [G * N, K] view
+      const int64_t bias_off = kGrouped ? static_cast<int64_t>(tile.b_row0 - tile.col0) : 0;
       // a bulk store clips at the ends of C only: in a grouped problem a 32-row slice that runs past the end
       // of its group would overwrite the next group's rows, so such slices take the row-masked stores below
       if (tma_out && (!kGrouped || row0 + 32 <= tile.row_end)) {
@@ -376,6 +378,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         // staging buffer and leave as one bulk tensor store, which clips rows >= M and columns >= N
         uint8_t* my_stage = out_stage + e * kOutBufBytes;
         uint8_t* dst_row = my_stage + lane * 128;
+        add_bias_cols<128>(p, reinterpret_cast<float*>(acc2), col0, bias_off);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           uint4 o[8];
@@ -412,7 +415,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             acc[2 * j] = acc2[c * 16 + j].x;
             acc[2 * j + 1] = acc2[c * 16 + j].y;
           }
-          epilogue_store32(p, row, col0 + c * 32, acc, 1.0f, c_rows_aligned(p));
+          epilogue_store32(p, row, col0 + c * 32, acc, 1.0f, c_rows_aligned(p), bias_off);
         }
       }
     }

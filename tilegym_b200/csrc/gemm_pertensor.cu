@@ -25,7 +25,7 @@ struct PtCfg {
   static constexpr int kCtrlBytes = 256;
   static constexpr int kSmemBytes = kStages * kStageBytes + kCtrlBytes + 1024;
   static_assert(kTmemCols >= 32 && kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns");
-  static_assert((2 * kStages + 4) * 8 + 8 <= kCtrlBytes, "control block");
+  static_assert((2 * kStages + 4) * 8 + 12 <= kCtrlBytes, "control block");
 };
 
 template <int BN>
@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(bar_tfull + 8 * i, 1);
       mbar_init(bar_tempty + 8 * i, 4);
     }
-    *abort_flag = 0u;
+    init_abort_flag(abort_flag, p.wait_limit_us);
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ---------------------------------------------------------- MMA issuer
     {
       const bool elected = elect_one();  // warp-uniform loops, one lane issues the tensor-core work
-      constexpr uint32_t idesc = make_idesc_e4m3_f32(kBM, BN);
+      const uint32_t idesc = make_idesc_e4m3_f32(kBM, BN) | ((p.flags & 32) ? kIdescFormat1 : 0u);  // e4m3 / e5m2
       int s = 0;
       uint32_t ph = 0;
       int buf = 0;

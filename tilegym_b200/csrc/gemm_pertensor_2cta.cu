@@ -34,7 +34,7 @@ constexpr int kOutBufBytes = 32 * 128;
 constexpr int kOutStageBytes = 4 * 2 * kOutBufBytes;  // 32 KB
 constexpr int kSmemBytes = kStages * kStageBytes + kOutStageBytes + kCtrlBytes + 1024;
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
-static_assert((2 * kStages + 4) * 8 + 8 <= kCtrlBytes, "control block");
+static_assert((2 * kStages + 4) * 8 + 12 <= kCtrlBytes, "control block");
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -184,7 +184,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       mbar_init(bar_tfull + 8 * i, 1);   // one commit by the leader's MMA thread
       mbar_init(bar_tempty + 8 * i, 8);  // four epilogue warps of each CTA
     }
-    *abort_flag = 0u;
+    init_abort_flag(abort_flag, p.wait_limit_us);
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -261,8 +261,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       bool ok = true;
       for (int u = pair_id; u < num_units && ok; u += num_pairs) {
         const int bn = (u < plan.full_tiles) ? kBN : kBN / plan.tail_div;
-        // e4m3: A / B format fields 0; 16-bit operands: format 0 = f16, 1 = bf16 in bits [7,10) and [10,13)
-        const uint32_t fmt16 = (kDense16 && (p.flags & 8)) ? ((1u << 7) | (1u << 10)) : 0u;
+        // A / B format fields in bits [7,10) and [10,13): 8-bit operands 0 = e4m3, 1 = e5m2 (flags bit 5);
+        // 16-bit operands 0 = f16, 1 = bf16 (flags bit 3)
+        const uint32_t fmt16 = (p.flags & (kDense16 ? 8 : 32)) ? kIdescFormat1 : 0u;
         constexpr bool dense16 = kDense16;
         const uint32_t idesc = make_idesc_e4m3_f32(256, bn) | fmt16;
         if (!__all_sync(0xffffffffu, mbar_wait(bar_tempty + 8 * buf, aph ^ 1u, abort_flag))) {

@@ -50,7 +50,7 @@ struct SmCfg {
   static constexpr int kInboxBytes = kInboxRows * kBM * 4;
   static constexpr int kCtrlBytes = 128;
   static constexpr int kSmemBytes = kStages * kStageBytes + kInboxBytes + kCtrlBytes + 1024;
-  static_assert((2 * kStages + 1) * 8 + 8 <= kCtrlBytes, "control block");
+  static_assert((2 * kStages + 1) * 8 + 12 <= kCtrlBytes, "control block");
   static_assert(2 * kSmemBytes <= 227 * 1024, "two CTAs per SM");
 };
 
@@ -225,7 +225,7 @@ __global__ void __launch_bounds__(kThreads, 2)
       mbar_init(bar_empty + 8 * i, 1);
     }
     mbar_init(bar_tfull, 1);
-    *abort_flag = 0u;
+    init_abort_flag(abort_flag, p.wait_limit_us);
     fence_mbar_init();
     // The ring is empty and only this thread touches the full barriers until the barrier below:
     // start the weight stream right away, TMEM allocation and the other warps catch up meanwhile.
@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(kThreads, 2)
   } else if (warp == 1) {
     {
       const bool elected = elect_one();  // warp-uniform loops, one lane issues the tensor-core work
-      constexpr uint32_t idesc = make_idesc_e4m3_f32(kBM, MP);
+      const uint32_t idesc = make_idesc_e4m3_f32(kBM, MP) | ((p.flags & 32) ? kIdescFormat1 : 0u);  // e4m3 / e5m2
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;

@@ -33,7 +33,7 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   tn = r / gsize;
 }
 
-__device__ __forceinline__ float load_bias(const void* bias, int dtype, int col) {
+__device__ __forceinline__ float load_bias(const void* bias, int dtype, int64_t col) {
   if (dtype == TG_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[col]);
   if (dtype == TG_F16) return __half2float(reinterpret_cast<const __half*>(bias)[col]);
   return reinterpret_cast<const float*>(bias)[col];
@@ -141,10 +141,34 @@ __device__ __forceinline__ bool c_rows_aligned(const GemmParams& p) {
   return ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0) && (((p.ldc * esz) & 15) == 0);
 }
 
+// acc[j] += bias[bias_off + col0 + j] for the kCols columns col0 .. of one output row (columns >= N skipped).
+// Every lane of a warp reads the same addresses, so the loads are broadcasts.
+template <int kCols>
+__device__ __forceinline__ void add_bias_cols(const GemmParams& p, float* acc, int col0, int64_t bias_off) {
+  if (p.bias == nullptr) return;
+  if (p.bias_dtype == TG_F32) {
+    const float* b = reinterpret_cast<const float*>(p.bias) + bias_off + col0;
+#pragma unroll
+    for (int j = 0; j < kCols; ++j)
+      if (col0 + j < p.N) acc[j] += __ldg(b + j);
+  } else if (p.bias_dtype == TG_BF16) {
+    const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(p.bias) + bias_off + col0;
+#pragma unroll
+    for (int j = 0; j < kCols; ++j)
+      if (col0 + j < p.N) acc[j] += __bfloat162float(b[j]);
+  } else {
+    const __half* b = reinterpret_cast<const __half*>(p.bias) + bias_off + col0;
+#pragma unroll
+    for (int j = 0; j < kCols; ++j)
+      if (col0 + j < p.N) acc[j] += __half2float(b[j]);
+  }
+}
+
 // Final per-tensor epilogue of 32 accumulator columns of one row:
-// out = acc * scale + bias[col] (+ beta * C_old).
+// out = acc * scale + bias[bias_off + col] (+ beta * C_old).  bias_off is the element offset of the row of a
+// [groups, N] bias that applies (0 for a plain [N] bias).
 __device__ __forceinline__ void epilogue_store32(const GemmParams& p, int64_t row, int col0, const float* acc,
-                                                 float scale, bool vec_ok) {
+                                                 float scale, bool vec_ok, int64_t bias_off = 0) {
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
     float v[8];
@@ -154,7 +178,7 @@ __device__ __forceinline__ void epilogue_store32(const GemmParams& p, int64_t ro
     if (p.bias != nullptr) {
 #pragma unroll
       for (int j = 0; j < 8; ++j)
-        if (col + j < p.N) v[j] += load_bias(p.bias, p.bias_dtype, col + j);
+        if (col + j < p.N) v[j] += load_bias(p.bias, p.bias_dtype, bias_off + col + j);
     }
     store8(p, row, col, v, vec_ok);
   }

@@ -42,9 +42,12 @@ struct GemmParams {
   int32_t num_groups;
   int32_t mtile_bound;  // ceil(M / 128) + num_groups >= the number of 128-row tiles of all groups
   // diagnostics
-  int32_t* status;  // device status word
+  int32_t* status;         // device status word
+  uint32_t wait_limit_us;  // bound of every device-side wait in microseconds (0 = the 2 s default)
   // bit 0 (small-M kernel): the weight operand is not written by the kernel that precedes this one on the
-  // stream, so its TMA loads may be issued before the programmatic-dependent-launch wait
+  // stream, so its TMA loads may be issued before the programmatic-dependent-launch wait;
+  // bit 1: launched with programmatic stream serialization; bit 2: SwiGLU epilogue; bits 3 / 4: bf16 / f16
+  // operands (dense kernel); bit 5: e5m2 instead of e4m3 operands (per-tensor kernels)
   int32_t flags;
 };
 
@@ -73,9 +76,6 @@ cudaError_t launch_gemm_blockscaled_wide(const CUtensorMap& tmA, const CUtensorM
 // tmB maps B [G, N, K] as [G * N, K] with 256-row boxes.
 cudaError_t launch_gemm_blockscaled_grouped(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap* tmC,
                                             const GemmParams& p, int num_sms, cudaStream_t stream);
-// CTA-pair block-scaled kernel: 256 x 192 tiles, tmA boxes 128 rows and tmB 96, p.tiles_n counts 192-wide tiles, no split-K.
-cudaError_t launch_gemm_blockscaled_2cta(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
-                                         int group_m, int num_sms, cudaStream_t stream);
 // Swap-AB split-K kernel for M <= 64: tmW boxes 128 weight rows, tmX boxes `mp` activation rows.
 cudaError_t launch_gemm_smallm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int mp,
                                cudaStream_t stream);
@@ -91,6 +91,7 @@ int32_t api_check_operand(const TgTensorDesc* t, const char* name);
 int32_t api_check_output(const TgTensorDesc* C, int64_t M, int64_t N);
 int32_t api_make_map(CUtensorMap* map, uint64_t ptr, int64_t rows, int64_t K, int64_t pitch, int box_rows);
 int32_t api_init_device(int dev, int* num_sms, int32_t** status);  // call with `dev` current
+uint32_t api_wait_limit_us();  // tg_set_wait_limit_us() value (0 = default), for GemmParams::wait_limit_us
 
 cudaError_t launch_act_quant(void* y, float* s, const void* x, int x_dtype, int64_t n_blocks, cudaStream_t stream);
 cudaError_t launch_weight_dequant(void* y, int y_dtype, const uint8_t* x, const float* s, int64_t M, int64_t N,

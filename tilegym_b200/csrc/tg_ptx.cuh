@@ -81,11 +81,18 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 
 // Every wait in these kernels is bounded.  A wait that has not completed
-// after kWaitLimitNs raises the CTA-wide abort flag and returns false; the
+// after the limit raises the CTA-wide abort flag and returns false; the
 // caller then leaves its loops, so that the CTA reaches its teardown, frees
 // its TMEM and returns.  The flag is also polled so that one expired wait
 // releases the other roles quickly.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+// The flag is a word of shared memory; the word after it holds the limit in microseconds (the host passes
+// it in GemmParams::wait_limit_us: 2 s by default, tg_set_wait_limit_us() changes it).
+constexpr uint32_t kDefaultWaitLimitUs = 2000000u;  // 2 s
+
+__device__ __forceinline__ void init_abort_flag(volatile uint32_t* abort_flag, uint32_t limit_us) {
+  abort_flag[0] = 0u;
+  abort_flag[1] = limit_us != 0u ? limit_us : kDefaultWaitLimitUs;
+}
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -94,12 +101,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 63u) == 0u) {
-      if (*abort_flag) return false;
+      if (abort_flag[0]) return false;
       uint64_t now = globaltimer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitLimitNs) {
-        *abort_flag = 1u;
+      } else if (now - t0 > static_cast<uint64_t>(abort_flag[1]) * 1000ull) {
+        abort_flag[0] = 1u;
         return false;
       }
     }
@@ -241,5 +248,7 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
 __host__ __device__ constexpr uint32_t make_idesc_e4m3_f32(int m, int n) {
   return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
+// OR-ed into the descriptor above: A and B format 1 = e5m2 (kind::f8f6f4), or = bf16 (kind::f16).
+constexpr uint32_t kIdescFormat1 = (1u << 7) | (1u << 10);
 
 }  // namespace tg

@@ -73,12 +73,11 @@ class FP8Linear(nn.Module):
         out_dtype = x.dtype if x.dtype in (torch.bfloat16, torch.float16, torch.float32) else self.out_dtype
         if self.mode == "per_tensor":
             xq, sx = ops.quant_per_tensor(x)
-            return ops.fp8_scaled_mm(xq, self.weight_fp8, sx, self.weight_scale, self.bias, out_dtype)
+            # the weight is a constant of the layer: decode-sized calls may stream it before the quantiser ends
+            return ops.fp8_scaled_mm(xq, self.weight_fp8, sx, self.weight_scale, self.bias, out_dtype,
+                                     static_weights=True)
         xq, sx = ops.act_quant(x, 128)
-        y = ops.w8a8_block_fp8_matmul(xq, self.weight_fp8, sx, self.weight_scale, [128, 128], out_dtype)
-        if self.bias is not None:
-            y = y + self.bias.to(y.dtype)
-        return y
+        return ops.fp8_block_scaled_mm(xq, self.weight_fp8, sx, self.weight_scale, self.bias, out_dtype)
 
     def extra_repr(self) -> str:
         return f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, mode={self.mode}"

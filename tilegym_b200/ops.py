@@ -19,11 +19,14 @@ from . import _lib
 _OUT_DTYPES = (torch.float32, torch.float16, torch.bfloat16)
 _IN_DTYPES = (torch.float32, torch.float16, torch.bfloat16)
 _FP8 = torch.float8_e4m3fn
+_FP8_TYPES = (torch.float8_e4m3fn, torch.float8_e5m2)
+_FP8_MAX = {torch.float8_e4m3fn: 448.0, torch.float8_e5m2: 57344.0}
 
 # One zero-initialised scratch buffer per (device, stream): the split-K paths
 # keep partial sums and arrival counters there and leave the counters zero.
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
 _amax_scratch: Dict[Tuple[int, int], torch.Tensor] = {}
+_MAX_STREAM_WORKSPACES = 8  # 48 MiB each
 
 
 def _need_cuda(*tensors: Optional[torch.Tensor]) -> torch.device:
@@ -66,8 +69,22 @@ def _workspace(dev: torch.device) -> torch.Tensor:
     if ws is None:
         nbytes = nbytes or int(_lib.lib().tg_fp8_gemm_workspace_bytes(0, 0, 0))
         ws = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+        # keep at most _MAX_STREAM_WORKSPACES per-stream buffers: the oldest is dropped (the caching allocator
+        # frees it in stream order, so launches still queued on its stream are safe; a stream that comes back
+        # simply gets a fresh zeroed buffer)
+        live = [k for k in _workspaces if k[1] != -1]
+        if len(live) >= _MAX_STREAM_WORKSPACES:
+            del _workspaces[live[0]]
         _workspaces[key] = ws
     return ws
+
+
+def reset_workspaces() -> None:
+    """Drops every cached scratch buffer (they are re-created, zeroed, on demand).  Call after
+    `_lib.device_status` has reported an expired device-side wait: the launch that gave up may have left
+    split-K arrival counters non-zero in the buffer it used."""
+    _workspaces.clear()
+    _amax_scratch.clear()
 
 
 # ----------------------------------------------------------------------------
@@ -105,18 +122,51 @@ def w8a8_block_fp8_matmul(
     assert math.ceil(K / block_k) == Bs.shape[1]
     if output_dtype not in _OUT_DTYPES:
         raise _lib.TileGymB200Error(-6, f"output_dtype {output_dtype} is not one of f32, f16, bf16")
+    if (block_n, block_k) != (128, 128):
+        raise _lib.TileGymB200Error(-6, f"only block_size [128, 128] is implemented, got [{block_n}, {block_k}]")
+    return fp8_block_scaled_mm(A, B, As, Bs, None, output_dtype)
 
+
+def fp8_block_scaled_mm(
+    A: torch.Tensor,
+    B: torch.Tensor,
+    As: torch.Tensor,
+    Bs: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    out_dtype: torch.dtype = torch.bfloat16,
+    out: Optional[torch.Tensor] = None,
+    beta: float = 0.0,
+) -> torch.Tensor:
+    """`w8a8_block_fp8_matmul` (1 x 128 activation scales, 128 x 128 weight scales) with the epilogue a Linear
+    needs: C = dequant(A) @ dequant(B).T + bias (+ beta * out), the bias added in fp32 before the one rounding
+    to `out_dtype`.  The reference operator (src/tilegym/suites/unsloth/ops.py:240-265) has no bias; this is
+    the block-scaled twin of `fp8_scaled_mm`.  With `out` the result is written (or, beta != 0, accumulated)
+    in place."""
+    dev = _need_cuda(A, B, As, Bs)
+    N, K = B.shape
     M = A.numel() // K
-    C = A.new_empty(A.shape[:-1] + (N,), dtype=output_dtype)
+    if out is None:
+        assert beta == 0.0, "beta needs an `out` tensor to accumulate into"
+        if out_dtype not in _OUT_DTYPES:
+            raise _lib.TileGymB200Error(-6, f"out_dtype {out_dtype} is not one of f32, f16, bf16")
+        out = A.new_empty(A.shape[:-1] + (N,), dtype=out_dtype)
+    else:
+        assert out.shape == A.shape[:-1] + (N,) and out.is_contiguous()
+    if not A.is_contiguous():
+        A = A.contiguous()
+    if not B.is_contiguous():
+        B = B.contiguous()
+    if bias is not None and not bias.is_contiguous():
+        bias = bias.contiguous()
     ws = _workspace(dev)
-    a2, as2, c2 = A.view(M, K), As.contiguous().view(M, -1), C.view(M, N)
+    a2, as2, c2 = A.view(M, K), As.contiguous().view(M, -1), out.view(M, N)
     bs2 = Bs.contiguous()
     rc = _lib.lib().tg_fp8_gemm_blockscaled(
-        _lib.ref(_lib.desc(c2)), _lib.ref(_lib.desc(a2)), _lib.ref(_lib.desc(B)), _lib.ref(_lib.desc(as2)),
-        _lib.ref(_lib.desc(bs2)), block_n, block_k, ws.data_ptr(), ws.numel(), dev.index, _stream(dev),
+        _lib.desc(c2), _lib.desc(a2), _lib.desc(B), _lib.desc(as2), _lib.desc(bs2), 128, 128, _lib.desc(bias),
+        float(beta), ws.data_ptr(), ws.numel(), dev.index, _stream(dev),
     )
     _lib.check_rc(rc)
-    return C
+    return out
 
 
 def ragged_block_scaled_bmm(
@@ -130,6 +180,9 @@ def ragged_block_scaled_bmm(
     transpose_a: bool = False,
     transpose_b: bool = True,
     out_dtype: Optional[torch.dtype] = None,
+    bias: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+    beta: float = 0.0,
     **kwargs,
 ) -> torch.Tensor:
     """Ragged (grouped) block-scaled FP8 GEMM: rows [m_indptr[q], m_indptr[q+1]) of `a` times weight b[q].T.
@@ -140,7 +193,8 @@ def ragged_block_scaled_bmm(
     (Q+1,) int32 on the device; returns a new (total_m, N) tensor (bf16 unless out_dtype says otherwise).
     Differences: segments need no alignment to 128 rows and may be empty; `max_m` / `max_m_device` are accepted
     and not needed (the kernel reads m_indptr itself, nothing is read back to the host); only 128 x 128 scale
-    blocks and e4m3 inputs are implemented.
+    blocks and e4m3 inputs are implemented.  Additions (keyword only in effect): `bias` (Q, N) adds row q to
+    the rows of group q, `out` / `beta` write into (accumulate onto) a caller's tensor.
     """
     assert transpose_a is False and transpose_b is True, "Only NT layout is supported"
     dev = _need_cuda(a, b, a_scale, b_scale, m_indptr)
@@ -161,10 +215,18 @@ def ragged_block_scaled_bmm(
         out_dtype = torch.bfloat16
     if out_dtype not in _OUT_DTYPES:
         raise _lib.TileGymB200Error(-6, f"out_dtype {out_dtype} is not one of f32, f16, bf16")
-    c = torch.empty((total_m, N), device=dev, dtype=out_dtype)
+    if out is not None:
+        assert out.shape == (total_m, N) and out.is_contiguous()
+        c = out
+    else:
+        assert beta == 0.0, "beta needs an `out` tensor to accumulate into"
+        c = torch.empty((total_m, N), device=dev, dtype=out_dtype)
+    if bias is not None and not bias.is_contiguous():
+        bias = bias.contiguous()
     rc = _lib.lib().tg_fp8_gemm_blockscaled_grouped(
         _lib.ref(_lib.desc(c)), _lib.ref(_lib.desc(a)), _lib.ref(_lib.desc(b)), _lib.ref(_lib.desc(a_scale)),
-        _lib.ref(_lib.desc(b_scale)), m_indptr.data_ptr(), 128, 128, dev.index, _stream(dev),
+        _lib.ref(_lib.desc(b_scale)), m_indptr.data_ptr(), 128, 128, _lib.desc(bias), float(beta), dev.index,
+        _stream(dev),
     )
     _lib.check_rc(rc)
     return c
@@ -303,12 +365,14 @@ def _pertensor(
     bias: Optional[torch.Tensor],
     beta: float,
     dev: torch.device,
+    flags: int = 0,
 ) -> None:
     ws = _workspace(dev)
     rc = _lib.lib().tg_fp8_gemm_pertensor(
         c2 if isinstance(c2, bytes) else _lib.desc(c2), a2 if isinstance(a2, bytes) else _lib.desc(a2), _lib.desc(b2),
         scale_a.data_ptr() if scale_a is not None else 0, scale_b.data_ptr() if scale_b is not None else 0,
-        float(alpha), _lib.ref(_lib.desc(bias)), float(beta), ws.data_ptr(), ws.numel(), dev.index, _stream(dev),
+        float(alpha), _lib.ref(_lib.desc(bias)), float(beta), ws.data_ptr(), ws.numel(), flags, dev.index,
+        _stream(dev),
     )
     _lib.check_rc(rc)
 
@@ -333,6 +397,7 @@ def fp8_scaled_mm(
     bias: Optional[torch.Tensor] = None,
     out_dtype: torch.dtype = torch.bfloat16,
     out: Optional[torch.Tensor] = None,
+    static_weights: bool = False,
 ) -> torch.Tensor:
     """C = (scale_a * A) @ (scale_b * B).T + bias, fp32 accumulation, `out_dtype` result.
 
@@ -340,6 +405,9 @@ def fp8_scaled_mm(
     one-element fp32 tensors kept on the device (no host synchronisation).
     The reference has no per-tensor-scaled GEMM with a bias vector; this is the
     operator its gemm_alpha_beta (alpha = scale_a * scale_b) approximates.
+    `static_weights=True` promises that B is not written by the kernel that runs just before this call on the
+    stream (the parameters of a Linear layer): decode-sized calls (at most 64 rows) then start streaming B
+    while that kernel is still finishing.  FP8Linear passes it.
     """
     dev = _need_cuda(A, B)
     assert A.dtype == _FP8 and B.dtype == _FP8, "A and B must be float8_e4m3fn"
@@ -358,7 +426,8 @@ def fp8_scaled_mm(
         bias = bias.contiguous()
     # contiguous (..., N) / (..., K) tensors are (M, N) / (M, K) matrices: describe them without making views
     _pertensor(_lib.desc2d(out.data_ptr(), M, N, N, out.dtype), _lib.desc2d(A.data_ptr(), M, K, K, A.dtype), B,
-               _scalar_f32(scale_a, dev, "scale_a"), _scalar_f32(scale_b, dev, "scale_b"), 1.0, bias, 0.0, dev)
+               _scalar_f32(scale_a, dev, "scale_a"), _scalar_f32(scale_b, dev, "scale_b"), 1.0, bias, 0.0, dev,
+               1 if static_weights else 0)
     return out
 
 
@@ -455,25 +524,36 @@ def gemm_alpha_beta(
 
     Signature of src/tilegym/suites/flashinfer/ops.py:25-55 and
     src/tilegym/suites/flashinfer/cutile/gemm/gemm_alpha_beta.py:336-381 (the
-    same contiguity asserts).  Only the FP8 path is implemented here: a and b
-    float8_e4m3fn, trans_a=False, trans_b=True (b is [N, K]).  `num_sms` and
-    tuning kwargs (`use_autotune`, `backend`, ...) are accepted and ignored:
-    the kernel always uses every SM.  Unlike the reference kernel, `c` is not
+    same contiguity asserts) for the dtype pairs of its test
+    (tests/suites/flashinfer/test_flashinfer_gemm_alpha_beta.py:44-53): e4m3 (or e5m2) operands with a
+    bf16 / f16 / f32 `c`, and f16 -> f16 / bf16 -> bf16 through the dense tcgen05 kind::f16 path.
+    trans_a=False, trans_b=True (a [M, K], b [N, K]) is the native layout; the other settings are served by
+    one transposed copy of the operand.  `num_sms` and tuning kwargs (`use_autotune`, `backend`, ...) are
+    accepted and ignored: the kernel always uses every SM.  Unlike the reference kernel, `c` is not
     read when beta == 0, so an uninitialised `c` cannot inject NaNs.
     """
     dev = _need_cuda(a, b, c)
-    if a.dtype != _FP8 or b.dtype != _FP8:
-        raise NotImplementedError("tilegym_b200.gemm_alpha_beta implements the float8_e4m3fn path only")
-    if trans_a or not trans_b:
-        raise NotImplementedError("tilegym_b200.gemm_alpha_beta needs trans_a=False, trans_b=True (A [M,K], B [N,K])")
-    M, K = a.shape
-    N, KB = b.shape
+    dense16 = a.dtype in (torch.bfloat16, torch.float16) and b.dtype == a.dtype
+    if not dense16 and (a.dtype not in _FP8_TYPES or b.dtype != a.dtype):
+        raise NotImplementedError(
+            "tilegym_b200.gemm_alpha_beta takes float8_e4m3fn, float8_e5m2, bfloat16 or float16 operands (a and b alike)"
+        )
+    # the kernels read both operands K-major: a as [M, K], b as [N, K]; other layouts cost one transposed copy
+    a2 = a.t().contiguous() if trans_a else a
+    b2 = b if trans_b else b.t().contiguous()
+    M, K = a2.shape
+    N, KB = b2.shape
     assert K == KB, "incompatible dimensions"
     assert c.shape == (M, N), "C must have shape [M, N]"
     assert a.is_contiguous(), "A matrix must be contiguous"
     assert b.is_contiguous(), "B matrix must be contiguous"
     assert c.is_contiguous(), "C matrix must be contiguous"
-    _pertensor(c, a, b, None, None, alpha, None, beta, dev)
+    if dense16:
+        rc = _lib.lib().tg_gemm_dense16(_lib.desc(c), _lib.desc(a2), _lib.desc(b2), float(alpha), None, float(beta),
+                                        dev.index, _stream(dev))
+        _lib.check_rc(rc)
+    else:
+        _pertensor(c, a2, b2, None, None, alpha, None, beta, dev)
     return c
 
 
@@ -488,17 +568,19 @@ def matmul(
 ) -> torch.Tensor:
     """Unscaled FP8 matmul with the reference's signature (src/tilegym/ops/ops.py:715-741).
 
-    e4m3 inputs only.  With trans_b=True, b is [N, K] and is used as is; otherwise
+    e4m3 or e5m2 (a and b alike) and bf16 / f16 inputs.  With trans_b=True, b is [N, K] and is used as is; otherwise
     b is [K, N] and is transposed into the K-major layout the kernel reads (one
     copy).  The result keeps the input dtype like the reference
-    (src/tilegym/ops/cutile/matmul.py:446): fp32 accumulation, clamp to +-448,
-    cast to e4m3.  Pass out_dtype=torch.bfloat16 to skip the narrowing cast.
+    (src/tilegym/ops/cutile/matmul.py:446): fp32 accumulation, clamp to the format's
+    largest finite value (448 / 57344), cast back.  Pass out_dtype=torch.bfloat16 to skip the narrowing cast.
     Tuning kwargs and `backend=` are accepted and ignored.
     """
     dev = _need_cuda(a, b)
     dense16 = a.dtype in (torch.bfloat16, torch.float16) and b.dtype == a.dtype
-    if not dense16 and (a.dtype != _FP8 or b.dtype != _FP8):
-        raise NotImplementedError("tilegym_b200.matmul implements float8_e4m3fn, bfloat16 and float16 inputs")
+    if not dense16 and (a.dtype not in _FP8_TYPES or b.dtype != a.dtype):
+        raise NotImplementedError(
+            "tilegym_b200.matmul implements float8_e4m3fn, float8_e5m2, bfloat16 and float16 inputs (a and b alike)"
+        )
     if trans_a:
         a = a.t()
     if not a.is_contiguous():
@@ -521,8 +603,57 @@ def matmul(
     c = torch.empty((M, N), dtype=torch.float32 if out_dtype is None else out_dtype, device=dev)
     _pertensor(c, a, bt, None, None, 1.0, None, 0.0, dev)
     if out_dtype is None:
-        return c.clamp_(-448.0, 448.0).to(_FP8)
+        hi = _FP8_MAX[a.dtype]
+        return c.clamp_(-hi, hi).to(a.dtype)
     return c
+
+
+def bmm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    transpose_a: Optional[bool] = None,
+    transpose_b: Optional[bool] = None,
+    static_persistent: Optional[bool] = True,
+    **kwargs,
+) -> torch.Tensor:
+    """Batched matmul with the reference's signature (src/tilegym/ops/ops.py:873-896, implementation
+    src/tilegym/ops/cutile/bmm.py:290-330): a (Q, M, K) (or (Q, K, M) with transpose_a), b (Q, K, N) (or
+    (Q, N, K) with transpose_b), result (Q, M, N) in the input dtype.  bf16 / f16 run the dense tcgen05
+    kind::f16 kernel, e4m3 / e5m2 the kind::f8f6f4 one (fp32 accumulation, result clamped and cast back),
+    one launch per batch entry on the current stream.  The kernels read K-major operands with 16-byte row
+    pitches: (Q, N, K) weights are used as they are, any other layout (and a K that is not a multiple of
+    8 / 16 elements) costs one padded / transposed copy.  Tuning kwargs are accepted and ignored."""
+    dev = _need_cuda(a, b)
+    assert a.dim() == 3 and b.dim() == 3, "bmm takes 3-D tensors"
+    dense16 = a.dtype in (torch.bfloat16, torch.float16) and b.dtype == a.dtype
+    if not dense16 and (a.dtype not in _FP8_TYPES or b.dtype != a.dtype):
+        raise NotImplementedError("tilegym_b200.bmm implements float8, bfloat16 and float16 inputs (a and b alike)")
+    am = a.transpose(1, 2) if transpose_a else a      # (Q, M, K)
+    bt = b if transpose_b else b.transpose(1, 2)      # (Q, N, K)
+    Q, M, K = am.shape
+    assert bt.shape[0] == Q and bt.shape[2] == K, "incompatible dimensions"
+    N = bt.shape[1]
+    kq = 8 if dense16 else 16  # elements per 16 bytes
+    if K % kq != 0:
+        pad = kq - K % kq  # zero columns add nothing to the products
+        if dense16:
+            am, bt = torch.nn.functional.pad(am, (0, pad)), torch.nn.functional.pad(bt, (0, pad))
+        else:
+            am = torch.nn.functional.pad(am.view(torch.uint8), (0, pad)).view(a.dtype)
+            bt = torch.nn.functional.pad(bt.view(torch.uint8), (0, pad)).view(a.dtype)
+    am, bt = am.contiguous(), bt.contiguous()
+    out = torch.empty((Q, M, N), dtype=a.dtype if dense16 else torch.float32, device=dev)
+    L, stream = _lib.lib(), _stream(dev)
+    for q in range(Q):
+        if dense16:
+            rc = L.tg_gemm_dense16(_lib.desc(out[q]), _lib.desc(am[q]), _lib.desc(bt[q]), 1.0, None, 0.0, dev.index, stream)
+            _lib.check_rc(rc)
+        else:
+            _pertensor(out[q], am[q], bt[q], None, None, 1.0, None, 0.0, dev)
+    if dense16:
+        return out
+    hi = _FP8_MAX[a.dtype]
+    return out.clamp_(-hi, hi).to(a.dtype)
 
 
 def set_static_weights(on: bool = True) -> bool:
