@@ -13,8 +13,7 @@ pytestmark = pytest.mark.gpu
 import tilegym_b200 as tg  # noqa: E402
 from tilegym_b200 import _lib  # noqa: E402
 
-KNOBS = ("TILEGYM_B200_SPLITS", "TILEGYM_B200_BS_WIDE", "TILEGYM_B200_BS_PAIR", "TILEGYM_B200_BS_SMALLM",
-         "TILEGYM_B200_TMA_STORE")
+KNOBS = ("TILEGYM_B200_SPLITS", "TILEGYM_B200_BS_WIDE", "TILEGYM_B200_BS_SMALLM", "TILEGYM_B200_TMA_STORE")
 
 
 @pytest.fixture(autouse=True)
@@ -31,7 +30,7 @@ def clean_knobs_and_status(dev):
 @pytest.mark.parametrize("bias_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("M,N,K", [(128, 3072, 5120), (4096, 3072, 1536), (300, 520, 1040), (64, 256, 2048)])
 def test_block_scaled_bias_joins_the_fp32_sum_before_the_rounding(dev, M, N, K, bias_dtype):
-    """Every block-scaled kernel (128 x 128 with and without K split, wide tile, CTA pair, small M) adds the
+    """Every block-scaled kernel (128 x 128 with and without K split, wide tile, small M) adds the
     bias in fp32 before the single rounding to bf16: 2 bf16 ulps / 1e-2 relative against the oracle."""
     g = torch.Generator().manual_seed(M + N + K)
     A = (torch.randn(M, K, generator=g) * 0.5).to(torch.float8_e4m3fn)

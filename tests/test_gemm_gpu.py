@@ -20,7 +20,7 @@ import tilegym_b200 as tg  # noqa: E402
 from tilegym_b200 import _lib  # noqa: E402
 
 KNOBS = ("TILEGYM_B200_BN", "TILEGYM_B200_SPLITS", "TILEGYM_B200_FORCE_PATH", "TILEGYM_B200_SMALLM_WS",
-         "TILEGYM_B200_2CTA", "TILEGYM_B200_GROUP_M", "TILEGYM_B200_BS_PAIR", "TILEGYM_B200_BS_WIDE", "TILEGYM_B200_TILE_ROWS", "TILEGYM_B200_TAIL_DIV", "TILEGYM_B200_PDL", "TILEGYM_B200_STATIC_WEIGHTS", "TILEGYM_B200_TMA_STORE")
+         "TILEGYM_B200_2CTA", "TILEGYM_B200_GROUP_M", "TILEGYM_B200_BS_WIDE", "TILEGYM_B200_TILE_ROWS", "TILEGYM_B200_TAIL_DIV", "TILEGYM_B200_PDL", "TILEGYM_B200_STATIC_WEIGHTS", "TILEGYM_B200_TMA_STORE", "TILEGYM_B200_BS_SMALLM")
 
 
 @pytest.fixture(autouse=True)
@@ -318,24 +318,6 @@ def test_block_scaled_reference_test_shapes(dev, shape):
     torch.testing.assert_close(out.cpu(), ref, rtol=1e-4, atol=1e-4)
 
 
-@pytest.mark.parametrize("M,N,K", [(300, 520, 1040), (256, 256, 128), (1000, 1100, 400)])
-def test_block_scaled_cta_pair_kernel_tails_and_agreement(dev, M, N, K):
-    """Ragged M / N / K through the 256 x 256 CTA-pair kernel, against the oracle and the 128 x 128 kernel."""
-    g = torch.Generator().manual_seed(M + N + K)
-    A = (torch.randn(M, K, generator=g) * 0.1).to(torch.float8_e4m3fn)
-    B = (torch.randn(N, K, generator=g) * 0.1).to(torch.float8_e4m3fn)
-    As = torch.rand(M, -(-K // 128), generator=g) + 0.1
-    Bs = torch.rand(-(-N // 128), -(-K // 128), generator=g) + 0.1
-    ref = R.ref_w8a8_block_fp8_matmul(A, B, As, Bs, [128, 128])
-    args = [t.to(dev) for t in (A, B, As, Bs)]
-    _lib.set_knob("TILEGYM_B200_BS_PAIR", "1")  # the CTA-pair kernel is opt-in
-    pair = tg.w8a8_block_fp8_matmul(*args, [128, 128])
-    torch.testing.assert_close(pair.cpu(), ref, rtol=1e-4, atol=1e-4)
-    _lib.set_knob("TILEGYM_B200_BS_PAIR", "0")
-    single = tg.w8a8_block_fp8_matmul(*args, [128, 128])
-    torch.testing.assert_close(single, pair, rtol=1e-5, atol=1e-5)  # the 128 x 128 kernel may split K here
-
-
 @pytest.mark.parametrize("M,N,K,dtype", [(2500, 3900, 400, torch.float32), (4096, 2304, 1152, torch.bfloat16),
                                          (1300, 7200, 2176, torch.float16)])
 def test_block_scaled_wide_tile_kernel_tails_and_agreement(dev, M, N, K, dtype):
@@ -358,6 +340,57 @@ def test_block_scaled_wide_tile_kernel_tails_and_agreement(dev, M, N, K, dtype):
     _lib.set_knob("TILEGYM_B200_BS_WIDE", "0")
     narrow = tg.w8a8_block_fp8_matmul(*args, [128, 128], dtype)
     assert torch.equal(wide, narrow)
+
+
+@pytest.mark.parametrize("splits", [None, "1", "2", "3", "8"])
+@pytest.mark.parametrize("M", [1, 7, 32, 33, 64, 100, 128])
+def test_block_scaled_small_m_kernel_against_oracle_and_tile_kernel(dev, M, splits):
+    """M <= 128 takes the swap-AB kernel (weights on the MMA M axis, K splits reduced inside a cluster): ragged
+    N and K, every split count, against the oracle; without a K split also bit for bit against the 128 x 128
+    tile kernel (same k-block order, same fused multiply-adds)."""
+    N, K = 520, 2064  # 5 weight tiles (the last one 8 rows), 17 k-blocks (the last one 16 deep)
+    g = torch.Generator().manual_seed(M)
+    A = (torch.randn(M, K, generator=g) * 0.5).to(torch.float8_e4m3fn)
+    B = (torch.randn(N, K, generator=g) * 0.1).to(torch.float8_e4m3fn)
+    As = torch.rand(M, -(-K // 128), generator=g) + 0.1
+    Bs = torch.rand(-(-N // 128), -(-K // 128), generator=g) + 0.1
+    ref = R.ref_w8a8_block_fp8_matmul(A, B, As, Bs, [128, 128], torch.bfloat16)
+    args = [t.to(dev) for t in (A, B, As, Bs)]
+    if splits is not None:
+        _lib.set_knob("TILEGYM_B200_SPLITS", splits)
+    out = tg.w8a8_block_fp8_matmul(*args, [128, 128], torch.bfloat16)
+    res = R.check_tolerance(out, ref)
+    assert res["ok"], res
+    if splits == "1":
+        _lib.set_knob("TILEGYM_B200_BS_SMALLM", "0")
+        tile = tg.w8a8_block_fp8_matmul(*args, [128, 128], torch.bfloat16)
+        assert torch.equal(out, tile)
+
+
+@pytest.mark.parametrize("out_dtype,N", [(torch.float32, 384), (torch.float16, 384), (torch.bfloat16, 100), (torch.float32, 130)])
+@pytest.mark.parametrize("M", [5, 128])
+def test_block_scaled_small_m_output_dtypes_and_unaligned_n(dev, M, out_dtype, N):
+    K = 1024
+    g = torch.Generator().manual_seed(M + N)
+    A = (torch.randn(M, K, generator=g) * 0.5).to(torch.float8_e4m3fn)
+    B = (torch.randn(N, K, generator=g) * 0.1).to(torch.float8_e4m3fn)
+    As = torch.rand(M, K // 128, generator=g) + 0.1
+    Bs = torch.rand(-(-N // 128), K // 128, generator=g) + 0.1
+    ref = R.ref_w8a8_block_fp8_matmul(A, B, As, Bs, [128, 128], out_dtype)
+    for splits in ("1", "4"):
+        _lib.set_knob("TILEGYM_B200_SPLITS", splits)
+        out = tg.w8a8_block_fp8_matmul(A.to(dev), B.to(dev), As.to(dev), Bs.to(dev), [128, 128], out_dtype)
+        if out_dtype == torch.float32:
+            torch.testing.assert_close(out.cpu(), ref, rtol=1e-4, atol=1e-4)
+        else:
+            assert R.check_tolerance(out, ref)["ok"]
+
+
+def test_block_scaled_small_m_is_bit_stable_and_back_to_back(dev):
+    a8, b8, As, Bs = (t.to(dev) for t in R.gen_block_scaled_case(128, 3072, 5120, seed=12))
+    first = tg.w8a8_block_fp8_matmul(a8, b8, As, Bs, [128, 128], torch.bfloat16).clone()
+    for _ in range(10):
+        assert torch.equal(first, tg.w8a8_block_fp8_matmul(a8, b8, As, Bs, [128, 128], torch.bfloat16))
 
 
 def test_block_scaled_split_k_and_leading_dims(dev):

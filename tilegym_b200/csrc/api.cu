@@ -93,14 +93,14 @@ int32_t init_device(int dev) {
 // tg_reload_env() is called (tests flip knobs between calls).
 enum Knob : int {
   kKnobSplits, kKnobTileRows, kKnobForcePath, kKnobPairMinTiles, kKnob2Cta, kKnobBn, kKnobSmallmWs, kKnobPdl,
-  kKnobStaticWeights, kKnobGroupM, kKnobTailDiv, kKnobTmaStore, kKnobBsWideMin, kKnobBsWide, kKnobBsPair,
+  kKnobStaticWeights, kKnobGroupM, kKnobTailDiv, kKnobTmaStore, kKnobBsWideMin, kKnobBsWide,
   kKnobBsSmallm, kKnobCount
 };
 const char* const kKnobNames[kKnobCount] = {
     "TILEGYM_B200_SPLITS", "TILEGYM_B200_TILE_ROWS", "TILEGYM_B200_FORCE_PATH", "TILEGYM_B200_PAIR_MIN_TILES",
     "TILEGYM_B200_2CTA", "TILEGYM_B200_BN", "TILEGYM_B200_SMALLM_WS", "TILEGYM_B200_PDL",
     "TILEGYM_B200_STATIC_WEIGHTS", "TILEGYM_B200_GROUP_M", "TILEGYM_B200_TAIL_DIV", "TILEGYM_B200_TMA_STORE",
-    "TILEGYM_B200_BS_WIDE_MIN", "TILEGYM_B200_BS_WIDE", "TILEGYM_B200_BS_PAIR", "TILEGYM_B200_BS_SMALLM"};
+    "TILEGYM_B200_BS_WIDE_MIN", "TILEGYM_B200_BS_WIDE", "TILEGYM_B200_BS_SMALLM"};
 struct KnobTable {
   bool loaded = false;
   bool present[kKnobCount] = {};
@@ -281,6 +281,47 @@ int suggest_splits_blockscaled(int64_t tiles, int num_kb, int num_sms, int min_k
     }
   }
   return best;
+}
+
+// K split of the small-M block-scaled kernel (one CTA per SM, the splits of a 128-row weight tile form a cluster
+// of at most 8 CTAs).  Only split counts whose CTAs are all resident at once are considered (`resident(s)` =
+// clusters of s CTAs the device holds; a second wave would double the time), every CTA gets at least two and at
+// most `max_kb` k-blocks (the staged scale table), and among those the cost model picks: set-up + k-blocks per
+// CTA + the cluster reduction, in k-block times (0.42 us each, measured).  With more than 32 activation rows a
+// CTA that would own more than 16 k-blocks is left to the 128 x 128 tile kernel (measured on N = 5120, K = 12288:
+// 24.3 against 21.1 us at M = 128, 17.2 against 20.0 us at M = 16).  TILEGYM_B200_SPLITS forces a count.
+// Returns false when nothing qualifies: the 128-row tile kernels then take the problem.
+template <typename ResidentFn>
+bool choose_bs_smallm_splits(int64_t rows, int64_t tiles, int num_kb, int max_kb, ResidentFn resident, int* splits,
+                             int* kbps) {
+  int best = 0, best_per = 0;
+  double best_cost = 1e300;
+  const int forced = knob(kKnobSplits, 0);
+  if (forced > 0) {  // taken as asked (rounded to a count in which every split owns a k-block), resident or not
+    if (forced > 8) return false;
+    const int per = (num_kb + forced - 1) / forced;
+    if (per > max_kb) return false;
+    *kbps = per;
+    *splits = (num_kb + per - 1) / per;
+    return true;
+  }
+  for (int s = 1; s <= 8; ++s) {
+    const int per = (num_kb + s - 1) / s;
+    if ((num_kb + per - 1) / per != s) continue;  // not a canonical split count
+    if (per > max_kb || (s > 1 && per < 2)) continue;
+    if (tiles > resident(s)) continue;
+    if (rows > 32 && per > 16) continue;  // long k-ranges with many rows: the tile kernel's workspace reduction wins
+    const double cost = per + (s > 1 ? 3.0 + 0.5 * s : 0.0);
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = s;
+      best_per = per;
+    }
+  }
+  if (best == 0) return false;
+  *splits = best;
+  *kbps = best_per;
+  return true;
 }
 
 // Tile width and K split of the single-CTA per-tensor kernel (65 <= M < 512 in practice), by a cost model in
@@ -811,6 +852,28 @@ int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, co
   const bool have_ws = workspace != 0 && workspace_bytes >= kWsCounterBytes + kWsPartialBytes;
   const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
   if (tiles > 0x3fffffff) return fail(TG_ERR_ARGS, "problem has too many tiles");
+  // Small M (M <= 128, no beta): the swap-AB kernel (weights on the MMA M axis, K splits reduced inside a
+  // cluster); TILEGYM_B200_BS_SMALLM=0 switches it off.
+  if (M <= 128 && beta == 0.0f && knob(kKnobBsSmallm, 1) != 0) {
+    int s = 0, per = 0;
+    const int mp = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
+    const int sms = st.num_sms;
+    if (choose_bs_smallm_splits(M, NB, p.num_kb, blockscaled_smallm_max_kb_per_cta(),
+                                [mp, sms](int sp) { return blockscaled_smallm_resident_clusters(mp, sp, sms); }, &s, &per)) {
+      p.tiles_m = 1;
+      p.tiles_n = static_cast<int32_t>(NB);
+      p.splits = s;
+      p.kb_per_split = per;
+      if (g_static_weights != 0 || knob(kKnobStaticWeights, 0) != 0) p.flags |= 1;
+      CUtensorMap tmW, tmX;
+      if ((rc = make_map(&tmW, B->ptr, N, K, B->strides[0], 128)) != TG_OK) return rc;
+      if ((rc = make_map(&tmX, A->ptr, M, K, A->strides[0], mp)) != TG_OK) return rc;
+      cudaError_t e0 = launch_gemm_blockscaled_smallm(tmW, tmX, p, mp, cs);
+      if (e0 != cudaSuccess)
+        return fail(TG_ERR_LAUNCH, "block-scaled GEMM (small M) launch failed: %s", cudaGetErrorString(e0));
+      return TG_OK;
+    }
+  }
   if (have_ws && tiles * 16 <= static_cast<int64_t>(kWsCounterBytes / 4)) {
     // a problem that fills half a wave of 128 x 256 tiles goes to the wide kernel, which has no K split
     const bool wide_unsplit = static_cast<int64_t>(p.tiles_m) * ((N + 255) / 256) >=

@@ -55,26 +55,6 @@ constexpr int kRegsHeavyGrouped = 232;
 static_assert(128 * (168 - kRegsLight) >= 256 * (kRegsHeavyGrouped - 168) && kRegsHeavyGrouped >= kRegsHeavy,
               "register budget");
 
-__device__ __forceinline__ void fma16x2(float2* acc, const uint32_t (&r)[32], float2 sc2) {
-#pragma unroll
-  for (int j = 0; j < 16; ++j)
-    acc[j] = __ffma2_rn(make_float2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])), sc2, acc[j]);
-}
-
-// Activation scales of one row for k-blocks kb .. kb+3 (0 where out of range or the row is not in the problem).
-__device__ __forceinline__ void load_as4(const float* as_row, int kb, int num_kb, bool in, bool vec, float (&a)[4]) {
-  if (in && vec && kb + 4 <= num_kb) {
-    const float4 v = __ldg(reinterpret_cast<const float4*>(as_row + kb));
-    a[0] = v.x;
-    a[1] = v.y;
-    a[2] = v.z;
-    a[3] = v.w;
-  } else {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) a[i] = (in && kb + i < num_kb) ? __ldg(as_row + kb + i) : 0.f;
-  }
-}
-
 // Where a tile sits.  Plain GEMM: 128-row tile tm, 256-column tile tn.  Grouped GEMM: the 128-row tiles of all
 // groups are numbered consecutively (group g owns ceil(rows_g / 128) of them; a tile never spans two groups),
 // its rows stop at the end of its group, and its weights / weight scales are those of the group.

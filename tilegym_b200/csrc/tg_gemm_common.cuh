@@ -214,6 +214,27 @@ __device__ __forceinline__ void stage_and_store64(const CUtensorMap* tmC, uint8_
   }
 }
 
+// ---- promotion helpers of the block-scaled kernels (acc += scale * partial on CUDA cores)
+__device__ __forceinline__ void fma16x2(float2* acc, const uint32_t (&r)[32], float2 sc2) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j)
+    acc[j] = __ffma2_rn(make_float2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])), sc2, acc[j]);
+}
+
+// Activation scales of one row for k-blocks kb .. kb+3 (0 where out of range or the row is not in the problem).
+__device__ __forceinline__ void load_as4(const float* as_row, int kb, int num_kb, bool in, bool vec, float (&a)[4]) {
+  if (in && vec && kb + 4 <= num_kb) {
+    const float4 v = __ldg(reinterpret_cast<const float4*>(as_row + kb));
+    a[0] = v.x;
+    a[1] = v.y;
+    a[2] = v.z;
+    a[3] = v.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) a[i] = (in && kb + i < num_kb) ? __ldg(as_row + kb + i) : 0.f;
+  }
+}
+
 // Split-K arrival: after a warp has written its partial results and fenced,
 // lane 0 bumps the counter of its (tile, slice); the warp that brings it to
 // `splits` is the last one, resets the counter for the next call and reduces.

@@ -76,6 +76,14 @@ cudaError_t launch_gemm_blockscaled_wide(const CUtensorMap& tmA, const CUtensorM
 // tmB maps B [G, N, K] as [G * N, K] with 256-row boxes.
 cudaError_t launch_gemm_blockscaled_grouped(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap* tmC,
                                             const GemmParams& p, int num_sms, cudaStream_t stream);
+// Swap-AB block-scaled kernel for M <= 128: tmW boxes 128 weight rows, tmX boxes `mp` (32 / 64 / 128) activation
+// rows; p.tiles_n counts 128-row weight tiles, the p.splits (1..8) K splits of a tile form a cluster, and every
+// split owns at most blockscaled_smallm_max_kb_per_cta() k-blocks.  No beta.
+int blockscaled_smallm_max_kb_per_cta();
+// clusters of `splits` CTAs of that kernel the current device holds at once (num_sms for splits == 1)
+int blockscaled_smallm_resident_clusters(int mp, int splits, int num_sms);
+cudaError_t launch_gemm_blockscaled_smallm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int mp,
+                                           cudaStream_t stream);
 // Swap-AB split-K kernel for M <= 64: tmW boxes 128 weight rows, tmX boxes `mp` activation rows.
 cudaError_t launch_gemm_smallm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int mp,
                                cudaStream_t stream);

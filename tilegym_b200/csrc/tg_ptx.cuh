@@ -51,32 +51,34 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 #ifndef TG_WAIT_HINT_NS
 #define TG_WAIT_HINT_NS 100000  // 0 compiles the plain form
 #endif
+// kHint: with a suspend-time hint the hardware may park the waiting thread for up to that long before it returns
+// (it still wakes when the phase completes); parked waiters draw less power than spinning ones, which under the
+// board's power cap is worth 1-2 % of sustained GEMM throughput.  Waits that sit on a latency-critical hand-over
+// (the per-k-block TMEM buffer exchange of the block-scaled kernels) use the plain form, which returns sooner.
+template <bool kHint = true>
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
-#if TG_WAIT_HINT_NS > 0
-  // with a suspend-time hint the hardware may park the waiting thread for up to that long before it returns
-  // (it still wakes as soon as the phase completes); parked waiters draw less power than spinning ones, which
-  // under the board's power cap is worth 1-2 % of sustained GEMM throughput
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(static_cast<uint32_t>(TG_WAIT_HINT_NS))
-      : "memory");
-#else
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-#endif
+  if constexpr (kHint && TG_WAIT_HINT_NS > 0) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(static_cast<uint32_t>(TG_WAIT_HINT_NS))
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+  }
   return ok;
 }
 
@@ -94,12 +96,13 @@ __device__ __forceinline__ void init_abort_flag(volatile uint32_t* abort_flag, u
   abort_flag[1] = limit_us != 0u ? limit_us : kDefaultWaitLimitUs;
 }
 
+template <bool kHint = true>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_try_wait<kHint>(bar, parity)) return true;
   uint64_t t0 = 0;
 #pragma unroll 1
   for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait<kHint>(bar, parity)) return true;
     if ((it & 63u) == 0u) {
       if (abort_flag[0]) return false;
       uint64_t now = globaltimer_ns();
