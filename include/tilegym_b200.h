@@ -138,6 +138,9 @@ TG_API int32_t tg_gemm_dense16(const TgTensorDesc* C, const TgTensorDesc* A, con
  * captured in a CUDA graph whose routing changes between replays); groups may be empty and need no alignment;
  * rows outside every group are left untouched; offsets are clamped to [0, M] on the device.
  * bias: NULL or a contiguous (G, N) f32 / f16 / bf16 matrix, row g added to the rows of group g; beta as above.
+ * row_scale: 0, or a DEVICE pointer to M fp32 factors: row m of the product is multiplied by row_scale[m] in
+ * fp32 before bias, beta * C and the rounding (the routing weight of a mixture-of-experts row,
+ * src/tilegym/ops/tilecpp/moe.cuh:193-200).
  * Replaces tilegym.suites.flashinfer.ops.ragged_block_scaled_bmm for e4m3 inputs in the NT layout
  * (src/tilegym/suites/flashinfer/ops.py:126-158, kernel
  * src/tilegym/suites/flashinfer/cutile/gemm/ragged_block_scaled_bmm.py:497-616).
@@ -145,7 +148,46 @@ TG_API int32_t tg_gemm_dense16(const TgTensorDesc* C, const TgTensorDesc* A, con
 TG_API int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
                                                const TgTensorDesc* As, const TgTensorDesc* Bs, uint64_t m_indptr,
                                                int32_t block_n, int32_t block_k, const TgTensorDesc* bias,
-                                               float beta, int32_t device_id, uint64_t stream);
+                                               float beta, uint64_t row_scale, int32_t device_id, uint64_t stream);
+
+/* ---- Mixture-of-experts layer around the grouped GEMM (reference: fused_experts_impl,
+ * src/tilegym/ops/moe_interface.py:116-322; kernels src/tilegym/ops/tilecpp/moe.cuh:72-563).  The reference pads
+ * each expert's token list to the tile height and gathers rows inside every GEMM tile through sorted_token_ids
+ * (moe_align_block_size, moe_interface.py:30-81); here rows are brought into expert order once, both expert
+ * GEMMs run on contiguous segments through tg_fp8_gemm_blockscaled_grouped, and the way back to token order is
+ * part of the final sum over the top-k experts.  Nothing is read back to the host. ---- */
+
+/* Routing: counting sort of the (token, slot) pairs by expert.  topk_ids: (T, top_k) int32 / int64, contiguous;
+ * topk_weights: same shape, f32 / f16 / bf16, or NULL.  Outputs (device pointers): m_indptr[E + 1] int32 segment
+ * offsets in expert order; sorted_ids[T * top_k] int32, flat pair index t * top_k + slot of every sorted row;
+ * pos[T * top_k] int32, its inverse (-1 for a pair whose expert id is outside [0, E)); w_sorted[T * top_k] f32,
+ * the routing weight of every sorted row (may be 0 when topk_weights is NULL); scratch: E int32.  The order of
+ * the rows inside an expert's segment is not specified (rows are computed independently of their position). */
+TG_API int32_t tg_moe_route(const TgTensorDesc* topk_ids, const TgTensorDesc* topk_weights, int32_t num_experts,
+                            uint64_t m_indptr, uint64_t sorted_ids, uint64_t pos, uint64_t w_sorted, uint64_t scratch,
+                            int32_t device_id, uint64_t stream);
+
+/* Row gather into expert order: A_sorted[r] = A[sorted_ids[r] / top_k], As_sorted likewise, for the
+ * m_indptr[E] routed rows.  A: (T, K) e4m3, As: (T, ceil(K/128)) f32; A_sorted: (R, K), As_sorted: (R, ceil(K/128)),
+ * R <= T * top_k, contiguous.  (The reference gathers per GEMM tile: ct::load_masked through offs_token / TOP_K,
+ * moe.cuh:150-165.) */
+TG_API int32_t tg_moe_permute_rows(const TgTensorDesc* A_sorted, const TgTensorDesc* As_sorted, const TgTensorDesc* A,
+                                   const TgTensorDesc* As, uint64_t sorted_ids, uint64_t m_indptr, int32_t num_experts,
+                                   int32_t topk, int32_t device_id, uint64_t stream);
+
+/* Between the two expert GEMMs: a = silu(X[:, :I]) * X[:, I:] in fp32, rounded to X's 16-bit type (the reference's
+ * intermediate tensor, moe_interface.py:262-267), then quantised to e4m3 for the second GEMM.  mode 0: scale 1 and
+ * a saturating cast, the reference's a2_scale of ones (moe_interface.py:269-279); mode 1: one scale amax / 448 per
+ * 128 elements (1 for an all-zero group), IEEE division.  X: (R, 2 I) bf16 / f16, I % 128 == 0; Y: (R, I) e4m3;
+ * S: (R, I / 128) f32; only the first m_indptr[E] rows are processed. */
+TG_API int32_t tg_moe_silu_mul_quant(const TgTensorDesc* Y, const TgTensorDesc* S, const TgTensorDesc* X, uint64_t m_indptr,
+                                     int32_t num_experts, int32_t mode, int32_t device_id, uint64_t stream);
+
+/* Back to token order: out[t, :] = sum over slot j of C[pos[t * top_k + j], :] (pairs with pos < 0 skipped), summed
+ * in fp32 and rounded once - the reference's torch.sum over the top-k axis (moe_interface.py:309-321) with the
+ * un-permutation folded in.  C: (R, H) bf16 / f16 in expert order, out: (T, H), H % 8 == 0. */
+TG_API int32_t tg_moe_unpermute_sum(const TgTensorDesc* out, const TgTensorDesc* C, uint64_t pos, int32_t topk,
+                                    int32_t device_id, uint64_t stream);
 
 /* Column-parallel GEMM fused with the all-gather of its output (multi-GPU, one
  * process per GPU).  This rank computes its slab C[M, n] = alpha*sa*sb*(A . B_shard^T)

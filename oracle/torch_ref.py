@@ -315,6 +315,54 @@ def ref_matmul(a: torch.Tensor, b: torch.Tensor, trans_b: bool = False) -> torch
     return out.to(a.dtype)
 
 
+def ref_moe_silu_mul_quant(x: torch.Tensor, mode: str = "ones") -> Tuple[torch.Tensor, torch.Tensor]:
+    """The step between the two expert GEMMs of fused_experts_impl (src/tilegym/ops/moe_interface.py:262-279):
+    silu_and_mul of [rows, 2 I] into [rows, I] (fp32 arithmetic, result in x's 16-bit dtype), then the cast to
+    e4m3 with an a2_scale of ones ("ones", the reference; values beyond +-448 saturate here where torch's cast
+    would give NaN) or a 1 x 128 amax / 448 quantisation ("block", ref_act_quant)."""
+    inter = x.shape[-1] // 2
+    act = (torch.nn.functional.silu(x[..., :inter].float()) * x[..., inter:].float()).to(x.dtype)
+    if mode == "block":
+        return ref_act_quant(act, 128)
+    y = act.float().clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
+    return y, torch.ones(*act.shape[:-1], inter // 128, dtype=torch.float32)
+
+
+def ref_fused_experts_fp8(
+    a8: torch.Tensor,
+    a1_scale: torch.Tensor,
+    w1: torch.Tensor,
+    w1_scale: torch.Tensor,
+    w2: torch.Tensor,
+    w2_scale: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    out_dtype: torch.dtype = torch.float16,
+    a2_quant: str = "ones",
+) -> torch.Tensor:
+    """The FP8 W8A8 path of fused_experts_impl (src/tilegym/ops/moe_interface.py:116-322) with the block-scale
+    arithmetic of its kernel (src/tilegym/ops/tilecpp/moe.cuh:175-200): per (token, slot) pair with expert e,
+    fc1 = dequant(a8[t]) . dequant(w1[e])^T in fp32 -> out_dtype; silu_and_mul -> out_dtype -> e4m3 (scale 1);
+    fc2 = dequant . dequant(w2[e])^T times the routing weight in fp32 -> out_dtype; out[t] = sum over the slots
+    (fp32) -> out_dtype.  Pairs are processed expert by expert (row order inside an expert does not matter)."""
+    T, H = a8.shape
+    E = w1.shape[0]
+    topk = topk_ids.shape[1]
+    c3 = torch.zeros(T, topk, w2.shape[1], dtype=out_dtype)
+    flat_ids = topk_ids.reshape(-1)
+    for e in range(E):
+        pairs = torch.nonzero(flat_ids == e).flatten()
+        if pairs.numel() == 0:
+            continue
+        tok = pairs // topk
+        fc1 = ref_w8a8_block_fp8_matmul(a8[tok], w1[e], a1_scale[tok], w1_scale[e], [128, 128], out_dtype)
+        y8, y_s = ref_moe_silu_mul_quant(fc1, a2_quant)
+        a_deq, b_deq = dequant_block_scaled(y8, w2[e], y_s, w2_scale[e], 128, 128)
+        fc2 = (a_deq @ b_deq.T) * topk_weights.reshape(-1)[pairs].float()[:, None]
+        c3.view(T * topk, -1)[pairs] = fc2.to(out_dtype)
+    return c3.float().sum(dim=1).to(out_dtype)
+
+
 def ref_bmm(a: torch.Tensor, b: torch.Tensor, transpose_a: bool = False, transpose_b: bool = False) -> torch.Tensor:
     """Batched matmul, output in the input dtype (tests/ops/test_bmm.py:17-23: transpose, torch.bmm).  Computed
     in fp32 with one cast at the end (torch.bmm on f16 CPU tensors accumulates in fp32 as well); 8-bit inputs

@@ -144,6 +144,45 @@ def main(ref_root: str, only=()) -> None:
             np.savez_compressed(os.path.join(HERE, f"ragged_bmm_q{Q}_m{m}_{N}x{K}.npz"),
                                 a=bits(a), b=bits(b), a_scale=bits(sa), b_scale=bits(sb), m_indptr=ind.numpy(),
                                 c=bits(c))
+    # --- mixture of experts: the operand recipe of the reference test (tests/ops/test_moe.py:112-142: normal(0, 0.5)
+    # tokens, normal(0, 0.1) weights, softmax routing weights, random expert ids) at half the width of its smallest
+    # shape (:70-76) so that the fixture stays small, block-quantised on the CPU; stored are the quantised
+    # operands and (a) the output of the test class's own torch reference (Test_MOE.reference) on the
+    # DEQUANTISED fp32 operands, (b) the two stages through tilegym.ops.moe_interface.fused_moe_torch
+    # (:82-113) on the same dequantised operands -------------------------------------------------------
+    if want("moe"):
+        from tests.ops.test_moe import Test_MOE as MOE
+        from tilegym.ops.moe_interface import fused_moe_torch
+
+        sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+        from oracle import torch_ref as R
+
+        T_, H, I_, E, topk = 16, 256, 128, 4, 2
+        torch.manual_seed(0)
+        x = torch.empty(T_, H).normal_(0, 0.5)
+        w1 = torch.empty(E, 2 * I_, H).normal_(0, 0.1)
+        w2 = torch.empty(E, H, I_).normal_(0, 0.1)
+        ids = torch.randint(0, E, (T_, topk), dtype=torch.long)
+        wts = torch.softmax(torch.randn(T_, topk), dim=-1)
+        a8, a_s = R.ref_act_quant(x, 128)
+        q1 = [R.ref_weight_quant_block(w1[e]) for e in range(E)]
+        q2 = [R.ref_weight_quant_block(w2[e]) for e in range(E)]
+        w1q, w1s = torch.stack([q for q, _ in q1]), torch.stack([s for _, s in q1])
+        w2q, w2s = torch.stack([q for q, _ in q2]), torch.stack([s for _, s in q2])
+        xd = a8.float() * a_s.repeat_interleave(128, dim=1)
+        w1d = torch.stack([R.ref_weight_dequant(w1q[e], w1s[e], 128, torch.float32) for e in range(E)])
+        w2d = torch.stack([R.ref_weight_dequant(w2q[e], w2s[e], 128, torch.float32) for e in range(E)])
+        full = MOE.reference(xd, w1d, w2d, wts, ids)
+        stage1 = fused_moe_torch(xd, w1d, None, wts, ids, False)        # [T, topk, 2 I]
+        mid = torch.nn.functional.silu(stage1[..., :I_]) * stage1[..., I_:]
+        # second stage of the pipeline: every (token, slot) row is its own "token" with one expert (top_k = 1)
+        stage2 = fused_moe_torch(mid.reshape(T_ * topk, I_), w2d, None, wts.reshape(-1, 1), ids.reshape(-1, 1), True)
+        np.savez_compressed(
+            os.path.join(HERE, f"moe_{T_}x{H}x{I_}_e{E}_k{topk}.npz"),
+            a8=bits(a8), a_s=bits(a_s), w1=bits(w1q), w1_s=bits(w1s), w2=bits(w2q), w2_s=bits(w2s),
+            ids=ids.numpy(), wts=bits(wts), full_f32=bits(full), stage1_f32=bits(stage1),
+            stage2_f32=bits(stage2.reshape(T_, topk, H)),
+        )
     print("golden fixtures written to", HERE)
 
 

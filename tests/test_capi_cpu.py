@@ -93,7 +93,7 @@ def test_grouped_blockscaled_argument_checks():
 
     def call(c=C, a=A, b=B, sa=As, sb=Bs, ptr=None, bn=128, bias=None):
         return L.tg_fp8_gemm_blockscaled_grouped(_d(c), _d(a), _d(b), _d(sa), _d(sb),
-                                                 ind.data_ptr() if ptr is None else ptr, bn, 128, _d(bias), 0.0, 0, 0)
+                                                 ind.data_ptr() if ptr is None else ptr, bn, 128, _d(bias), 0.0, 0, 0, 0)
 
     assert call(bias=torch.zeros(128)) == -6  # a grouped bias is [groups, N]
 
@@ -107,6 +107,34 @@ def test_grouped_blockscaled_argument_checks():
     assert call(b=B.view(torch.uint8)) == -2
     assert call(a=torch.zeros(0, 256, dtype=torch.float8_e4m3fn), c=torch.zeros(0, 128, dtype=torch.bfloat16),
                 sa=torch.zeros(0, 2)) == 0  # nothing to do, no device needed
+
+
+def test_moe_argument_checks():
+    L = _lib.lib()
+    ids = torch.zeros(8, 2, dtype=torch.int64)
+    buf = torch.zeros(64, dtype=torch.int32)
+    p = buf.data_ptr()
+    assert L.tg_moe_route(_d(ids.float()), None, 4, p, p, p, p, p, 0, 0) == -2          # ids must be integers
+    assert L.tg_moe_route(_d(ids), _d(torch.zeros(8, 3)), 4, p, p, p, p, p, 0, 0) == -6  # weights shaped like ids
+    assert L.tg_moe_route(_d(ids), None, 0, p, p, p, p, p, 0, 0) == -6
+    assert L.tg_moe_route(_d(ids), None, 4, 0, p, p, p, p, 0, 0) == -5
+    a = torch.zeros(8, 256, dtype=torch.float8_e4m3fn)
+    a_s = torch.zeros(8, 2)
+    out = torch.zeros(16, 256, dtype=torch.float8_e4m3fn)
+    out_s = torch.zeros(16, 2)
+    assert L.tg_moe_permute_rows(_d(out), _d(out_s), _d(a.view(torch.uint8)), _d(a_s), p, p, 4, 2, 0, 0) == -2
+    assert L.tg_moe_permute_rows(_d(out), _d(torch.zeros(16, 3)), _d(a), _d(a_s), p, p, 4, 2, 0, 0) == -6
+    assert L.tg_moe_permute_rows(_d(torch.zeros(24, 256, dtype=torch.float8_e4m3fn)), _d(torch.zeros(24, 2)), _d(a),
+                                 _d(a_s), p, p, 4, 2, 0, 0) == -6                         # more rows than tokens x top_k
+    x = torch.zeros(4, 512, dtype=torch.bfloat16)
+    y = torch.zeros(4, 256, dtype=torch.float8_e4m3fn)
+    assert L.tg_moe_silu_mul_quant(_d(y), _d(torch.zeros(4, 2)), _d(x), p, 4, 2, 0, 0) == -6  # mode
+    assert L.tg_moe_silu_mul_quant(_d(y), _d(torch.zeros(4, 3)), _d(x), p, 4, 0, 0, 0) == -6
+    assert L.tg_moe_silu_mul_quant(_d(y), _d(torch.zeros(4, 2)), _d(x.float()), p, 4, 0, 0, 0) == -2
+    c = torch.zeros(16, 256, dtype=torch.bfloat16)
+    assert L.tg_moe_unpermute_sum(_d(torch.zeros(8, 256, dtype=torch.float16)), _d(c), p, 2, 0, 0) == -2
+    assert L.tg_moe_unpermute_sum(_d(torch.zeros(4, 256, dtype=torch.bfloat16)), _d(c), p, 2, 0, 0) == -6
+    assert L.tg_moe_unpermute_sum(_d(torch.zeros(8, 256, dtype=torch.bfloat16)), _d(c), 0, 2, 0, 0) == -5
 
 
 def test_quantiser_argument_checks():

@@ -90,7 +90,7 @@ def test_rows_outside_every_group_are_left_alone_and_bad_offsets_are_clamped(dev
     c = torch.full((256, 256), 7.0, dtype=torch.bfloat16, device=dev)
     args = [t.to(dev) for t in (a8, b, As, bs, ind)]
     rc = L.tg_fp8_gemm_blockscaled_grouped(_lib.ref(_lib.desc(c)), *[_lib.ref(_lib.desc(t)) for t in args[:4]],
-                                            args[4].data_ptr(), 128, 128, None, 0.0, dev.index,
+                                            args[4].data_ptr(), 128, 128, None, 0.0, 0, dev.index,
                                            torch.cuda.current_stream().cuda_stream)
     _lib.check_rc(rc)
     _lib.device_status(dev.index)

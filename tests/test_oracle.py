@@ -119,6 +119,27 @@ def test_block_scaled_bias_form_reduces_to_the_reference_form():
     torch.testing.assert_close(full, plain + bias + 0.5 * c, rtol=1e-6, atol=1e-6)
 
 
+def test_moe_oracle_matches_the_reference_torch_moe():
+    """The MoE oracle against outputs of the reference's own torch code on the dequantised operands of the
+    fixture: its first GEMM stage equals tilegym.ops.moe_interface.fused_moe_torch to fp32 summation order, and
+    the whole layer agrees with tests/ops/test_moe.py's Test_MOE.reference within that test's fp8 tolerance
+    (and much closer: the only difference is the e4m3 rounding of the intermediate, which the reference's
+    FP8 path performs and its torch test reference does not)."""
+    g = load_golden("moe_16x256x128_e4_k2.npz")
+    T, topk = g["ids"].shape
+    fc1 = torch.stack([torch.stack([R.ref_w8a8_block_fp8_matmul(g["a8"][t:t + 1], g["w1"][int(g["ids"][t, j])],
+                                                                 g["a_s"][t:t + 1], g["w1_s"][int(g["ids"][t, j])],
+                                                                 [128, 128], torch.float32)[0] for j in range(topk)])
+                       for t in range(T)])
+    torch.testing.assert_close(fc1, g["stage1_f32"], rtol=1e-4, atol=1e-4)
+    for mode in ("ones", "block"):
+        out = R.ref_fused_experts_fp8(g["a8"], g["a_s"], g["w1"], g["w1_s"], g["w2"], g["w2_s"], g["wts"], g["ids"],
+                                      torch.float16, mode)
+        torch.testing.assert_close(out.float(), g["full_f32"], rtol=5e-1, atol=5e-1)  # the reference test's bound
+        assert float((out.float() - g["full_f32"]).abs().max()) <= 0.05 * float(g["full_f32"].abs().max())
+    torch.testing.assert_close(g["stage2_f32"].sum(1), g["full_f32"], rtol=1e-4, atol=1e-4)
+
+
 def test_ref_bmm_follows_torch_bmm():
     torch.manual_seed(1)
     a, b = torch.rand(3, 20, 33, dtype=torch.float16), torch.rand(3, 40, 33, dtype=torch.float16)

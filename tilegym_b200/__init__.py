@@ -28,4 +28,6 @@ from .ops import (  # noqa: F401
     weight_quant_block,
 )
 
+from .moe import FP8MoE, fused_experts_impl, fused_moe, moe_align_block_size  # noqa: E402,F401
+
 __version__ = "0.1.0"

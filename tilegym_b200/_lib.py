@@ -105,8 +105,24 @@ SIGNATURES = {
     ),
     "tg_fp8_gemm_blockscaled_grouped": (
         ctypes.c_int32,
-        [_P, _P, _P, _P, _P, ctypes.c_uint64, ctypes.c_int32, ctypes.c_int32, _P, ctypes.c_float, ctypes.c_int32,
-         ctypes.c_uint64],
+        [_P, _P, _P, _P, _P, ctypes.c_uint64, ctypes.c_int32, ctypes.c_int32, _P, ctypes.c_float, ctypes.c_uint64,
+         ctypes.c_int32, ctypes.c_uint64],
+    ),
+    "tg_moe_route": (
+        ctypes.c_int32,
+        [_P, _P, ctypes.c_int32, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64,
+         ctypes.c_int32, ctypes.c_uint64],
+    ),
+    "tg_moe_permute_rows": (
+        ctypes.c_int32,
+        [_P, _P, _P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64],
+    ),
+    "tg_moe_silu_mul_quant": (
+        ctypes.c_int32,
+        [_P, _P, _P, ctypes.c_uint64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64],
+    ),
+    "tg_moe_unpermute_sum": (
+        ctypes.c_int32, [_P, _P, ctypes.c_uint64, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64],
     ),
     "tg_act_quant": (ctypes.c_int32, [_P, _P, _P, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64]),
     "tg_per_token_group_quant": (

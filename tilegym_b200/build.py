@@ -20,7 +20,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 OBJ_DIR = os.path.join(PKG_DIR, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libtilegym_b200.so")
 
-SOURCES = ["api.cu", "gemm_pertensor.cu", "gemm_pertensor_2cta.cu", "gemm_blockscaled.cu", "gemm_blockscaled_wide.cu", "gemm_blockscaled_smallm.cu", "gemm_smallm.cu", "quant.cu", "group_quant.cu", "no_alloc.cu", "selftest.cu"]
+SOURCES = ["api.cu", "gemm_pertensor.cu", "gemm_pertensor_2cta.cu", "gemm_blockscaled.cu", "gemm_blockscaled_wide.cu", "gemm_blockscaled_smallm.cu", "gemm_smallm.cu", "quant.cu", "group_quant.cu", "no_alloc.cu", "selftest.cu", "moe.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",

@@ -713,7 +713,7 @@ int32_t tg_gemm_dense16(const TgTensorDesc* C, const TgTensorDesc* A, const TgTe
 int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
                                         const TgTensorDesc* As, const TgTensorDesc* Bs, uint64_t m_indptr,
                                         int32_t block_n, int32_t block_k, const TgTensorDesc* bias, float beta,
-                                        int32_t device_id, uint64_t stream) {
+                                        uint64_t row_scale, int32_t device_id, uint64_t stream) {
   int32_t rc;
   if ((rc = check_operand(A, "A")) != TG_OK) return rc;
   if (B == nullptr || As == nullptr || Bs == nullptr) return fail(TG_ERR_NULL, "a descriptor is null");
@@ -740,6 +740,7 @@ int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDes
   if ((As->ptr & 3u) || (Bs->ptr & 3u)) return fail(TG_ERR_ALIGN, "scale pointers must be 4-byte aligned");
   if (m_indptr == 0) return fail(TG_ERR_NULL, "m_indptr is null");
   if (m_indptr & 3u) return fail(TG_ERR_ALIGN, "m_indptr must be 4-byte aligned");
+  if (row_scale & 3u) return fail(TG_ERR_ALIGN, "row_scale must be 4-byte aligned");
   if ((rc = check_bias(bias, G, N)) != TG_OK) return rc;
   if (M == 0) return TG_OK;
 
@@ -776,6 +777,7 @@ int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDes
   p.status = st.status;
   if (knob(kKnobPdl, 1) != 0) p.flags |= 2;  // programmatic dependent launch
   p.m_indptr = reinterpret_cast<const int32_t*>(m_indptr);
+  p.row_scale = reinterpret_cast<const float*>(row_scale);
   p.num_groups = static_cast<int32_t>(G);
   // every group adds at most one partly filled 128-row tile to the ceil(M / 128) a dense problem would have
   const int64_t bound = (M + 127) / 128 + G;

@@ -349,6 +349,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (!ok) break;
       const int row0 = tile.row0 + q * 32;
+      if (kGrouped && p.row_scale != nullptr) {  // e.g. the routing weight of a mixture-of-experts row
+        const float w = row < tile.row_end ? __ldg(p.row_scale + row) : 0.f;
+        const float2 w2 = make_float2(w, w);
+#pragma unroll
+        for (int j = 0; j < 64; ++j) acc2[j] = __fmul2_rn(acc2[j], w2);
+      }
       // bias row of a [groups, N] bias: the tile's weight rows start at b_row0 = group * N + col0 in the [G * N, K] view
       const int64_t bias_off = kGrouped ? static_cast<int64_t>(tile.b_row0 - tile.col0) : 0;
       // a bulk store clips at the ends of C only: in a grouped problem a 32-row slice that runs past the end

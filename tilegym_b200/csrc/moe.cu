@@ -1,0 +1,437 @@
+// The kernels around the grouped block-scaled GEMM that make up the FP8 mixture-of-experts layer
+// (reference: fused_experts_impl, src/tilegym/ops/moe_interface.py:116-322, and its kernels
+// src/tilegym/ops/tilecpp/moe.cuh:72-563).  The reference pads every expert's token list to a multiple of the
+// tile height and lets every GEMM tile gather its rows through sorted_token_ids; here the rows are brought
+// into expert order ONCE, so that both expert GEMMs run on contiguous row segments (m_indptr) with plain TMA
+// loads and bulk stores, and the way back to token order is folded into the final sum over the top-k experts:
+//
+//   tg_moe_route          top-k ids -> per-expert segment offsets, the permutation and its inverse, and the
+//                         routing weights in expert order (a counting sort on the device, no host read-back);
+//   tg_moe_permute_rows   e4m3 activation rows and their 1 x 128 scales -> expert order (a row gather);
+//   tg_moe_silu_mul_quant silu(gate) * up of the first GEMM's output, rounded to 16 bits like the reference's
+//                         intermediate, then to e4m3 for the second GEMM (scale 1 as the reference does, or a
+//                         proper 1 x 128 amax / 448 scale);
+//   tg_moe_unpermute_sum  out[t] = sum over the token's top-k rows of the second GEMM's output (fp32 sum, one rounding).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+#include <cstdio>
+
+#include "tg_internal.h"
+#include "tg_quant_common.cuh"
+
+namespace tg {
+namespace {
+
+// ------------------------------------------------------------------------------------------ routing
+template <typename IdT>
+__global__ void moe_count_kernel(const IdT* __restrict__ ids, int64_t n, int num_experts, int32_t* __restrict__ counts) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t e = static_cast<int64_t>(ids[i]);
+    if (e >= 0 && e < num_experts) atomicAdd(counts + e, 1);
+  }
+}
+
+// One block: exclusive scan of the counts -> m_indptr[0 .. E]; the counts become the experts' write cursors.
+__global__ void moe_scan_kernel(int32_t* __restrict__ counts, int num_experts, int32_t* __restrict__ m_indptr) {
+  __shared__ int32_t carry;
+  __shared__ int32_t warp_sums[32];
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int base = 0; base < num_experts; base += blockDim.x) {
+    const int e = base + threadIdx.x;
+    const int32_t c = e < num_experts ? counts[e] : 0;
+    int32_t incl = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int32_t w = lane < static_cast<int>(blockDim.x >> 5) ? warp_sums[lane] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int32_t v = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += v;
+      }
+      warp_sums[lane] = w;  // inclusive sums of the warps
+    }
+    __syncthreads();
+    const int32_t before = carry + (warp > 0 ? warp_sums[warp - 1] : 0) + incl - c;
+    if (e < num_experts) {
+      m_indptr[e] = before;
+      counts[e] = before;  // cursor
+    }
+    __syncthreads();
+    if (threadIdx.x == blockDim.x - 1) carry = before + c;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) m_indptr[num_experts] = carry;
+}
+
+template <typename IdT, typename WT>
+__global__ void moe_place_kernel(const IdT* __restrict__ ids, const WT* __restrict__ weights, int64_t n, int num_experts,
+                                 int32_t* __restrict__ cursors, int32_t* __restrict__ sorted_ids,
+                                 int32_t* __restrict__ pos, float* __restrict__ w_sorted) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t e = static_cast<int64_t>(ids[i]);
+    if (e >= 0 && e < num_experts) {
+      const int32_t r = atomicAdd(cursors + e, 1);
+      sorted_ids[r] = static_cast<int32_t>(i);
+      pos[i] = r;
+      if (w_sorted != nullptr) w_sorted[r] = weights != nullptr ? static_cast<float>(weights[i]) : 1.0f;
+    } else {
+      pos[i] = -1;  // an id outside [0, E): the (token, slot) pair takes part in nothing
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------ row gather
+// dst row r = src row sorted_ids[r] / topk: `row_bytes` (a multiple of 16) of e4m3 data and `kb` scales.
+__global__ void __launch_bounds__(128) moe_permute_rows_kernel(uint8_t* __restrict__ dst, float* __restrict__ dst_s,
+                                                               const uint8_t* __restrict__ src,
+                                                               const float* __restrict__ src_s,
+                                                               const int32_t* __restrict__ sorted_ids,
+                                                               const int32_t* __restrict__ m_indptr, int num_experts,
+                                                               int topk, int64_t row_bytes, int64_t src_pitch, int kb,
+                                                               int64_t src_s_pitch) {
+  const int32_t rows = __ldg(m_indptr + num_experts);  // rows in expert order (pairs with a valid expert id)
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const int64_t t = __ldg(sorted_ids + r) / topk;
+    const uint4* s4 = reinterpret_cast<const uint4*>(src + t * src_pitch);
+    uint4* d4 = reinterpret_cast<uint4*>(dst + r * row_bytes);
+    for (int64_t c = threadIdx.x; c < row_bytes / 16; c += blockDim.x) d4[c] = __ldg(s4 + c);
+    for (int c = threadIdx.x; c < kb; c += blockDim.x) dst_s[r * kb + c] = __ldg(src_s + t * src_s_pitch + c);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ silu * mul + quantise
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) {
+  return __half2float(v);
+}
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) {
+  return __float2half_rn(v);
+}
+template <typename T>
+__device__ __forceinline__ float round16(float v);
+template <>
+__device__ __forceinline__ float round16<__nv_bfloat16>(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+template <>
+__device__ __forceinline__ float round16<__half>(float v) {
+  return __half2float(__float2half_rn(v));
+}
+
+// One warp per group of 128 output elements (lane = 4 consecutive ones).  X row = [gate (I) | up (I)].
+// mode 0: scale 1, y = e4m3(a) (saturating); mode 1: scale = amax / 448 (1 for an all-zero group), y = e4m3(a / scale).
+template <typename T>
+__global__ void __launch_bounds__(256) moe_silu_mul_quant_kernel(uint8_t* __restrict__ y, float* __restrict__ s,
+                                                                 const T* __restrict__ x,
+                                                                 const int32_t* __restrict__ m_indptr, int num_experts,
+                                                                 int64_t inter, int mode) {
+  const int lane = threadIdx.x & 31;
+  const int64_t groups_per_row = inter / 128;
+  const int64_t rows = m_indptr != nullptr ? static_cast<int64_t>(__ldg(m_indptr + num_experts)) : 0;
+  const int64_t n_groups = rows * groups_per_row;
+  const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  for (int64_t g = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; g < n_groups; g += warps) {
+    const int64_t r = g / groups_per_row, gc = g - r * groups_per_row;
+    const T* gate = x + r * (2 * inter) + gc * 128 + lane * 4;
+    const T* up = gate + inter;
+    const uint2 gv = *reinterpret_cast<const uint2*>(gate);
+    const uint2 uv = *reinterpret_cast<const uint2*>(up);
+    const T* gp = reinterpret_cast<const T*>(&gv);
+    const T* upv = reinterpret_cast<const T*>(&uv);
+    float a[4];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float gf = to_f32<T>(gp[i]), uf = to_f32<T>(upv[i]);
+      // silu(g) * u in fp32, rounded once to the 16-bit type of the reference's intermediate tensor
+      a[i] = round16<T>((gf / (1.0f + expf(-gf))) * uf);
+      amax = fmaxf(amax, fabsf(a[i]));
+    }
+    float scale = 1.0f;
+    if (mode == 1) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      scale = __fdiv_rn(amax, 448.0f);
+      if (scale == 0.f) scale = 1.0f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = __fdiv_rn(a[i], scale);
+    }
+    const uint32_t lo = q8_cast2<kQ8E4M3>(a[0], a[1], -448.f, 448.f);
+    const uint32_t hi = q8_cast2<kQ8E4M3>(a[2], a[3], -448.f, 448.f);
+    *reinterpret_cast<uint32_t*>(y + r * inter + gc * 128 + lane * 4) = lo | (hi << 16);
+    if (lane == 0) s[r * groups_per_row + gc] = scale;
+  }
+}
+
+// ------------------------------------------------------------------------------------------ back to token order
+// out[t, :] = sum_j c[pos[t * topk + j], :] (fp32 sum, one rounding); eight columns per thread.
+template <typename T>
+__global__ void __launch_bounds__(256) moe_unpermute_sum_kernel(T* __restrict__ out, const T* __restrict__ c,
+                                                                const int32_t* __restrict__ pos, int64_t tokens,
+                                                                int topk, int64_t hidden) {
+  const int64_t chunks = hidden / 8;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < tokens * chunks;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t t = i / chunks, ch = i - t * chunks;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < topk; ++j) {
+      const int32_t r = __ldg(pos + t * topk + j);
+      if (r < 0) continue;
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(c + static_cast<int64_t>(r) * hidden) + ch);
+      const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += to_f32<T>(e[k]);
+    }
+    uint4 o;
+    T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) oe[k] = from_f32<T>(acc[k]);
+    reinterpret_cast<uint4*>(out + t * hidden)[ch] = o;
+  }
+}
+
+int grid_for(int64_t work_items, int per_block, int num_sms, int waves) {
+  int64_t g = (work_items + per_block - 1) / per_block;
+  const int64_t cap = static_cast<int64_t>(num_sms) * waves;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return static_cast<int>(g);
+}
+
+struct Guard {
+  int prev = -1;
+  bool changed = false;
+  cudaError_t err = cudaSuccess;
+  explicit Guard(int dev) {
+    err = cudaGetDevice(&prev);
+    if (err == cudaSuccess && prev != dev) {
+      err = cudaSetDevice(dev);
+      changed = (err == cudaSuccess);
+    }
+  }
+  ~Guard() {
+    if (changed) cudaSetDevice(prev);
+  }
+};
+
+int32_t launch_status(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) return TG_OK;
+  char msg[200];
+  snprintf(msg, sizeof(msg), "%s launch failed: %s", what, cudaGetErrorString(e));
+  return api_fail(TG_ERR_LAUNCH, msg);
+}
+
+bool contiguous_2d(const TgTensorDesc* t) { return t->ndim == 2 && t->strides[1] == 1 && t->strides[0] == t->shape[1]; }
+
+}  // namespace
+}  // namespace tg
+
+using namespace tg;
+
+extern "C" {
+
+TG_API int32_t tg_moe_route(const TgTensorDesc* topk_ids, const TgTensorDesc* topk_weights, int32_t num_experts,
+                            uint64_t m_indptr, uint64_t sorted_ids, uint64_t pos, uint64_t w_sorted, uint64_t scratch,
+                            int32_t device_id, uint64_t stream) {
+  if (topk_ids == nullptr) return api_fail(TG_ERR_NULL, "topk_ids descriptor is null");
+  if (topk_ids->dtype != TG_I32 && topk_ids->dtype != TG_I64) return api_fail(TG_ERR_DTYPE, "topk_ids must be int32 or int64");
+  if (!contiguous_2d(topk_ids)) return api_fail(TG_ERR_ARGS, "topk_ids must be a contiguous [tokens, top_k] matrix");
+  if (num_experts < 1 || num_experts > (1 << 20)) return api_fail(TG_ERR_ARGS, "num_experts out of range");
+  const int64_t n = topk_ids->shape[0] * topk_ids->shape[1];
+  if (n > 0x7fffffff) return api_fail(TG_ERR_ARGS, "too many (token, expert) pairs");
+  if (topk_weights != nullptr) {
+    if (topk_weights->dtype != TG_F32 && topk_weights->dtype != TG_BF16 && topk_weights->dtype != TG_F16)
+      return api_fail(TG_ERR_DTYPE, "topk_weights must be f32, f16 or bf16");
+    if (!contiguous_2d(topk_weights) || topk_weights->shape[0] != topk_ids->shape[0] ||
+        topk_weights->shape[1] != topk_ids->shape[1])
+      return api_fail(TG_ERR_ARGS, "topk_weights must be contiguous and shaped like topk_ids");
+    if (w_sorted == 0) return api_fail(TG_ERR_NULL, "w_sorted is null");
+  }
+  if (m_indptr == 0 || sorted_ids == 0 || pos == 0 || scratch == 0) return api_fail(TG_ERR_NULL, "an output pointer is null");
+  if ((m_indptr | sorted_ids | pos | w_sorted | scratch) & 3u) return api_fail(TG_ERR_ALIGN, "outputs must be 4-byte aligned");
+  if (n > 0 && (topk_ids->ptr == 0 || (topk_weights != nullptr && topk_weights->ptr == 0)))
+    return api_fail(TG_ERR_NULL, "data pointer is null");
+  Guard guard(device_id);
+  if (guard.err != cudaSuccess) {
+    cudaGetLastError();
+    return api_fail(TG_ERR_DEVICE, "cannot select the CUDA device");
+  }
+  int num_sms = 0;
+  int32_t* status = nullptr;
+  int32_t rc = api_init_device(device_id, &num_sms, &status);
+  if (rc != TG_OK) return rc;
+  cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+  int32_t* counts = reinterpret_cast<int32_t*>(scratch);
+  if (cudaMemsetAsync(counts, 0, sizeof(int32_t) * static_cast<size_t>(num_experts), cs) != cudaSuccess)
+    return launch_status("moe route (clear)");
+  const int grid = grid_for(n, 256, num_sms, 8);
+  const bool i64 = topk_ids->dtype == TG_I64;
+  if (n > 0) {
+    if (i64)
+      moe_count_kernel<int64_t><<<grid, 256, 0, cs>>>(reinterpret_cast<const int64_t*>(topk_ids->ptr), n, num_experts, counts);
+    else
+      moe_count_kernel<int32_t><<<grid, 256, 0, cs>>>(reinterpret_cast<const int32_t*>(topk_ids->ptr), n, num_experts, counts);
+  }
+  moe_scan_kernel<<<1, 1024, 0, cs>>>(counts, num_experts, reinterpret_cast<int32_t*>(m_indptr));
+  if (n > 0) {
+    int32_t* sid = reinterpret_cast<int32_t*>(sorted_ids);
+    int32_t* ps = reinterpret_cast<int32_t*>(pos);
+    float* ws = reinterpret_cast<float*>(w_sorted);
+    const int wd = topk_weights != nullptr ? topk_weights->dtype : TG_F32;
+    const void* wp = topk_weights != nullptr ? reinterpret_cast<const void*>(topk_weights->ptr) : nullptr;
+#define TG_PLACE(IdT, WT)                                                                                       \
+  moe_place_kernel<IdT, WT><<<grid, 256, 0, cs>>>(reinterpret_cast<const IdT*>(topk_ids->ptr),                   \
+                                                  reinterpret_cast<const WT*>(wp), n, num_experts, counts, sid, ps, ws)
+    if (i64) {
+      if (wd == TG_BF16) TG_PLACE(int64_t, __nv_bfloat16);
+      else if (wd == TG_F16) TG_PLACE(int64_t, __half);
+      else TG_PLACE(int64_t, float);
+    } else {
+      if (wd == TG_BF16) TG_PLACE(int32_t, __nv_bfloat16);
+      else if (wd == TG_F16) TG_PLACE(int32_t, __half);
+      else TG_PLACE(int32_t, float);
+    }
+#undef TG_PLACE
+  }
+  return launch_status("moe route");
+}
+
+TG_API int32_t tg_moe_permute_rows(const TgTensorDesc* A_sorted, const TgTensorDesc* As_sorted, const TgTensorDesc* A,
+                                   const TgTensorDesc* As, uint64_t sorted_ids, uint64_t m_indptr, int32_t num_experts,
+                                   int32_t topk, int32_t device_id, uint64_t stream) {
+  if (A_sorted == nullptr || As_sorted == nullptr || A == nullptr || As == nullptr) return api_fail(TG_ERR_NULL, "a descriptor is null");
+  if (A->dtype != TG_F8E4M3 || A_sorted->dtype != TG_F8E4M3) return api_fail(TG_ERR_DTYPE, "A and A_sorted must be float8_e4m3fn");
+  if (As->dtype != TG_F32 || As_sorted->dtype != TG_F32) return api_fail(TG_ERR_DTYPE, "scales must be f32");
+  if (A->ndim != 2 || As->ndim != 2 || !contiguous_2d(A_sorted) || !contiguous_2d(As_sorted))
+    return api_fail(TG_ERR_ARGS, "A, As must be 2-D and the outputs contiguous 2-D");
+  const int64_t T = A->shape[0], K = A->shape[1], KB = As->shape[1], R = A_sorted->shape[0];
+  if (A->strides[1] != 1 || As->strides[1] != 1 || A->strides[0] < K || As->strides[0] < KB)
+    return api_fail(TG_ERR_ARGS, "rows of A and As must be contiguous");
+  if (K % 16 != 0 || (A->strides[0] & 15) != 0) return api_fail(TG_ERR_ALIGN, "K and the row pitch of A must be multiples of 16");
+  if (As->shape[0] != T || A_sorted->shape[1] != K || As_sorted->shape[0] != R || As_sorted->shape[1] != KB)
+    return api_fail(TG_ERR_ARGS, "shapes of A, As, A_sorted, As_sorted do not fit together");
+  if (topk < 1 || num_experts < 1) return api_fail(TG_ERR_ARGS, "topk and num_experts must be positive");
+  if (R > T * topk) return api_fail(TG_ERR_ARGS, "A_sorted has more rows than tokens x top_k");
+  if (sorted_ids == 0 || m_indptr == 0) return api_fail(TG_ERR_NULL, "sorted_ids / m_indptr is null");
+  if (R == 0 || T == 0) return TG_OK;
+  if (A->ptr == 0 || As->ptr == 0 || A_sorted->ptr == 0 || As_sorted->ptr == 0) return api_fail(TG_ERR_NULL, "data pointer is null");
+  if ((A->ptr | A_sorted->ptr) & 15u) return api_fail(TG_ERR_ALIGN, "A and A_sorted must be 16-byte aligned");
+  Guard guard(device_id);
+  if (guard.err != cudaSuccess) {
+    cudaGetLastError();
+    return api_fail(TG_ERR_DEVICE, "cannot select the CUDA device");
+  }
+  int num_sms = 0;
+  int32_t* status = nullptr;
+  int32_t rc = api_init_device(device_id, &num_sms, &status);
+  if (rc != TG_OK) return rc;
+  const int grid = grid_for(R, 1, num_sms, 16);
+  moe_permute_rows_kernel<<<grid, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<uint8_t*>(A_sorted->ptr), reinterpret_cast<float*>(As_sorted->ptr),
+      reinterpret_cast<const uint8_t*>(A->ptr), reinterpret_cast<const float*>(As->ptr),
+      reinterpret_cast<const int32_t*>(sorted_ids), reinterpret_cast<const int32_t*>(m_indptr), num_experts, topk, K,
+      A->strides[0], static_cast<int>(KB), As->strides[0]);
+  return launch_status("moe permute rows");
+}
+
+TG_API int32_t tg_moe_silu_mul_quant(const TgTensorDesc* Y, const TgTensorDesc* S, const TgTensorDesc* X, uint64_t m_indptr,
+                                     int32_t num_experts, int32_t mode, int32_t device_id, uint64_t stream) {
+  if (Y == nullptr || S == nullptr || X == nullptr) return api_fail(TG_ERR_NULL, "a descriptor is null");
+  if (X->dtype != TG_BF16 && X->dtype != TG_F16) return api_fail(TG_ERR_DTYPE, "X must be bf16 or f16");
+  if (Y->dtype != TG_F8E4M3) return api_fail(TG_ERR_DTYPE, "Y must be float8_e4m3fn");
+  if (S->dtype != TG_F32) return api_fail(TG_ERR_DTYPE, "S must be f32");
+  if (!contiguous_2d(X) || !contiguous_2d(Y) || !contiguous_2d(S)) return api_fail(TG_ERR_ARGS, "X, Y and S must be contiguous 2-D");
+  const int64_t R = X->shape[0], I = X->shape[1] / 2;
+  if (X->shape[1] != 2 * I || I % 128 != 0 || I == 0) return api_fail(TG_ERR_ARGS, "X must be [rows, 2 * I] with I a multiple of 128");
+  if (Y->shape[0] != R || Y->shape[1] != I || S->shape[0] != R || S->shape[1] != I / 128)
+    return api_fail(TG_ERR_ARGS, "Y must be [rows, I] and S [rows, I / 128]");
+  if (mode != 0 && mode != 1) return api_fail(TG_ERR_ARGS, "mode must be 0 (scale 1) or 1 (amax / 448 per 128 elements)");
+  if (m_indptr == 0) return api_fail(TG_ERR_NULL, "m_indptr is null");
+  if (num_experts < 1) return api_fail(TG_ERR_ARGS, "num_experts must be positive");
+  if (R == 0) return TG_OK;
+  if (X->ptr == 0 || Y->ptr == 0 || S->ptr == 0) return api_fail(TG_ERR_NULL, "data pointer is null");
+  if ((X->ptr & 7u) || (Y->ptr & 3u)) return api_fail(TG_ERR_ALIGN, "X must be 8-byte and Y 4-byte aligned");
+  Guard guard(device_id);
+  if (guard.err != cudaSuccess) {
+    cudaGetLastError();
+    return api_fail(TG_ERR_DEVICE, "cannot select the CUDA device");
+  }
+  int num_sms = 0;
+  int32_t* status = nullptr;
+  int32_t rc = api_init_device(device_id, &num_sms, &status);
+  if (rc != TG_OK) return rc;
+  const int grid = grid_for(R * (I / 128), 8, num_sms, 8);
+  cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+  if (X->dtype == TG_BF16)
+    moe_silu_mul_quant_kernel<__nv_bfloat16><<<grid, 256, 0, cs>>>(
+        reinterpret_cast<uint8_t*>(Y->ptr), reinterpret_cast<float*>(S->ptr), reinterpret_cast<const __nv_bfloat16*>(X->ptr),
+        reinterpret_cast<const int32_t*>(m_indptr), num_experts, I, mode);
+  else
+    moe_silu_mul_quant_kernel<__half><<<grid, 256, 0, cs>>>(
+        reinterpret_cast<uint8_t*>(Y->ptr), reinterpret_cast<float*>(S->ptr), reinterpret_cast<const __half*>(X->ptr),
+        reinterpret_cast<const int32_t*>(m_indptr), num_experts, I, mode);
+  return launch_status("moe silu_mul_quant");
+}
+
+TG_API int32_t tg_moe_unpermute_sum(const TgTensorDesc* out, const TgTensorDesc* C, uint64_t pos, int32_t topk,
+                                    int32_t device_id, uint64_t stream) {
+  if (out == nullptr || C == nullptr) return api_fail(TG_ERR_NULL, "a descriptor is null");
+  if ((C->dtype != TG_BF16 && C->dtype != TG_F16) || out->dtype != C->dtype)
+    return api_fail(TG_ERR_DTYPE, "C and out must both be bf16 or both f16");
+  if (!contiguous_2d(out) || !contiguous_2d(C)) return api_fail(TG_ERR_ARGS, "out and C must be contiguous 2-D");
+  const int64_t T = out->shape[0], H = out->shape[1];
+  if (C->shape[1] != H || H % 8 != 0) return api_fail(TG_ERR_ARGS, "C must have out's width, a multiple of 8");
+  if (topk < 1 || C->shape[0] > T * topk) return api_fail(TG_ERR_ARGS, "C has more rows than tokens x top_k");
+  if (pos == 0) return api_fail(TG_ERR_NULL, "pos is null");
+  if (T == 0 || H == 0) return TG_OK;
+  if (out->ptr == 0 || (C->shape[0] > 0 && C->ptr == 0)) return api_fail(TG_ERR_NULL, "data pointer is null");
+  if ((out->ptr | C->ptr) & 15u) return api_fail(TG_ERR_ALIGN, "out and C must be 16-byte aligned");
+  Guard guard(device_id);
+  if (guard.err != cudaSuccess) {
+    cudaGetLastError();
+    return api_fail(TG_ERR_DEVICE, "cannot select the CUDA device");
+  }
+  int num_sms = 0;
+  int32_t* status = nullptr;
+  int32_t rc = api_init_device(device_id, &num_sms, &status);
+  if (rc != TG_OK) return rc;
+  const int grid = grid_for(T * (H / 8), 256, num_sms, 8);
+  cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+  if (C->dtype == TG_BF16)
+    moe_unpermute_sum_kernel<__nv_bfloat16><<<grid, 256, 0, cs>>>(
+        reinterpret_cast<__nv_bfloat16*>(out->ptr), reinterpret_cast<const __nv_bfloat16*>(C->ptr),
+        reinterpret_cast<const int32_t*>(pos), T, topk, H);
+  else
+    moe_unpermute_sum_kernel<__half><<<grid, 256, 0, cs>>>(reinterpret_cast<__half*>(out->ptr),
+                                                           reinterpret_cast<const __half*>(C->ptr),
+                                                           reinterpret_cast<const int32_t*>(pos), T, topk, H);
+  return launch_status("moe unpermute_sum");
+}
+
+}  // extern "C"

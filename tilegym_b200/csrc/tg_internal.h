@@ -41,6 +41,7 @@ struct GemmParams {
   const int32_t* m_indptr;  // device, num_groups + 1 entries
   int32_t num_groups;
   int32_t mtile_bound;  // ceil(M / 128) + num_groups >= the number of 128-row tiles of all groups
+  const float* row_scale;  // grouped GEMM: nullptr, or one factor per row of C applied before bias and rounding
   // diagnostics
   int32_t* status;         // device status word
   uint32_t wait_limit_us;  // bound of every device-side wait in microseconds (0 = the 2 s default)

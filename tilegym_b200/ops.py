@@ -183,6 +183,7 @@ def ragged_block_scaled_bmm(
     bias: Optional[torch.Tensor] = None,
     out: Optional[torch.Tensor] = None,
     beta: float = 0.0,
+    row_scale: Optional[torch.Tensor] = None,
     **kwargs,
 ) -> torch.Tensor:
     """Ragged (grouped) block-scaled FP8 GEMM: rows [m_indptr[q], m_indptr[q+1]) of `a` times weight b[q].T.
@@ -194,7 +195,8 @@ def ragged_block_scaled_bmm(
     Differences: segments need no alignment to 128 rows and may be empty; `max_m` / `max_m_device` are accepted
     and not needed (the kernel reads m_indptr itself, nothing is read back to the host); only 128 x 128 scale
     blocks and e4m3 inputs are implemented.  Additions (keyword only in effect): `bias` (Q, N) adds row q to
-    the rows of group q, `out` / `beta` write into (accumulate onto) a caller's tensor.
+    the rows of group q, `out` / `beta` write into (accumulate onto) a caller's tensor, `row_scale` (total_m,)
+    f32 multiplies every row of the product (a mixture-of-experts routing weight).
     """
     assert transpose_a is False and transpose_b is True, "Only NT layout is supported"
     dev = _need_cuda(a, b, a_scale, b_scale, m_indptr)
@@ -223,10 +225,12 @@ def ragged_block_scaled_bmm(
         c = torch.empty((total_m, N), device=dev, dtype=out_dtype)
     if bias is not None and not bias.is_contiguous():
         bias = bias.contiguous()
+    if row_scale is not None:
+        assert row_scale.dtype == torch.float32 and row_scale.is_contiguous() and row_scale.numel() >= total_m
     rc = _lib.lib().tg_fp8_gemm_blockscaled_grouped(
         _lib.ref(_lib.desc(c)), _lib.ref(_lib.desc(a)), _lib.ref(_lib.desc(b)), _lib.ref(_lib.desc(a_scale)),
-        _lib.ref(_lib.desc(b_scale)), m_indptr.data_ptr(), 128, 128, _lib.desc(bias), float(beta), dev.index,
-        _stream(dev),
+        _lib.ref(_lib.desc(b_scale)), m_indptr.data_ptr(), 128, 128, _lib.desc(bias), float(beta),
+        row_scale.data_ptr() if row_scale is not None else 0, dev.index, _stream(dev),
     )
     _lib.check_rc(rc)
     return c
