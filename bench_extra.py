@@ -268,6 +268,36 @@ def llama70b_one_gpu(dev, fp8_peak_tflops: float):
             "frac_of_burst_peak": round(tflops / fp8_peak_tflops, 3)}
 
 
+def moe_layer_sweep(dev, fp8_peak_tflops: float):
+    """One FP8 mixture-of-experts layer with DeepSeek-V2-Lite's expert shape (hidden 2048, intermediate 1408 -> 1536
+    here, a multiple of 128; 64 experts, top-6) on 4096 tokens: the whole fused_experts_impl call, with the first
+    GEMM's SiLU * mul + quantise epilogue and without it (separate elementwise pass)."""
+    from tilegym_b200 import moe
+
+    T, H, I, E, topk = 4096, 2048, 1536, 64, 6
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(T, H, generator=g, device=dev, dtype=torch.bfloat16)
+    w1 = torch.randn(E, 2 * I, H, generator=g, device=dev, dtype=torch.bfloat16).mul_(0.05).to(torch.float8_e4m3fn)
+    w2 = torch.randn(E, H, I, generator=g, device=dev, dtype=torch.bfloat16).mul_(0.05).to(torch.float8_e4m3fn)
+    w1s = torch.rand(E, 2 * I // 128, H // 128, generator=g, device=dev) + 0.5
+    w2s = torch.rand(E, H // 128, I // 128, generator=g, device=dev) + 0.5
+    ids = torch.randint(0, E, (T, topk), generator=g, device=dev)
+    wts = torch.softmax(torch.randn(T, topk, generator=g, device=dev), dim=-1)
+    w1i, w1si = moe.interleave_gate_up_blocks(w1, w1s)
+    flops = 2.0 * T * topk * (2 * I * H + H * I)
+    res = {"shape": f"tokens={T} hidden={H} intermediate={I} experts={E} top_k={topk}", "gflop": round(flops / 1e9, 1)}
+    fused = lambda i: moe.fused_experts_impl(x, w1i, w2, wts, ids, use_fp8_w8a8=True, w1_scale=w1si, w2_scale=w2s,  # noqa: E731
+                                             a2_quant="block", w1_interleaved=True)
+    separate = lambda i: moe.fused_experts_impl(x, w1, w2, wts, ids, use_fp8_w8a8=True, w1_scale=w1s, w2_scale=w2s,  # noqa: E731
+                                                a2_quant="block")
+    # the layer is a dozen short launches: replayed from a CUDA graph (its routing tables never leave the device)
+    res["fused_epilogue_us"] = round(graph_time_us(fused, 2, replays=10), 1)
+    res["separate_silu_mul_us"] = round(graph_time_us(separate, 2, replays=10), 1)
+    res["fused_tflops"] = round(flops / res["fused_epilogue_us"] / 1e6, 1)
+    res["fused_frac_of_burst_peak"] = round(res["fused_tflops"] / fp8_peak_tflops, 3)
+    return res
+
+
 def run_configs(dev, peaks):
     """Bounded sweeps of the benchmark configurations the headline number does not cover."""
     hbm = float(peaks["hbm_gbs"])
@@ -293,6 +323,7 @@ def run(dev, peaks):
         "method": "CUDA-graph replay over rotating weight copies (> 3x L2), time per launch; fractions are of the "
                   "measured HBM copy bandwidth / of 2 x measured bf16 burst",
         "grouped_block_scaled": grouped_sweep(dev, fp8),
+        "moe_layer": moe_layer_sweep(dev, fp8),
         "quantisers": quantiser_sweep(dev, hbm),
         "swiglu_gate_up": swiglu_sweep(dev),
         "llama8b_mlp_block": mlp_block_sweep(dev),

@@ -175,6 +175,18 @@ TG_API int32_t tg_moe_permute_rows(const TgTensorDesc* A_sorted, const TgTensorD
                                    const TgTensorDesc* As, uint64_t sorted_ids, uint64_t m_indptr, int32_t num_experts,
                                    int32_t topk, int32_t device_id, uint64_t stream);
 
+/* The first expert GEMM with the step after it in its epilogue: grouped block-scaled GEMM as above whose weights'
+ * rows alternate 128 gate rows and 128 up rows (B: (G, 2 I, K), Bs rows likewise; arrange once at load time), so
+ * that every 128 x 256 tile holds gate and up of 128 outputs.  Per row: both rounded to round_dtype (bf16 / f16, the
+ * type of the reference's intermediate), silu(gate) * up, rounded again, then e4m3 with quant_mode 0 (scale 1) or 1
+ * (amax / 448 over each 128 outputs).  Y: (M, I) e4m3; Ys: (M, I / 128) f32.  The [M, 2 I] intermediate never
+ * reaches memory.  Replaces invoke_fused_moe_kernel + silu_and_mul + the cast of
+ * src/tilegym/ops/moe_interface.py:247-279 (kernel src/tilegym/ops/tilecpp/moe.cuh:249-405). */
+TG_API int32_t tg_fp8_gemm_blockscaled_grouped_swiglu(const TgTensorDesc* Y, const TgTensorDesc* Ys, const TgTensorDesc* A,
+                                                      const TgTensorDesc* B, const TgTensorDesc* As, const TgTensorDesc* Bs,
+                                                      uint64_t m_indptr, int32_t round_dtype, int32_t quant_mode,
+                                                      int32_t device_id, uint64_t stream);
+
 /* Between the two expert GEMMs: a = silu(X[:, :I]) * X[:, I:] in fp32, rounded to X's 16-bit type (the reference's
  * intermediate tensor, moe_interface.py:262-267), then quantised to e4m3 for the second GEMM.  mode 0: scale 1 and
  * a saturating cast, the reference's a2_scale of ones (moe_interface.py:269-279); mode 1: one scale amax / 448 per

@@ -114,6 +114,27 @@ def test_fused_experts_reference_test_shapes(dev, T, H, I, E, topk):
     _lib.device_status(dev.index)
 
 
+@pytest.mark.parametrize("a2_quant", ["ones", "block"])
+@pytest.mark.parametrize("dtype", [torch.float8_e4m3fn, torch.bfloat16])
+@pytest.mark.parametrize("T,H,I,E,topk", [(64, 1024, 512, 20, 8), (700, 512, 384, 6, 3), (5, 256, 128, 3, 1)])
+def test_first_gemm_with_silu_mul_in_its_epilogue(dev, T, H, I, E, topk, dtype, a2_quant):
+    """With the gate / up rows of w1 interleaved in blocks of 128 the first GEMM applies silu * mul and the e4m3
+    quantisation itself: same oracle, same tolerance, and close to the unfused path (not bit-identical: the fused
+    epilogue uses the fast exponential)."""
+    x, w1, w1s, w2, w2s, wts, ids = make_case(T, H, I, E, topk, seed=3 * T + E)
+    a8, a_s = R.ref_act_quant(x.to(torch.bfloat16) if dtype == torch.bfloat16 else x, 128)
+    out_dtype = torch.bfloat16 if dtype == torch.bfloat16 else torch.float16
+    ref = R.ref_fused_experts_fp8(a8, a_s, w1, w1s, w2, w2s, wts, ids, out_dtype, a2_quant)
+    w1i, w1si = moe.interleave_gate_up_blocks(w1.to(dev), w1s.to(dev))
+    hidden = x.to(torch.bfloat16).to(dev) if dtype == torch.bfloat16 else a8.to(dev)
+    out = moe.fused_experts_impl(hidden, w1i, w2.to(dev), wts.to(dev), ids.to(dev), use_fp8_w8a8=True, w1_scale=w1si,
+                                 w2_scale=w2s.to(dev), a1_scale=None if dtype == torch.bfloat16 else a_s.to(dev),
+                                 a2_quant=a2_quant, w1_interleaved=True)
+    assert out.dtype == out_dtype
+    close_enough(out, ref)
+    _lib.device_status(dev.index)
+
+
 def test_fused_moe_bf16_activations_are_quantised_on_the_way(dev):
     x, w1, w1s, w2, w2s, wts, ids = make_case(48, 512, 256, 8, 2, seed=11, dtype=torch.bfloat16)
     a8, a_s = R.ref_act_quant(x, 128)
@@ -150,11 +171,12 @@ def test_silu_mul_quant_and_unpermute_sum_pieces(dev):
     R_, I = 50, 384
     g = torch.Generator().manual_seed(6)
     x = (torch.randn(R_, 2 * I, generator=g) * 2).to(torch.float16)
-    ind = torch.tensor([0, 20, 50], dtype=torch.int32)
+    ind = torch.tensor([0, 20, 50], dtype=torch.int32, device=dev)  # device operands stay referenced until the
+    xd = x.to(dev)                                                  # kernels that read them have been enqueued
     for mode, name in ((0, "ones"), (1, "block")):
         y = torch.zeros(R_, I, dtype=torch.float8_e4m3fn, device=dev)
         s = torch.zeros(R_, I // 128, device=dev)
-        rc = _lib.lib().tg_moe_silu_mul_quant(_lib.desc(y), _lib.desc(s), _lib.desc(x.to(dev)), ind.to(dev).data_ptr(), 2,
+        rc = _lib.lib().tg_moe_silu_mul_quant(_lib.desc(y), _lib.desc(s), _lib.desc(xd), ind.data_ptr(), 2,
                                               mode, dev.index, torch.cuda.current_stream(dev).cuda_stream)
         _lib.check_rc(rc)
         yr, sr = R.ref_moe_silu_mul_quant(x, name)
@@ -169,7 +191,8 @@ def test_silu_mul_quant_and_unpermute_sum_pieces(dev):
     pos = torch.randperm(T * topk, generator=g).to(torch.int32)
     pos[7] = -1
     out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
-    _lib.check_rc(_lib.lib().tg_moe_unpermute_sum(_lib.desc(out), _lib.desc(c.to(dev)), pos.to(dev).data_ptr(), topk,
+    cd, posd = c.to(dev), pos.to(dev)
+    _lib.check_rc(_lib.lib().tg_moe_unpermute_sum(_lib.desc(out), _lib.desc(cd), posd.data_ptr(), topk,
                                                    dev.index, torch.cuda.current_stream(dev).cuda_stream))
     rows = c.float()[pos.long().clamp_min(0)] * (pos >= 0).float()[:, None]
     assert torch.equal(out.cpu(), rows.view(T, topk, H).sum(1).to(torch.bfloat16))

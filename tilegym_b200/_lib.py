@@ -108,6 +108,10 @@ SIGNATURES = {
         [_P, _P, _P, _P, _P, ctypes.c_uint64, ctypes.c_int32, ctypes.c_int32, _P, ctypes.c_float, ctypes.c_uint64,
          ctypes.c_int32, ctypes.c_uint64],
     ),
+    "tg_fp8_gemm_blockscaled_grouped_swiglu": (
+        ctypes.c_int32,
+        [_P, _P, _P, _P, _P, _P, ctypes.c_uint64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64],
+    ),
     "tg_moe_route": (
         ctypes.c_int32,
         [_P, _P, ctypes.c_int32, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64,

@@ -794,6 +794,85 @@ int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDes
   return TG_OK;
 }
 
+// First GEMM of a mixture-of-experts layer with SiLU * mul and the e4m3 quantisation in its epilogue.
+int32_t tg_fp8_gemm_blockscaled_grouped_swiglu(const TgTensorDesc* Y, const TgTensorDesc* Ys, const TgTensorDesc* A,
+                                               const TgTensorDesc* B, const TgTensorDesc* As, const TgTensorDesc* Bs,
+                                               uint64_t m_indptr, int32_t round_dtype, int32_t quant_mode,
+                                               int32_t device_id, uint64_t stream) {
+  int32_t rc;
+  if ((rc = check_operand(A, "A")) != TG_OK) return rc;
+  if (Y == nullptr || Ys == nullptr || B == nullptr || As == nullptr || Bs == nullptr) return fail(TG_ERR_NULL, "a descriptor is null");
+  if (B->dtype != TG_F8E4M3 || Y->dtype != TG_F8E4M3) return fail(TG_ERR_DTYPE, "B and Y must be float8_e4m3fn");
+  if (round_dtype != TG_BF16 && round_dtype != TG_F16) return fail(TG_ERR_DTYPE, "round_dtype must be bf16 or f16");
+  if (quant_mode != 0 && quant_mode != 1) return fail(TG_ERR_ARGS, "quant_mode must be 0 (scale 1) or 1 (amax / 448 per 128 outputs)");
+  if (B->ndim != 3) return fail(TG_ERR_ARGS, "B must be [groups, N, K], got %d-D", B->ndim);
+  const int64_t M = A->shape[0], K = A->shape[1], G = B->shape[0], N = B->shape[1];
+  if (G <= 0 || N <= 0 || B->shape[2] != K) return fail(TG_ERR_ARGS, "B must be [groups >= 1, N >= 1, K = %lld]", (long long)K);
+  if (N % 256 != 0) return fail(TG_ERR_ARGS, "N (gate + up rows, alternating in blocks of 128) must be a multiple of 256, got %lld", (long long)N);
+  if (B->strides[2] != 1 || B->strides[1] != K || B->strides[0] != N * K) return fail(TG_ERR_ARGS, "B must be contiguous");
+  if (B->ptr == 0) return fail(TG_ERR_NULL, "B data pointer is null");
+  if ((B->ptr & 15u) != 0 || (K & 15) != 0) return fail(TG_ERR_ALIGN, "B needs a 16-byte aligned base and K %% 16 == 0 for TMA");
+  if (G * N > 0x7fffffff || G > 0x7fffff) return fail(TG_ERR_ARGS, "B is too large");
+  const int64_t KB = (K + 127) / 128, NB = N / 128, I = N / 2;
+  if (Y->ndim != 2 || Y->shape[0] != M || Y->shape[1] != I || Y->strides[1] != 1 || Y->strides[0] != I)
+    return fail(TG_ERR_ARGS, "Y must be a contiguous [M, N / 2] matrix");
+  if (Ys->dtype != TG_F32 || Ys->ndim != 2 || Ys->shape[0] != M || Ys->shape[1] != I / 128 || Ys->strides[1] != 1 ||
+      Ys->strides[0] != I / 128)
+    return fail(TG_ERR_ARGS, "Ys must be a contiguous f32 [M, N / 256] matrix");
+  if (As->dtype != TG_F32 || Bs->dtype != TG_F32) return fail(TG_ERR_DTYPE, "As and Bs must be f32");
+  if (As->ndim != 2 || As->shape[0] != M || As->shape[1] != KB || As->strides[1] != 1 || As->strides[0] < KB)
+    return fail(TG_ERR_ARGS, "As must be [M, ceil(K/128)] with contiguous rows");
+  if (Bs->ndim != 3 || Bs->shape[0] != G || Bs->shape[1] != NB || Bs->shape[2] != KB || Bs->strides[2] != 1 ||
+      Bs->strides[1] != KB || Bs->strides[0] != NB * KB)
+    return fail(TG_ERR_ARGS, "Bs must be contiguous [groups, N / 128, ceil(K/128)]");
+  if (m_indptr == 0) return fail(TG_ERR_NULL, "m_indptr is null");
+  if (m_indptr & 3u) return fail(TG_ERR_ALIGN, "m_indptr must be 4-byte aligned");
+  if (M == 0) return TG_OK;
+  if (Y->ptr == 0 || Ys->ptr == 0 || As->ptr == 0 || Bs->ptr == 0) return fail(TG_ERR_NULL, "data pointer is null");
+  if ((Y->ptr & 15u) || (Ys->ptr & 3u) || (As->ptr & 3u) || (Bs->ptr & 3u)) return fail(TG_ERR_ALIGN, "Y must be 16-byte, scales 4-byte aligned");
+
+  DeviceGuard guard(device_id);
+  if (guard.err != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TG_ERR_DEVICE, "cannot select CUDA device %d", device_id);
+  }
+  if ((rc = init_device(device_id)) != TG_OK) return rc;
+  const DeviceState& st = g_dev[device_id];
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.wait_limit_us = g_wait_limit_us;
+  p.M = static_cast<int32_t>(M);
+  p.N = static_cast<int32_t>(N);
+  p.K = static_cast<int32_t>(K);
+  p.num_kb = static_cast<int32_t>(KB);
+  p.tiles_n = static_cast<int32_t>(N / 256);
+  p.C = reinterpret_cast<void*>(Y->ptr);
+  p.ldc = I;
+  p.out_dtype = round_dtype;
+  p.alpha = 1.0f;
+  p.As = reinterpret_cast<const float*>(As->ptr);
+  p.Bs = reinterpret_cast<const float*>(Bs->ptr);
+  p.ldas = As->strides[0];
+  p.ldbs = KB;
+  p.splits = 1;
+  p.kb_per_split = p.num_kb;
+  p.status = st.status;
+  if (knob(kKnobPdl, 1) != 0) p.flags |= 2;
+  p.m_indptr = reinterpret_cast<const int32_t*>(m_indptr);
+  p.num_groups = static_cast<int32_t>(G);
+  p.y_scale = reinterpret_cast<float*>(Ys->ptr);
+  p.quant_mode = quant_mode;
+  const int64_t bound = (M + 127) / 128 + G;
+  if (bound * p.tiles_n > 0x3fffffff) return fail(TG_ERR_ARGS, "problem has too many tiles");
+  p.mtile_bound = static_cast<int32_t>(bound);
+  CUtensorMap tmA, tmB;
+  if ((rc = make_map(&tmA, A->ptr, M, K, A->strides[0], 128)) != TG_OK) return rc;
+  if ((rc = make_map(&tmB, B->ptr, G * N, K, K, 256)) != TG_OK) return rc;
+  cudaError_t e = launch_gemm_blockscaled_grouped_swiglu(tmA, tmB, p, st.num_sms, reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(TG_ERR_LAUNCH, "grouped block-scaled GEMM (SiLU * mul epilogue) launch failed: %s", cudaGetErrorString(e));
+  return TG_OK;
+}
+
 int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
                                 const TgTensorDesc* As, const TgTensorDesc* Bs, int32_t block_n, int32_t block_k,
                                 const TgTensorDesc* bias, float beta, uint64_t workspace, uint64_t workspace_bytes,

@@ -12,6 +12,8 @@
 // src/tilegym/suites/flashinfer/cutile/gemm/ragged_block_scaled_bmm.py:497-616: rows [m_indptr[g], m_indptr[g+1])
 // of A use weight g; only the tile look-up differs (locate_tile).
 // Roles: warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, warps 2-3 idle, warps 4-11 promotion + store.
+#include <cuda_fp8.h>
+
 #include "tg_gemm_common.cuh"
 
 namespace tg {
@@ -45,7 +47,7 @@ constexpr int kCtrlBytes = 256;
 constexpr int kOutBufBytes = 32 * 128;  // per promotion warp: 32 rows x 64 two-byte columns, 128-byte swizzle
 constexpr int kOutStageBytes = kEpiWarps * kOutBufBytes;
 constexpr int kSmemBytes = kStages * kStageBytes + kOutStageBytes + kCtrlBytes + 1024;
-static_assert((2 * kStages + 2 * kAccBufs) * 8 + 12 <= kCtrlBytes, "control block");
+static_assert((2 * kStages + 2 * kAccBufs + 8) * 8 + 12 <= kCtrlBytes, "control block");
 static_assert(kSmemBytes <= 227 * 1024, "shared memory per CTA");
 
 // 384 threads x 168 registers fill the register file; 128 threads give up 128 each, 256 threads take 64 each.
@@ -137,7 +139,12 @@ __device__ __forceinline__ TileRef locate_tile(int t, int mtiles, const GemmPara
   }
 }
 
-template <bool kGrouped>
+// kSwiglu (grouped only): the weights' rows alternate 128 gate rows and 128 up rows, so the tile's two column halves
+// are gate and up of the same 128 outputs; the epilogue rounds both to the 16-bit type the reference's
+// intermediate has, forms silu(gate) * up, rounds again, quantises to e4m3 (scale 1, or amax / 448 over the 128
+// outputs a thread holds for its row) and stores e4m3 rows and scales: the first GEMM of a mixture-of-experts
+// layer with src/tilegym/ops/moe_interface.py:262-279 in its epilogue.
+template <bool kGrouped, bool kSwiglu = false>
 __global__ void __launch_bounds__(kThreads, 1)
     tg_fp8_gemm_blockscaled_wide_kernel(const __grid_constant__ CUtensorMap tmA,
                                         const __grid_constant__ CUtensorMap tmB,
@@ -155,7 +162,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t bar_empty = bar_full + 8 * S;
   const uint32_t bar_tfull = bar_empty + 8 * S;
   const uint32_t bar_tempty = bar_tfull + 8 * kAccBufs;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + (2 * S + 2 * kAccBufs) * 8);
+  const uint32_t bar_xfull = bar_tempty + 8 * kAccBufs;  // 4 + 4: gate / up exchange of the SiLU * mul epilogue,
+  const uint32_t bar_xfree = bar_xfull + 8 * 4;          // one pair of barriers per row quadrant
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + (2 * S + 2 * kAccBufs + 8) * 8);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -170,6 +179,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int i = 0; i < kAccBufs; ++i) {
       mbar_init(bar_tfull + 8 * i, 1);
       mbar_init(bar_tempty + 8 * i, kEpiWarps);
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(bar_xfull + 8 * i, 1);
+      mbar_init(bar_xfree + 8 * i, 1);
     }
     init_abort_flag(abort_flag, p.wait_limit_us);
     fence_mbar_init();
@@ -286,6 +299,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint32_t aph = 0;
     bool ok = true;
     [[maybe_unused]] int eit = 0;
+    [[maybe_unused]] uint32_t xph = 0;  // phase of the gate / up exchange barriers
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       const TileRef tile = locate_tile<kGrouped>(t, mtiles, p, lane);
       if (!tile.valid) continue;
@@ -348,6 +362,104 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
       if (!ok) break;
+      if constexpr (kSwiglu) {
+        // The up warp (half 1) of a row quadrant hands its 128 values, rounded to 16 bits, to the gate warp (half 0)
+        // through its staging buffer, 64 columns at a time (two bounded barriers per round: filled / drained).
+        const bool bf = p.out_dtype == TG_BF16;
+        uint8_t* xchg = out_stage + (q + 4) * kOutBufBytes;  // the up warp's buffer; 128-byte rows, swizzled
+        uint8_t* xrow = xchg + lane * 128;
+        float* acc = reinterpret_cast<float*>(acc2);
+#pragma unroll
+        for (int r = 0; r < 2 && ok; ++r) {
+          if (half == 1) {
+            // the gate warp has read the previous round out of the buffer
+            if (!__all_sync(0xffffffffu, mbar_wait(bar_xfree + 8 * q, xph ^ 1u, abort_flag))) {
+              report_timeout(p.status, kRoleEpilogue * 1000 + 52);
+              ok = false;
+              break;
+            }
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              const float* v = acc + r * 64 + g * 8;
+              const uint4 o = bf ? make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                                              pack_bf16x2(v[6], v[7]))
+                                 : make_uint4(pack_f16x2(v[0], v[1]), pack_f16x2(v[2], v[3]), pack_f16x2(v[4], v[5]),
+                                              pack_f16x2(v[6], v[7]));
+              *reinterpret_cast<uint4*>(xrow + ((g ^ (lane & 7)) << 4)) = o;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_xfull + 8 * q);  // release: the rows are in shared memory
+          } else {
+            if (!__all_sync(0xffffffffu, mbar_wait(bar_xfull + 8 * q, xph, abort_flag))) {
+              report_timeout(p.status, kRoleEpilogue * 1000 + 53);
+              ok = false;
+              break;
+            }
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              const uint4 u4 = *reinterpret_cast<const uint4*>(xrow + ((g ^ (lane & 7)) << 4));
+              const uint32_t uw[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float* a = acc + r * 64 + g * 8 + 2 * j;
+                float u0, u1, g0, g1;
+                if (bf) {
+                  u0 = __uint_as_float(uw[j] << 16);
+                  u1 = __uint_as_float(uw[j] & 0xffff0000u);
+                  g0 = __bfloat162float(__float2bfloat16_rn(a[0]));
+                  g1 = __bfloat162float(__float2bfloat16_rn(a[1]));
+                } else {
+                  const float2 uf = __half22float2(*reinterpret_cast<const __half2*>(&uw[j]));
+                  u0 = uf.x;
+                  u1 = uf.y;
+                  g0 = __half2float(__float2half_rn(a[0]));
+                  g1 = __half2float(__float2half_rn(a[1]));
+                }
+                const float y0 = __fdividef(g0, 1.0f + __expf(-g0)) * u0;
+                const float y1 = __fdividef(g1, 1.0f + __expf(-g1)) * u1;
+                a[0] = bf ? __bfloat162float(__float2bfloat16_rn(y0)) : __half2float(__float2half_rn(y0));
+                a[1] = bf ? __bfloat162float(__float2bfloat16_rn(y1)) : __half2float(__float2half_rn(y1));
+              }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_xfree + 8 * q);  // the buffer may be refilled
+          }
+          xph ^= 1u;
+        }
+        if (!ok) break;
+        if (half == 0 && row < tile.row_end) {
+          // this thread now holds the 128 outputs of its row: quantise and store one 128-byte line
+          float scale = 1.0f;
+          if (p.quant_mode == 1) {
+            float amax = 0.f;
+#pragma unroll
+            for (int j = 0; j < 128; ++j) amax = fmaxf(amax, fabsf(acc[j]));
+            scale = __fdiv_rn(amax, 448.0f);
+            if (scale == 0.f) scale = 1.0f;
+          }
+          const int out_col = tile.col0 >> 1;  // 128 outputs per 256-column tile
+          uint8_t* dst = reinterpret_cast<uint8_t*>(p.C) + row * p.ldc + out_col;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float v[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                v[i] = acc[g * 16 + j * 4 + i];
+                if (p.quant_mode == 1) v[i] = __fdiv_rn(v[i], scale);
+              }
+              const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[0], v[1]), __NV_SATFINITE, __NV_E4M3);
+              const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[2], v[3]), __NV_SATFINITE, __NV_E4M3);
+              w[j] = lo | (hi << 16);
+            }
+            *reinterpret_cast<uint4*>(dst + g * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          p.y_scale[row * (p.N >> 8) + (tile.col0 >> 8)] = scale;
+        }
+        continue;
+      }
       const int row0 = tile.row0 + q * 32;
       if (kGrouped && p.row_scale != nullptr) {  // e.g. the routing weight of a mixture-of-experts row
         const float w = row < tile.row_end ? __ldg(p.row_scale + row) : 0.f;
@@ -451,6 +563,31 @@ cudaError_t launch_wide(const CUtensorMap& tmA, const CUtensorMap& tmB, const CU
 cudaError_t launch_gemm_blockscaled_wide(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap* tmC,
                                          const GemmParams& p, int num_sms, cudaStream_t stream) {
   return launch_wide<false>(tmA, tmB, tmC, p, p.tiles_m * p.tiles_n, num_sms, stream);
+}
+
+cudaError_t launch_gemm_blockscaled_grouped_swiglu(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
+                                                   int num_sms, cudaStream_t stream) {
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(tg_fp8_gemm_blockscaled_wide_kernel<true, true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  const int tiles = p.mtile_bound * p.tiles_n;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(tiles < num_sms ? tiles : num_sms), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (p.flags & 2) ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, tg_fp8_gemm_blockscaled_wide_kernel<true, true>, tmA, tmB, tmA, p, 0);
 }
 
 // Grouped problem: p.M = total rows, p.m_indptr / num_groups / mtile_bound set, tmB maps B as [G * N, K].

@@ -42,6 +42,11 @@ struct GemmParams {
   int32_t num_groups;
   int32_t mtile_bound;  // ceil(M / 128) + num_groups >= the number of 128-row tiles of all groups
   const float* row_scale;  // grouped GEMM: nullptr, or one factor per row of C applied before bias and rounding
+  // grouped GEMM with the SiLU * mul + quantise epilogue (first GEMM of a mixture-of-experts layer): C is the e4m3
+  // output [M, N / 2] (ldc in bytes = elements), out_dtype the 16-bit type the reference rounds to on the way,
+  // y_scale its [M, N / 256] scales, quant_mode 0 (scale 1) or 1 (amax / 448 per 128 outputs)
+  float* y_scale;
+  int32_t quant_mode;
   // diagnostics
   int32_t* status;         // device status word
   uint32_t wait_limit_us;  // bound of every device-side wait in microseconds (0 = the 2 s default)
@@ -77,6 +82,10 @@ cudaError_t launch_gemm_blockscaled_wide(const CUtensorMap& tmA, const CUtensorM
 // tmB maps B [G, N, K] as [G * N, K] with 256-row boxes.
 cudaError_t launch_gemm_blockscaled_grouped(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap* tmC,
                                             const GemmParams& p, int num_sms, cudaStream_t stream);
+// The same with the SiLU * mul + quantise epilogue: the weights' rows alternate 128 gate rows and 128 up rows, so
+// every 128 x 256 tile holds gate and up of 128 outputs; p.C / p.y_scale / p.quant_mode describe the e4m3 output.
+cudaError_t launch_gemm_blockscaled_grouped_swiglu(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
+                                                   int num_sms, cudaStream_t stream);
 // Swap-AB block-scaled kernel for M <= 128: tmW boxes 128 weight rows, tmX boxes `mp` (32 / 64 / 128) activation
 // rows; p.tiles_n counts 128-row weight tiles, the p.splits (1..8) K splits of a tile form a cluster, and every
 // split owns at most blockscaled_smallm_max_kb_per_cta() k-blocks.  No beta.

@@ -103,6 +103,7 @@ def fused_experts_impl(
     w2_scale: Optional[torch.Tensor] = None,
     a1_scale: Optional[torch.Tensor] = None,
     a2_quant: str = "ones",
+    w1_interleaved: bool = False,
 ) -> torch.Tensor:
     """out[t] = sum_j topk_weights[t, j] * w2[e] . (silu(gate) * up),  [gate | up] = w1[e] . x[t],  e = topk_ids[t, j].
 
@@ -112,7 +113,10 @@ def fused_experts_impl(
     e4m3 with w2_scale (E, H / 128, I / 128).  Like the reference the result is float16 for e4m3 (or f16)
     hidden_states and bfloat16 for bf16 ones, the first GEMM's output and silu * mul are rounded to that
     type, and the intermediate is cast to e4m3 with scale 1 (`a2_quant="ones"`, moe_interface.py:269-279);
-    `a2_quant="block"` quantises it per 1 x 128 with amax / 448 instead, which keeps more of its range."""
+    `a2_quant="block"` quantises it per 1 x 128 with amax / 448 instead, which keeps more of its range.
+    `w1_interleaved=True` says that w1 / w1_scale were rearranged by `interleave_gate_up_blocks` (128 gate rows,
+    128 up rows, alternating): the first GEMM then applies silu * mul and the quantisation in its epilogue and
+    the [rows, 2 I] intermediate is never written."""
     if use_int8_w8a16:
         raise NotImplementedError("tilegym_b200.fused_experts_impl implements the FP8 W8A8 path only (no int8 weights)")
     if not use_fp8_w8a8 or w1_scale is None or w2_scale is None:
@@ -151,17 +155,37 @@ def fused_experts_impl(
     as_sorted = torch.empty((R, H // 128), dtype=torch.float32, device=dev)
     _lib.check_rc(L.tg_moe_permute_rows(_lib.desc(a_sorted), _lib.desc(as_sorted), _lib.desc(a8), _lib.desc(a_s),
                                         sorted_ids.data_ptr(), m_indptr.data_ptr(), E, topk, dev.index, stream))
-    # fc1 on contiguous expert segments: [rows, 2 I] in the 16-bit type
-    c1 = ops.ragged_block_scaled_bmm(a_sorted, w1, as_sorted, w1_scale, m_indptr, R, out_dtype=out_dtype)
     y8 = torch.empty((R, inter), dtype=_FP8, device=dev)
     y_s = torch.empty((R, inter // 128), dtype=torch.float32, device=dev)
-    _lib.check_rc(L.tg_moe_silu_mul_quant(_lib.desc(y8), _lib.desc(y_s), _lib.desc(c1), m_indptr.data_ptr(), E,
-                                          1 if a2_quant == "block" else 0, dev.index, stream))
+    mode = 1 if a2_quant == "block" else 0
+    if w1_interleaved:
+        # fc1 with silu * mul and the quantisation in its epilogue
+        _lib.check_rc(L.tg_fp8_gemm_blockscaled_grouped_swiglu(
+            _lib.desc(y8), _lib.desc(y_s), _lib.desc(a_sorted), _lib.desc(w1), _lib.desc(as_sorted), _lib.desc(w1_scale),
+            m_indptr.data_ptr(), _lib.DTYPE_CODES[out_dtype], mode, dev.index, stream))
+    else:
+        # fc1 on contiguous expert segments: [rows, 2 I] in the 16-bit type, then silu * mul + quantise
+        c1 = ops.ragged_block_scaled_bmm(a_sorted, w1, as_sorted, w1_scale, m_indptr, R, out_dtype=out_dtype)
+        _lib.check_rc(L.tg_moe_silu_mul_quant(_lib.desc(y8), _lib.desc(y_s), _lib.desc(c1), m_indptr.data_ptr(), E,
+                                              mode, dev.index, stream))
     # fc2, routing weight applied to the fp32 sums before the rounding
     c3 = ops.ragged_block_scaled_bmm(y8, w2, y_s, w2_scale, m_indptr, R, out_dtype=out_dtype, row_scale=w_sorted)
     out = hidden_states if (inplace and hidden_states.dtype == out_dtype) else torch.empty((T, H), dtype=out_dtype, device=dev)
     _lib.check_rc(L.tg_moe_unpermute_sum(_lib.desc(out), _lib.desc(c3), pos.data_ptr(), topk, dev.index, stream))
     return out
+
+
+def interleave_gate_up_blocks(w1: torch.Tensor, w1_scale: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Rearranges a fused gate / up weight (E, 2 I, H) = [gate rows | up rows] and its 128 x 128 scales
+    (E, 2 I / 128, H / 128) into the order the fused first GEMM reads: 128 gate rows, the 128 up rows of the same
+    outputs, the next 128 gate rows, ...  Done once, at load time."""
+    E, n2, H = w1.shape
+    inter = n2 // 2
+    assert inter % 128 == 0
+    w = w1.view(torch.uint8) if w1.dtype == _FP8 else w1
+    w = w.reshape(E, 2, inter // 128, 128, H).transpose(1, 2).reshape(E, n2, H).contiguous()
+    sc = w1_scale.reshape(E, 2, inter // 128, -1).transpose(1, 2).reshape(E, n2 // 128, -1).contiguous()
+    return (w.view(_FP8) if w1.dtype == _FP8 else w), sc
 
 
 def fused_moe(
@@ -188,6 +212,7 @@ class FP8MoE(torch.nn.Module):
 
     def __init__(self, w1_fp8, w1_scale, w2_fp8, w2_scale, a2_quant: str = "block"):
         super().__init__()
+        w1_fp8, w1_scale = interleave_gate_up_blocks(w1_fp8, w1_scale)  # silu * mul runs in the first GEMM's epilogue
         self.register_buffer("w1", w1_fp8)
         self.register_buffer("w1_scale", w1_scale)
         self.register_buffer("w2", w2_fp8)
@@ -207,5 +232,5 @@ class FP8MoE(torch.nn.Module):
         x = hidden_states.reshape(-1, shape[-1]).contiguous()
         out = fused_experts_impl(x, self.w1, self.w2, topk_weights.reshape(x.shape[0], -1),
                                  topk_ids.reshape(x.shape[0], -1), use_fp8_w8a8=True, w1_scale=self.w1_scale,
-                                 w2_scale=self.w2_scale, a2_quant=self.a2_quant)
+                                 w2_scale=self.w2_scale, a2_quant=self.a2_quant, w1_interleaved=True)
         return out.reshape(shape)
