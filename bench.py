@@ -584,6 +584,25 @@ def run_one(args):
         print(json.dumps({"one": args.one, "us_per_launch": sec / args.steps * 1e6,
                           "tflops": 2.0 * M * N * K * args.steps / sec / 1e12}), flush=True)
         return
+    if kind == "moe":
+        # one FP8 mixture-of-experts layer: M tokens, hidden N, intermediate K, 64 experts, top-6
+        from tilegym_b200 import moe
+
+        E, topk = 64, 6
+        x = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
+        w1 = torch.randn(E, 2 * K, N, device=dev, dtype=torch.bfloat16).mul_(0.05).to(torch.float8_e4m3fn)
+        w2 = torch.randn(E, N, K, device=dev, dtype=torch.bfloat16).mul_(0.05).to(torch.float8_e4m3fn)
+        w1s = torch.rand(E, 2 * K // 128, N // 128, device=dev) + 0.5
+        w2s = torch.rand(E, N // 128, K // 128, device=dev) + 0.5
+        ids = torch.randint(0, E, (M, topk), device=dev)
+        wts = torch.softmax(torch.randn(M, topk, device=dev), dim=-1)
+        w1i, w1si = moe.interleave_gate_up_blocks(w1, w1s)
+        fn = lambda: moe.fused_experts_impl(x, w1i, w2, wts, ids, use_fp8_w8a8=True, w1_scale=w1si, w2_scale=w2s,  # noqa: E731
+                                            a2_quant="block", w1_interleaved=True)
+        sec = timed(fn, args.steps, args.warmup, dev)
+        print(json.dumps({"one": args.one, "us_per_call": sec / args.steps * 1e6,
+                          "tflops": 2.0 * M * topk * 3 * K * N * args.steps / sec / 1e12}), flush=True)
+        return
     a8, b8, sa, sb = make_case(M, N, K, dev, 1)
     if kind == "swiglu":
         out = torch.empty(M, N // 2, dtype=torch.bfloat16, device=dev)
@@ -596,7 +615,7 @@ def run_one(args):
         Bs = torch.rand((N + 127) // 128, (K + 127) // 128, device=dev) + 0.5
         fn = lambda: tg.w8a8_block_fp8_matmul(a8, b8, As, Bs, [128, 128], torch.bfloat16)  # noqa: E731
     else:
-        raise SystemExit("--one KIND must be pertensor, swiglu, blockscaled, grouped, actquant, groupquant, quantpt or dequant")
+        raise SystemExit("--one KIND must be pertensor, swiglu, blockscaled, grouped, moe, actquant, groupquant, quantpt or dequant")
     sec = timed(fn, args.steps, args.warmup, dev)
     print(json.dumps({"one": args.one, "us_per_launch": sec / args.steps * 1e6,
                       "tflops": 2.0 * M * N * K * args.steps / sec / 1e12,
@@ -618,8 +637,8 @@ def main():
     ap.add_argument("--chunks", type=int, default=8, help="N>1: M-slabs whose all-gather overlaps the next slab's GEMM")
     ap.add_argument("--one", default=None, metavar="KIND:M,N,K",
                     help="profiling aid: run one kernel steps+warmup times. GEMMs pertensor / swiglu / blockscaled / "
-                         "grouped (M rows in 8 groups); quantisers actquant / groupquant (K = group size) / quantpt / "
-                         "dequant on an M x N tensor")
+                         "grouped (M rows in 8 groups); moe (M tokens, hidden N, intermediate K, 64 experts, top-6); "
+                         "quantisers actquant / groupquant (K = group size) / quantpt / dequant on an M x N tensor")
     args = ap.parse_args()
     if args.one:
         run_one(args)
