@@ -217,6 +217,18 @@ TG_API int32_t tg_fp8_gemm_pertensor_allgather(const TgTensorDesc* C, const TgTe
                                                const TgTensorDesc* bias, const uint64_t* peer_ptrs,
                                                int32_t num_peers, int32_t device_id, uint64_t stream);
 
+/* Column-parallel GEMM followed by an NCCL all-gather of the output slabs (multi-GPU, one process per GPU): this
+ * rank computes its slab C_all[rank] = alpha*sa*sb*(A . B_shard^T) + bias_shard and ncclAllGather fills the other
+ * ranks' slabs, in place, on the same stream.  C_all: contiguous (world, M, n) f32 / f16 / bf16; logical element
+ * C[m, g*n + j] is C_all[g, m, j].  comm: the caller's ncclComm_t (as an integer); the library resolves
+ * ncclAllGather at run time from the NCCL the process has loaded, so it has no link-time dependency on NCCL.
+ * workspace as for tg_fp8_gemm_pertensor.  The reference is single-GPU; there is no counterpart.  (The fused
+ * entry above overlaps the transfer with the GEMM; this one is the plain library collective.) */
+TG_API int32_t tg_shard_gemm_allgather(const TgTensorDesc* C_all, const TgTensorDesc* A, const TgTensorDesc* B_shard,
+                                       uint64_t scale_a, uint64_t scale_b, float alpha, const TgTensorDesc* bias_shard,
+                                       int32_t rank, int32_t world, uint64_t comm, uint64_t workspace,
+                                       uint64_t workspace_bytes, int32_t device_id, uint64_t stream);
+
 /* The small-M (M <= 64) path of tg_fp8_gemm_pertensor for callers that cannot
  * allocate device memory - a server whose pool already owns the GPU, or a
  * decode loop that must never reach cudaMalloc / cudaFree because they

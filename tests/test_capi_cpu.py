@@ -109,6 +109,24 @@ def test_grouped_blockscaled_argument_checks():
                 sa=torch.zeros(0, 2)) == 0  # nothing to do, no device needed
 
 
+def test_shard_gemm_allgather_argument_checks():
+    L = _lib.lib()
+    a = torch.zeros(128, 128, dtype=torch.float8_e4m3fn)
+    c = torch.zeros(2, 128, 128, dtype=torch.bfloat16)
+
+    def call(C=c, rank=0, world=2, comm=1):
+        return L.tg_shard_gemm_allgather(_d(C), _d(a), _d(a), 0, 0, 1.0, None, rank, world, comm, 0, 0, 0, 0)
+
+    assert call(rank=2) == -6
+    assert call(world=3) == -6                      # C_all's first extent is the world size
+    assert call(C=c[:, :, :64]) == -6               # NCCL gathers contiguous slabs
+    assert call(comm=0) == -5
+    assert call(C=c.to(torch.int32)) == -2
+    e = torch.zeros(0, 128, dtype=torch.float8_e4m3fn)
+    assert L.tg_shard_gemm_allgather(_d(torch.zeros(2, 0, 128, dtype=torch.bfloat16)), _d(e), _d(a), 0, 0, 1.0, None,
+                                     1, 2, 1, 0, 0, 0, 0) == 0  # nothing to do, no device or NCCL needed
+
+
 def test_moe_argument_checks():
     L = _lib.lib()
     ids = torch.zeros(8, 2, dtype=torch.int64)

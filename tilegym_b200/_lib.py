@@ -85,6 +85,11 @@ SIGNATURES = {
         [_P, _P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_float, _P, ctypes.POINTER(ctypes.c_uint64),
          ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64],
     ),
+    "tg_shard_gemm_allgather": (
+        ctypes.c_int32,
+        [_P, _P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_float, _P, ctypes.c_int32, ctypes.c_int32,
+         ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int32, ctypes.c_uint64],
+    ),
     "tg_fp8_gemm_pertensor_smallm_static": (
         ctypes.c_int32,
         [_P, _P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_float, _P, ctypes.c_float, ctypes.c_int32,

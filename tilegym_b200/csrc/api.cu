@@ -7,6 +7,8 @@
 #include <cstdlib>
 #include <cstring>
 
+#include <dlfcn.h>
+
 #include "tg_internal.h"
 
 namespace tg {
@@ -630,6 +632,59 @@ int32_t tg_fp8_gemm_pertensor_allgather(const TgTensorDesc* C, const TgTensorDes
     if (peer_ptrs[i] & 15u) return fail(TG_ERR_ALIGN, "peer pointer %d is not 16-byte aligned", i);
   }
   return pertensor_impl(C, A, B, scale_a, scale_b, alpha, bias, 0.0f, 0, 0, peer_ptrs, num_peers, device_id, stream);
+}
+
+// ncclAllGather of the NCCL library the process already uses (torch's, or whatever the caller linked), resolved at
+// run time so that this library has no link-time dependency on NCCL.
+typedef int (*NcclAllGatherFn)(const void*, void*, size_t, int, void*, cudaStream_t);
+static NcclAllGatherFn resolve_nccl_allgather() {
+  static NcclAllGatherFn fn = nullptr;
+  static bool tried = false;
+  if (tried) return fn;
+  tried = true;
+  void* sym = dlsym(RTLD_DEFAULT, "ncclAllGather");
+  if (sym == nullptr) {
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);  // already loaded under that name (e.g. by torch)?
+    if (h == nullptr) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (h != nullptr) sym = dlsym(h, "ncclAllGather");
+  }
+  fn = reinterpret_cast<NcclAllGatherFn>(sym);
+  return fn;
+}
+
+int32_t tg_shard_gemm_allgather(const TgTensorDesc* C_all, const TgTensorDesc* A, const TgTensorDesc* B_shard,
+                                uint64_t scale_a, uint64_t scale_b, float alpha, const TgTensorDesc* bias_shard,
+                                int32_t rank, int32_t world, uint64_t comm, uint64_t workspace,
+                                uint64_t workspace_bytes, int32_t device_id, uint64_t stream) {
+  if (C_all == nullptr || A == nullptr || B_shard == nullptr) return fail(TG_ERR_NULL, "a descriptor is null");
+  if (world < 1 || rank < 0 || rank >= world) return fail(TG_ERR_ARGS, "rank %d of %d is out of range", rank, world);
+  if (C_all->ndim != 3 || C_all->shape[0] != world) return fail(TG_ERR_ARGS, "C_all must be [world, M, n]");
+  if (!is_out_dtype(C_all->dtype)) return fail(TG_ERR_DTYPE, "C_all must be f32, f16 or bf16");
+  const int64_t M = C_all->shape[1], n = C_all->shape[2];
+  if (M > 0 && n > 0 && (C_all->strides[2] != 1 || C_all->strides[1] != n || C_all->strides[0] != M * n))
+    return fail(TG_ERR_ARGS, "C_all must be contiguous (NCCL gathers contiguous slabs)");
+  if (world > 1 && comm == 0) return fail(TG_ERR_NULL, "comm (ncclComm_t) is null");
+  TgTensorDesc slab;
+  memset(&slab, 0, sizeof(slab));
+  slab.ptr = C_all->ptr + static_cast<uint64_t>(rank) * M * n * esize(C_all->dtype);
+  slab.ndim = 2;
+  slab.shape[0] = M;
+  slab.shape[1] = n;
+  slab.strides[0] = n;
+  slab.strides[1] = 1;
+  slab.dtype = C_all->dtype;
+  int32_t rc = pertensor_impl(&slab, A, B_shard, scale_a, scale_b, alpha, bias_shard, 0.0f, workspace, workspace_bytes,
+                              nullptr, 0, device_id, stream);
+  if (rc != TG_OK || world == 1 || M == 0 || n == 0) return rc;
+  NcclAllGatherFn gather = resolve_nccl_allgather();
+  if (gather == nullptr) return fail(TG_ERR_DEVICE, "ncclAllGather not found: no libnccl.so.2 is loaded or loadable in this process");
+  const int nccl_dtype = C_all->dtype == TG_BF16 ? 9 : (C_all->dtype == TG_F16 ? 6 : 7);  // ncclBfloat16 / Float16 / Float32
+  DeviceGuard guard(device_id);
+  const int r = gather(reinterpret_cast<const void*>(slab.ptr), reinterpret_cast<void*>(C_all->ptr),
+                       static_cast<size_t>(M) * static_cast<size_t>(n), nccl_dtype, reinterpret_cast<void*>(comm),
+                       reinterpret_cast<cudaStream_t>(stream));
+  if (r != 0) return fail(TG_ERR_LAUNCH, "ncclAllGather failed with ncclResult_t %d", r);
+  return TG_OK;
 }
 
 int32_t tg_fp8_gemm_pertensor_swiglu(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
