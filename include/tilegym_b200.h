@@ -330,6 +330,14 @@ TG_API uint32_t tg_set_wait_limit_us(uint32_t limit_us);
  * usable.  No reference counterpart. */
 TG_API int32_t tg_selftest_wait_timeout(uint32_t limit_us, int32_t device_id, uint64_t stream);
 
+/* Self-test of the quantisers' arithmetic: compares their division-free quotient and scale with IEEE division for
+ * every (group maximum, element) pair a 16-bit input type (x_dtype: TG_BF16 / TG_F16) can produce, for the target
+ * format y_dtype (TG_F8E4M3 / TG_F8E5M2 / TG_I8).  counts: four 64-bit words on the device, filled on the stream
+ * with {pairs whose bytes differ, pairs compared, scales that differ, maxima outside the fast path's range}; the
+ * first and third must be 0.  A few milliseconds.  The reference has no counterpart. */
+TG_API int32_t tg_selftest_quant16(int32_t x_dtype, int32_t y_dtype, uint64_t counts, int32_t device_id,
+                                   uint64_t stream);
+
 /* Reads (and clears) the device-side status word of `device_id` after
  * synchronising the device: 0, or TG_ERR_TIMEOUT with *detail set to a code
  * naming the wait that gave up.  detail may be NULL. */

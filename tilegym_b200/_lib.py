@@ -148,6 +148,7 @@ SIGNATURES = {
     "tg_reload_env": (None, []),
     "tg_set_wait_limit_us": (ctypes.c_uint32, [ctypes.c_uint32]),
     "tg_selftest_wait_timeout": (ctypes.c_int32, [ctypes.c_uint32, ctypes.c_int32, ctypes.c_uint64]),
+    "tg_selftest_quant16": (ctypes.c_int32, [ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64, ctypes.c_int32, ctypes.c_uint64]),
 }
 
 

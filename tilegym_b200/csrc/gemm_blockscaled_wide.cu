@@ -15,6 +15,7 @@
 #include <cuda_fp8.h>
 
 #include "tg_gemm_common.cuh"
+#include "tg_quant_common.cuh"
 
 namespace tg {
 
@@ -437,6 +438,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             scale = __fdiv_rn(amax, 448.0f);
             if (scale == 0.f) scale = 1.0f;
           }
+          // the outputs are 16-bit values and the scale is RN(16-bit amax / 448): the test-free quotient applies
+          const bool fast = p.quant_mode == 1 && q8_scale_is_tame(scale);
+          const float rcp = __frcp_rn(scale);
           const int out_col = tile.col0 >> 1;  // 128 outputs per 256-column tile
           uint8_t* dst = reinterpret_cast<uint8_t*>(p.C) + row * p.ldc + out_col;
 #pragma unroll
@@ -446,9 +450,14 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int j = 0; j < 4; ++j) {
               float v[4];
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                v[i] = acc[g * 16 + j * 4 + i];
-                if (p.quant_mode == 1) v[i] = __fdiv_rn(v[i], scale);
+              for (int i = 0; i < 4; ++i) v[i] = acc[g * 16 + j * 4 + i];
+              if (fast) {
+                const float2 q0 = q8_quot2(make_float2(v[0], v[1]), scale, rcp);
+                const float2 q1 = q8_quot2(make_float2(v[2], v[3]), scale, rcp);
+                v[0] = q0.x; v[1] = q0.y; v[2] = q1.x; v[3] = q1.y;
+              } else if (p.quant_mode == 1) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) v[i] = __fdiv_rn(v[i], scale);
               }
               const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[0], v[1]), __NV_SATFINITE, __NV_E4M3);
               const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[2], v[3]), __NV_SATFINITE, __NV_E4M3);

@@ -50,15 +50,6 @@ __device__ __forceinline__ void load_elems(const T* src, float (&v)[EPT]) {
   }
 }
 
-// Smallest power of two >= max(|s|, 1e-10): ceil(log2) read off the exponent and mantissa bits, so the
-// result does not depend on a log2 implementation.
-__device__ __forceinline__ float round_up_pow2(float s) {
-  s = fmaxf(fabsf(s), 1e-10f);
-  const uint32_t b = __float_as_uint(s);
-  const uint32_t exp_bits = (b & 0x7f800000u) + ((b & 0x007fffffu) ? 0x00800000u : 0u);
-  return __uint_as_float(exp_bits);
-}
-
 // Where group g's scale goes: row g / groups_per_row, column g % groups_per_row, through the caller's strides.
 // 64-bit division costs a few hundred instructions, so the common sizes take a 32-bit one.
 __device__ __forceinline__ int64_t scale_index(int64_t g, int64_t groups_per_row, int64_t row_stride,
@@ -73,15 +64,37 @@ __device__ __forceinline__ int64_t scale_index(int64_t g, int64_t groups_per_row
   return row * row_stride + (g - row * groups_per_row) * group_stride;
 }
 
+// |x| maximum of two packed 16-bit pairs, element-wise (NaN operands are ignored, like fmaxf).
+template <typename T>
+__device__ __forceinline__ uint32_t absmax_pairs(uint32_t a, uint32_t b) {
+  if constexpr (std::is_same<T, __half>::value) {
+    const __half2 m = __hmax2(__habs2(*reinterpret_cast<const __half2*>(&a)), __habs2(*reinterpret_cast<const __half2*>(&b)));
+    return *reinterpret_cast<const uint32_t*>(&m);
+  } else {
+    const __nv_bfloat162 m = __hmax2(__habs2(*reinterpret_cast<const __nv_bfloat162*>(&a)),
+                                     __habs2(*reinterpret_cast<const __nv_bfloat162*>(&b)));
+    return *reinterpret_cast<const uint32_t*>(&m);
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ float2 unpack_pair(uint32_t w) {
+  if constexpr (std::is_same<T, __half>::value) return __half22float2(*reinterpret_cast<const __half2*>(&w));
+  else return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));  // bf16 -> fp32 is a shift
+}
+
 // A thread owns a chunk of EPT consecutive elements; the `tpg` = group_size / EPT lanes (a power of two, at
 // most 32) that share a group sit next to each other in a warp.  `zero_to_one` selects the 1 x 128 activation
-// quantiser's rule (scale 1.0 for an all-zero group, no eps).
+// quantiser's rule (scale 1.0 for an all-zero group, no eps).  16-bit inputs stay packed for the |x| maximum and
+// take the test-free quotient of tg_quant_common.cuh (its precondition - a scale that is RN(amax / qmax) of a
+// 16-bit amax, or a power of two - fails only where eps replaces the maximum; those groups and fp32 inputs go
+// through the guarded reciprocal).  `dense_scales`: S is contiguous row-major, so group g's scale is s[g].
 template <typename T, int KIND, int EPT>
 __global__ void __launch_bounds__(256)
     tg_per_token_group_quant_kernel(uint8_t* __restrict__ y, float* __restrict__ s, const T* __restrict__ x,
                                     int64_t n_chunks, int tpg, int64_t groups_per_row, int64_t s_row_stride,
-                                    int64_t s_group_stride, float eps, float qmin, float qmax, int ue8m0,
-                                    int zero_to_one) {
+                                    int64_t s_group_stride, float eps, float qmin, float qmax, float qmax_rcp,
+                                    int ue8m0, int zero_to_one, int dense_scales) {
   const int lane = threadIdx.x & 31;
   const int tpg_shift = 31 - __clz(tpg);
   const int64_t span = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -90,35 +103,82 @@ __global__ void __launch_bounds__(256)
        base += span) {
     const int64_t c = base + lane;
     const bool live = c < n_chunks;
-    float v[EPT];
-#pragma unroll
-    for (int j = 0; j < EPT; ++j) v[j] = 0.f;
-    if (live) load_elems<T, EPT>(x + c * EPT, v);
-    float amax = 0.f;
-#pragma unroll
-    for (int j = 0; j < EPT; ++j) amax = fmaxf(amax, fabsf(v[j]));
-    for (int o = tpg >> 1; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    float scale;
-    if (zero_to_one) {
-      scale = __fdiv_rn(amax, qmax);
-      if (scale == 0.f) scale = 1.0f;
-    } else {
-      scale = __fdiv_rn(fmaxf(amax, eps), qmax);
-      if (ue8m0) scale = round_up_pow2(scale);
-    }
-    const bool tame = q8_scale_is_tame(scale);
-    const float r = __frcp_rn(scale);
     uint32_t out[EPT / 4];
+    float scale;
+    if constexpr (sizeof(T) == 2) {
+      uint32_t w[EPT / 2];
 #pragma unroll
-    for (int w = 0; w < EPT / 4; ++w)
-      out[w] = q8_pair<KIND>(v[4 * w], v[4 * w + 1], scale, r, tame, qmin, qmax) |
-               (q8_pair<KIND>(v[4 * w + 2], v[4 * w + 3], scale, r, tame, qmin, qmax) << 16);
+      for (int j = 0; j < EPT / 2; ++j) w[j] = 0u;
+      if (live) {
+#pragma unroll
+        for (int i = 0; i < EPT / 8; ++i) {
+          const uint4 t = __ldcs(reinterpret_cast<const uint4*>(x + c * EPT) + i);
+          w[4 * i] = t.x; w[4 * i + 1] = t.y; w[4 * i + 2] = t.z; w[4 * i + 3] = t.w;
+        }
+      }
+      uint32_t m2 = absmax_pairs<T>(w[0], w[1]);
+#pragma unroll
+      for (int j = 2; j < EPT / 2; j += 2) m2 = absmax_pairs<T>(m2, absmax_pairs<T>(w[j], w[j + 1]));
+      const float2 mm = unpack_pair<T>(m2);
+      float amax = fmaxf(mm.x, mm.y);
+      for (int o = tpg >> 1; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      bool exact_form = true;  // is the scale RN(16-bit amax / qmax) or a power of two?
+      if (zero_to_one) {
+        scale = q8_scale_from_amax(amax, qmax, qmax_rcp);
+        if (scale == 0.f) scale = 1.0f;
+      } else {
+        exact_form = ue8m0 || amax >= eps;
+        scale = amax >= eps ? q8_scale_from_amax(amax, qmax, qmax_rcp) : __fdiv_rn(eps, qmax);
+        if (ue8m0) scale = round_up_pow2(scale);
+      }
+      const float r = __frcp_rn(scale);
+      if (q8_scale_is_tame(scale) && exact_form) {
+#pragma unroll
+        for (int k = 0; k < EPT / 4; ++k) {
+          const float2 q0 = q8_quot2(unpack_pair<T>(w[2 * k]), scale, r);
+          const float2 q1 = q8_quot2(unpack_pair<T>(w[2 * k + 1]), scale, r);
+          out[k] = q8_cast2<KIND>(q0.x, q0.y, qmin, qmax) | (q8_cast2<KIND>(q1.x, q1.y, qmin, qmax) << 16);
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < EPT / 4; ++k) {
+          const float2 x0 = unpack_pair<T>(w[2 * k]), x1 = unpack_pair<T>(w[2 * k + 1]);
+          out[k] = q8_pair<KIND>(x0.x, x0.y, scale, r, false, qmin, qmax) |
+                   (q8_pair<KIND>(x1.x, x1.y, scale, r, false, qmin, qmax) << 16);
+        }
+      }
+    } else {
+      float v[EPT];
+#pragma unroll
+      for (int j = 0; j < EPT; ++j) v[j] = 0.f;
+      if (live) load_elems<T, EPT>(x + c * EPT, v);
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < EPT; ++j) amax = fmaxf(amax, fabsf(v[j]));
+      for (int o = tpg >> 1; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      if (zero_to_one) {
+        scale = __fdiv_rn(amax, qmax);
+        if (scale == 0.f) scale = 1.0f;
+      } else {
+        scale = __fdiv_rn(fmaxf(amax, eps), qmax);
+        if (ue8m0) scale = round_up_pow2(scale);
+      }
+      const bool tame = q8_scale_is_tame(scale);
+      const float r = __frcp_rn(scale);
+#pragma unroll
+      for (int k = 0; k < EPT / 4; ++k)
+        out[k] = q8_pair<KIND>(v[4 * k], v[4 * k + 1], scale, r, tame, qmin, qmax) |
+                 (q8_pair<KIND>(v[4 * k + 2], v[4 * k + 3], scale, r, tame, qmin, qmax) << 16);
+    }
     if (live) {
       if constexpr (EPT == 16)
         __stcs(reinterpret_cast<uint4*>(y + c * EPT), make_uint4(out[0], out[1], out[2], out[3]));
       else
         __stcs(reinterpret_cast<uint2*>(y + c * EPT), make_uint2(out[0], out[1]));
-      if ((lane & (tpg - 1)) == 0) s[scale_index(c >> tpg_shift, groups_per_row, s_row_stride, s_group_stride)] = scale;
+      if ((lane & (tpg - 1)) == 0) {
+        const int64_t g = c >> tpg_shift;
+        s[dense_scales ? g : scale_index(g, groups_per_row, s_row_stride, s_group_stride)] = scale;
+      }
     }
   }
 }
@@ -127,6 +187,8 @@ template <typename T, int EPT>
 cudaError_t launch_kind(int kind, uint8_t* y, float* s, const T* x, int64_t n_chunks, int tpg, int64_t gpr,
                         int64_t srs, int64_t sgs, float eps, float qmin, float qmax, int ue8m0, int zero_to_one,
                         int num_sms, cudaStream_t stream) {
+  const float qmax_rcp = 1.0f / qmax;  // IEEE division on the host: RN(1 / qmax)
+  const int dense = (sgs == 1 && srs == gpr) || (gpr == 1 && srs == 1);
   const int threads = 256;
   int64_t blocks = (n_chunks + threads - 1) / threads;
   const int64_t cap = static_cast<int64_t>(num_sms) * 16;  // 8 resident CTAs per SM, two rounds
@@ -134,11 +196,11 @@ cudaError_t launch_kind(int kind, uint8_t* y, float* s, const T* x, int64_t n_ch
   if (blocks < 1) blocks = 1;
   const dim3 grid(static_cast<unsigned>(blocks));
   if (kind == kQ8E4M3)
-    tg_per_token_group_quant_kernel<T, kQ8E4M3, EPT><<<grid, threads, 0, stream>>>(y, s, x, n_chunks, tpg, gpr, srs, sgs, eps, qmin, qmax, ue8m0, zero_to_one);
+    tg_per_token_group_quant_kernel<T, kQ8E4M3, EPT><<<grid, threads, 0, stream>>>(y, s, x, n_chunks, tpg, gpr, srs, sgs, eps, qmin, qmax, qmax_rcp, ue8m0, zero_to_one, dense);
   else if (kind == kQ8E5M2)
-    tg_per_token_group_quant_kernel<T, kQ8E5M2, EPT><<<grid, threads, 0, stream>>>(y, s, x, n_chunks, tpg, gpr, srs, sgs, eps, qmin, qmax, ue8m0, zero_to_one);
+    tg_per_token_group_quant_kernel<T, kQ8E5M2, EPT><<<grid, threads, 0, stream>>>(y, s, x, n_chunks, tpg, gpr, srs, sgs, eps, qmin, qmax, qmax_rcp, ue8m0, zero_to_one, dense);
   else
-    tg_per_token_group_quant_kernel<T, kQ8Int8, EPT><<<grid, threads, 0, stream>>>(y, s, x, n_chunks, tpg, gpr, srs, sgs, eps, qmin, qmax, ue8m0, zero_to_one);
+    tg_per_token_group_quant_kernel<T, kQ8Int8, EPT><<<grid, threads, 0, stream>>>(y, s, x, n_chunks, tpg, gpr, srs, sgs, eps, qmin, qmax, qmax_rcp, ue8m0, zero_to_one, dense);
   return cudaGetLastError();
 }
 

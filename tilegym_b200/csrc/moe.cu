@@ -179,8 +179,14 @@ __global__ void __launch_bounds__(256) moe_silu_mul_quant_kernel(uint8_t* __rest
       for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
       scale = __fdiv_rn(amax, 448.0f);
       if (scale == 0.f) scale = 1.0f;
+      if (q8_scale_is_tame(scale)) {  // 16-bit values over RN(16-bit amax / 448): the test-free quotient applies
+        const float rcp = __frcp_rn(scale);
+        const float2 q0 = q8_quot2(make_float2(a[0], a[1]), scale, rcp), q1 = q8_quot2(make_float2(a[2], a[3]), scale, rcp);
+        a[0] = q0.x; a[1] = q0.y; a[2] = q1.x; a[3] = q1.y;
+      } else {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] = __fdiv_rn(a[i], scale);
+        for (int i = 0; i < 4; ++i) a[i] = __fdiv_rn(a[i], scale);
+      }
     }
     const uint32_t lo = q8_cast2<kQ8E4M3>(a[0], a[1], -448.f, 448.f);
     const uint32_t hi = q8_cast2<kQ8E4M3>(a[2], a[3], -448.f, 448.f);

@@ -8,6 +8,8 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
+#include <type_traits>
+
 #include "tg_internal.h"
 #include "tg_quant_common.cuh"
 
@@ -159,6 +161,46 @@ __global__ void __launch_bounds__(256) tg_quant_pertensor_kernel(uint8_t* __rest
   }
 }
 
+// The same pass for 16-bit inputs whose size and addresses allow 16 elements per thread (two 16-byte loads, one
+// 16-byte store): the tensor's scale is RN(amax / 448) of a 16-bit amax, which is the form the test-free quotient
+// of tg_quant_common.cuh is verified for.
+template <typename T>
+__global__ void __launch_bounds__(256) tg_quant_pertensor16_kernel(uint8_t* __restrict__ y, float* scale_out,
+                                                                   const T* __restrict__ x, int64_t n_chunks,
+                                                                   const uint32_t* amax_bits) {
+  float scale = __fdiv_rn(__uint_as_float(*amax_bits), kE4M3Max);
+  if (scale == 0.f) scale = 1.0f;
+  if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
+  const bool tame = q8_scale_is_tame(scale);
+  const float r = __frcp_rn(scale);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; c < n_chunks; c += stride) {
+    const uint4 t0 = __ldcs(reinterpret_cast<const uint4*>(x + c * 16));
+    const uint4 t1 = __ldcs(reinterpret_cast<const uint4*>(x + c * 16) + 1);
+    const uint32_t w[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
+    uint32_t out[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 x0, x1;
+      if constexpr (sizeof(T) == 2 && !std::is_same<T, __half>::value) {
+        x0 = make_float2(__uint_as_float(w[2 * k] << 16), __uint_as_float(w[2 * k] & 0xffff0000u));
+        x1 = make_float2(__uint_as_float(w[2 * k + 1] << 16), __uint_as_float(w[2 * k + 1] & 0xffff0000u));
+      } else {
+        x0 = __half22float2(*reinterpret_cast<const __half2*>(&w[2 * k]));
+        x1 = __half22float2(*reinterpret_cast<const __half2*>(&w[2 * k + 1]));
+      }
+      if (tame) {
+        const float2 q0 = q8_quot2(x0, scale, r), q1 = q8_quot2(x1, scale, r);
+        out[k] = q8_cast2<kQ8E4M3>(q0.x, q0.y, -kE4M3Max, kE4M3Max) | (q8_cast2<kQ8E4M3>(q1.x, q1.y, -kE4M3Max, kE4M3Max) << 16);
+      } else {
+        out[k] = q8_pair<kQ8E4M3>(x0.x, x0.y, scale, r, false, -kE4M3Max, kE4M3Max) |
+                 (q8_pair<kQ8E4M3>(x1.x, x1.y, scale, r, false, -kE4M3Max, kE4M3Max) << 16);
+      }
+    }
+    __stcs(reinterpret_cast<uint4*>(y + c * 16), make_uint4(out[0], out[1], out[2], out[3]));
+  }
+}
+
 // ------------------------------------------------------- 128x128 weight quant
 // One CTA per 128 x 128 block; thread t owns columns 4*(t%32) .. +3 of rows
 // t/32, t/32+8, ... (16 rows), keeps them in registers across the block-wide
@@ -253,14 +295,19 @@ cudaError_t launch_quant_pertensor(uint8_t* y, float* scale_out, const void* x, 
   cudaError_t e = cudaMemsetAsync(amax_scratch, 0, sizeof(uint32_t), stream);
   if (e != cudaSuccess) return e;
   const int grid = grid_for((numel + 3) / 4, 256, num_sms * 8);
+  const bool wide = x_dtype != TG_F32 && numel % 16 == 0 && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) &&
+                    ((reinterpret_cast<uintptr_t>(y) & 15u) == 0);
+  const int grid16 = grid_for(numel / 16, 256, num_sms * 16);
   if (x_dtype == TG_BF16) {
     const auto* xx = static_cast<const __nv_bfloat16*>(x);
     tg_amax_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(xx, numel, amax_scratch);
-    tg_quant_pertensor_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(y, scale_out, xx, numel, amax_scratch);
+    if (wide) tg_quant_pertensor16_kernel<__nv_bfloat16><<<grid16, 256, 0, stream>>>(y, scale_out, xx, numel / 16, amax_scratch);
+    else tg_quant_pertensor_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(y, scale_out, xx, numel, amax_scratch);
   } else if (x_dtype == TG_F16) {
     const auto* xx = static_cast<const __half*>(x);
     tg_amax_kernel<__half><<<grid, 256, 0, stream>>>(xx, numel, amax_scratch);
-    tg_quant_pertensor_kernel<__half><<<grid, 256, 0, stream>>>(y, scale_out, xx, numel, amax_scratch);
+    if (wide) tg_quant_pertensor16_kernel<__half><<<grid16, 256, 0, stream>>>(y, scale_out, xx, numel / 16, amax_scratch);
+    else tg_quant_pertensor_kernel<__half><<<grid, 256, 0, stream>>>(y, scale_out, xx, numel, amax_scratch);
   } else {
     const auto* xx = static_cast<const float*>(x);
     tg_amax_kernel<float><<<grid, 256, 0, stream>>>(xx, numel, amax_scratch);

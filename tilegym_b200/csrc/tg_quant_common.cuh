@@ -20,6 +20,15 @@ enum Q8Kind : int { kQ8E4M3 = 0, kQ8E5M2 = 1, kQ8Int8 = 2 };
 // group whose scale is outside it all take __fdiv_rn.
 __device__ __forceinline__ bool q8_scale_is_tame(float s) { return s > 1e-20f && s < 1e20f; }
 
+// Smallest power of two >= max(|s|, 1e-10): ceil(log2) read off the exponent and mantissa bits, so the
+// result does not depend on a log2 implementation.
+__device__ __forceinline__ float round_up_pow2(float s) {
+  s = fmaxf(fabsf(s), 1e-10f);
+  const uint32_t b = __float_as_uint(s);
+  const uint32_t exp_bits = (b & 0x7f800000u) + ((b & 0x007fffffu) ? 0x00800000u : 0u);
+  return __uint_as_float(exp_bits);
+}
+
 // May cast(a) differ from cast(q) for some q within 4 ulps of a?
 template <int KIND>
 __device__ __forceinline__ bool q8_unsafe(float a) {
@@ -49,6 +58,31 @@ __device__ __forceinline__ uint32_t q8_cast2(float lo, float hi, float qmin, flo
     return static_cast<uint32_t>(
         __nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, KIND == kQ8E4M3 ? __NV_E4M3 : __NV_E5M2));
   }
+}
+
+// x / s for two neighbouring elements, correctly rounded, from the group's reciprocal r = RN(1 / s) with three
+// packed FMA-pipe instructions and no test: a = x r is within two ulps of the quotient, e = x - a s is exact in
+// an FMA, and a + e r is the quotient to ~2^-46 before its single rounding (Markstein's correction step).  For
+// 16-bit inputs and scales of the form RN(amax / qmax) the result has been compared with div.rn for EVERY
+// (amax, x) pair (tg_selftest_quant16: 2^31 quotients per input type and target format); callers use it for
+// those only.  e is +0 whenever the residual vanishes, which would turn x = -0 into +0: x's sign bit is put back
+// (a no-op for every other x, since r > 0).
+__device__ __forceinline__ float2 q8_quot2(float2 x, float s, float r) {
+  const float2 r2 = make_float2(r, r);
+  const float2 a = __fmul2_rn(x, r2);
+  const float2 e = __ffma2_rn(a, make_float2(-s, -s), x);
+  float2 q = __ffma2_rn(e, r2, a);
+  q.x = __uint_as_float(__float_as_uint(q.x) | (__float_as_uint(x.x) & 0x80000000u));
+  q.y = __uint_as_float(__float_as_uint(q.y) | (__float_as_uint(x.y) & 0x80000000u));
+  return q;
+}
+
+// amax / qmax (qmax = 448, 57344 or 127) the same way: c = RN(1 / qmax).  Exact for every 16-bit amax whose
+// quotient is a normal number (checked by the same self-test); smaller ones take div.rn.
+__device__ __forceinline__ float q8_scale_from_amax(float amax, float qmax, float c) {
+  if (amax < 1e-30f) return __fdiv_rn(amax, qmax);
+  const float q = amax * c;
+  return __fmaf_rn(__fmaf_rn(-q, qmax, amax), c, q);
 }
 
 // Two neighbouring elements -> two bytes (x0 in the low byte).
