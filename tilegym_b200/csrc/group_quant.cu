@@ -99,8 +99,23 @@ __global__ void __launch_bounds__(256)
   const int tpg_shift = 31 - __clz(tpg);
   const int64_t span = static_cast<int64_t>(gridDim.x) * blockDim.x;
   // all lanes of a warp run the same number of iterations (the shuffles need them)
-  for (int64_t base = static_cast<int64_t>(blockIdx.x) * blockDim.x + (threadIdx.x & ~31); base < n_chunks;
-       base += span) {
+  // 16-bit inputs: the next iteration's chunk is requested before this one is worked on, which keeps a second
+  // set of loads in flight per thread through the shuffle / convert / store part
+  [[maybe_unused]] uint32_t w_next[EPT / 2];
+  [[maybe_unused]] auto fetch = [&](int64_t chunk, uint32_t (&dst)[EPT / 2]) {
+#pragma unroll
+    for (int j = 0; j < EPT / 2; ++j) dst[j] = 0u;
+    if (chunk < n_chunks) {
+#pragma unroll
+      for (int i = 0; i < EPT / 8; ++i) {
+        const uint4 t = __ldcs(reinterpret_cast<const uint4*>(x + chunk * EPT) + i);
+        dst[4 * i] = t.x; dst[4 * i + 1] = t.y; dst[4 * i + 2] = t.z; dst[4 * i + 3] = t.w;
+      }
+    }
+  };
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * blockDim.x + (threadIdx.x & ~31);
+  if constexpr (sizeof(T) == 2) fetch(first + lane, w_next);
+  for (int64_t base = first; base < n_chunks; base += span) {
     const int64_t c = base + lane;
     const bool live = c < n_chunks;
     uint32_t out[EPT / 4];
@@ -108,14 +123,8 @@ __global__ void __launch_bounds__(256)
     if constexpr (sizeof(T) == 2) {
       uint32_t w[EPT / 2];
 #pragma unroll
-      for (int j = 0; j < EPT / 2; ++j) w[j] = 0u;
-      if (live) {
-#pragma unroll
-        for (int i = 0; i < EPT / 8; ++i) {
-          const uint4 t = __ldcs(reinterpret_cast<const uint4*>(x + c * EPT) + i);
-          w[4 * i] = t.x; w[4 * i + 1] = t.y; w[4 * i + 2] = t.z; w[4 * i + 3] = t.w;
-        }
-      }
+      for (int j = 0; j < EPT / 2; ++j) w[j] = w_next[j];
+      if (base + span < n_chunks) fetch(c + span, w_next);
       uint32_t m2 = absmax_pairs<T>(w[0], w[1]);
 #pragma unroll
       for (int j = 2; j < EPT / 2; j += 2) m2 = absmax_pairs<T>(m2, absmax_pairs<T>(w[j], w[j + 1]));

@@ -174,9 +174,18 @@ __global__ void __launch_bounds__(256) tg_quant_pertensor16_kernel(uint8_t* __re
   const bool tame = q8_scale_is_tame(scale);
   const float r = __frcp_rn(scale);
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; c < n_chunks; c += stride) {
-    const uint4 t0 = __ldcs(reinterpret_cast<const uint4*>(x + c * 16));
-    const uint4 t1 = __ldcs(reinterpret_cast<const uint4*>(x + c * 16) + 1);
+  int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  uint4 n0 = make_uint4(0u, 0u, 0u, 0u), n1 = n0;
+  if (c < n_chunks) {
+    n0 = __ldcs(reinterpret_cast<const uint4*>(x + c * 16));
+    n1 = __ldcs(reinterpret_cast<const uint4*>(x + c * 16) + 1);
+  }
+  for (; c < n_chunks; c += stride) {
+    const uint4 t0 = n0, t1 = n1;
+    if (c + stride < n_chunks) {  // the next chunk is requested before this one is converted
+      n0 = __ldcs(reinterpret_cast<const uint4*>(x + (c + stride) * 16));
+      n1 = __ldcs(reinterpret_cast<const uint4*>(x + (c + stride) * 16) + 1);
+    }
     const uint32_t w[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
     uint32_t out[4];
 #pragma unroll
