@@ -86,7 +86,7 @@ def _worker_c_entry(rank, world, port, path):
     M, n, K = 384, 256, 1024
     N = n * world
     a8, b8, sa, sb = R.gen_per_tensor_case(M, N, K, 21)
-    bias = torch.randn(N, dtype=torch.bfloat16)
+    bias = torch.randn(N, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)  # the same on every rank
     ref = R.ref_fp8_scaled_mm(a8, b8, sa, sb, bias=bias)
     shard = sharded.shard_weight(b8.view(torch.uint8), world, rank).view(torch.float8_e4m3fn).to(dev)
     bias_shard = bias[rank * n:(rank + 1) * n].contiguous().to(dev)
@@ -99,7 +99,10 @@ def _worker_c_entry(rank, world, port, path):
     torch.cuda.synchronize(dev)
     _lib.device_status(rank)
     full = c_all.permute(1, 0, 2).reshape(M, N)
-    ok = rc == 0 and R.check_tolerance(full, ref)["ok"]
+    res = R.check_tolerance(full, ref)
+    ok = rc == 0 and res["ok"]
+    if not ok:
+        print(f"rank {rank}: rc={rc} {_lib.lib().tg_last_error_string()} {res}", flush=True)
     nccl.ncclCommDestroy.argtypes = [ctypes.c_void_p]
     nccl.ncclCommDestroy(comm)
     flags = torch.tensor([int(ok)])
