@@ -19,6 +19,7 @@
 // Roles: warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, warps 2-5 promotion + store.
 // Replaces, for small M, the kernel at src/tilegym/suites/unsloth/cutile/fp8.py:243-334.
 #include "tg_gemm_common.cuh"
+#include "tg_cluster_reduce.cuh"
 
 namespace tg {
 
@@ -64,27 +65,6 @@ struct BsmCfg {
   static_assert((2 * kStages + 5) * 8 + 12 <= kCtrlBytes, "control block");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory per CTA");
 };
-
-__device__ __forceinline__ uint32_t bsm_map_to_cta(uint32_t smem_addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-  return r;
-}
-// Bulk copy of `bytes` (a multiple of 16) from this CTA's shared memory to the shared memory of another CTA of the
-// cluster; completion is counted in bytes on an mbarrier of the destination CTA.
-__device__ __forceinline__ void bsm_bulk_copy_to_peer(uint32_t dst_cluster_addr, uint32_t src_cta_addr, uint32_t bytes,
-                                                      uint32_t mbar_cluster_addr) {
-  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   dst_cluster_addr),
-               "r"(src_cta_addr), "r"(bytes), "r"(mbar_cluster_addr)
-               : "memory");
-}
-__device__ __forceinline__ void bsm_cluster_arrive() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void bsm_cluster_wait() {
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
 
 template <typename T>
 __device__ __forceinline__ T bsm_cast(float v);
@@ -132,50 +112,6 @@ __device__ __forceinline__ void bsm_store_column(T* c, int64_t ldc, const float 
 #pragma unroll
   for (int m = 0; m < MP; ++m)
     if (m < mv) c[m * ldc] = bsm_cast<T>(acc[m] + bias);
-}
-
-// Cluster reduction, owner side, one output row: the sum over the splits, in split order (bit-stable), of four
-// consecutive columns; split `own` is read from this CTA's own partial tile, the others from the inbox blocks.
-__device__ __forceinline__ float4 bsm_sum_splits(const float* tile_row, const float* inbox_row, int rpr, int splits,
-                                                 int own) {
-  float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int s2 = 0; s2 < splits; ++s2) {
-    const float4 v = *reinterpret_cast<const float4*>(s2 == own ? tile_row : inbox_row + s2 * rpr * kBM);
-    sum.x += v.x;
-    sum.y += v.y;
-    sum.z += v.z;
-    sum.w += v.w;
-  }
-  return sum;
-}
-
-// Stores v[0..4) at columns col .. col + 3 of one output row (columns >= n_valid skipped); `vec_ok`: the four
-// elements start on a boundary of their combined size.
-__device__ __forceinline__ void bsm_store4(const GemmParams& p, int64_t row, int64_t col, const float (&v)[4],
-                                           int n_valid, bool vec_ok) {
-  const int64_t off = row * p.ldc + col;
-  if (p.out_dtype == TG_BF16) {
-    __nv_bfloat16* c = reinterpret_cast<__nv_bfloat16*>(p.C) + off;
-    if (vec_ok && n_valid >= 4) {
-      *reinterpret_cast<uint2*>(c) = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
-    } else {
-      for (int i = 0; i < 4 && i < n_valid; ++i) c[i] = __float2bfloat16_rn(v[i]);
-    }
-  } else if (p.out_dtype == TG_F16) {
-    __half* c = reinterpret_cast<__half*>(p.C) + off;
-    if (vec_ok && n_valid >= 4) {
-      *reinterpret_cast<uint2*>(c) = make_uint2(pack_f16x2(v[0], v[1]), pack_f16x2(v[2], v[3]));
-    } else {
-      for (int i = 0; i < 4 && i < n_valid; ++i) c[i] = __float2half_rn(v[i]);
-    }
-  } else {
-    float* c = reinterpret_cast<float*>(p.C) + off;
-    if (vec_ok && n_valid >= 4) {
-      *reinterpret_cast<float4*>(c) = make_float4(v[0], v[1], v[2], v[3]);
-    } else {
-      for (int i = 0; i < 4 && i < n_valid; ++i) c[i] = v[i];
-    }
-  }
 }
 
 template <int MP, bool CLUSTER>
@@ -453,8 +389,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     // MMAs complete, so nothing reads or fills its stages any more): tiles and inboxes, which lie over the
     // stages, may be written.
     __syncwarp();
-    bsm_cluster_arrive();
-    bsm_cluster_wait();
+    cl_arrive();
+    cl_wait();
     if (threadIdx.x == 64) TG_BSM_STAMP(41);
     if (warp >= 2) {
       if (have_acc) {
@@ -469,9 +405,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           const int r = (sp + i) % p.splits;
           const int rows = max(0, min(rpr, mv - r * rpr));
           if (rows > 0)
-            bsm_bulk_copy_to_peer(bsm_map_to_cta(smem_u32(inb + sp * rpr * kBM), static_cast<uint32_t>(r)),
+            cl_bulk_copy_to_peer(cl_map_to_cta(smem_u32(inb + sp * rpr * kBM), static_cast<uint32_t>(r)),
                                   smem_u32(tile + r * rpr * kBM), static_cast<uint32_t>(rows * kBM * 4),
-                                  bsm_map_to_cta(bar_inbox, static_cast<uint32_t>(r)));
+                                  cl_map_to_cta(bar_inbox, static_cast<uint32_t>(r)));
         }
       }
       if (threadIdx.x == 64) TG_BSM_STAMP(42);
@@ -498,17 +434,17 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         if (n_valid > 0) {
           for (int j = t >> 5; j < my_rows; j += 4) {
-            const float4 sum = bsm_sum_splits(tile + (my_r0 + j) * kBM + c4, inb + j * kBM + c4, rpr, p.splits, sp);
+            const float4 sum = cl_sum_splits(tile + (my_r0 + j) * kBM + c4, inb + j * kBM + c4, rpr, p.splits, sp);
             const float v[4] = {sum.x + b4[0], sum.y + b4[1], sum.z + b4[2], sum.w + b4[3]};
-            bsm_store4(p, my_r0 + j, static_cast<int64_t>(row0) + c4, v, n_valid, vec_ok);
+            cl_store4(p, my_r0 + j, static_cast<int64_t>(row0) + c4, v, n_valid, vec_ok);
           }
         }
       }
     }
     // a CTA may only leave once no bulk copy still reads its tile: every owner has seen all its bytes arrive
     __syncwarp();
-    bsm_cluster_arrive();
-    bsm_cluster_wait();
+    cl_arrive();
+    cl_wait();
   }
 
   if (threadIdx.x == 64) TG_BSM_STAMP(44);

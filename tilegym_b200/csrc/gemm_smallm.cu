@@ -9,14 +9,20 @@
 //     CTAs spread evenly over the SMs;
 //   * the first ring of TMA loads is issued before the CTA's set-up barrier;
 //   * split-K, cluster variant: the CTAs that share a weight tile form one
-//     thread-block cluster; every CTA PUSHES its fp32 partial rows into the
-//     shared memory of the CTA that owns them (output row m belongs to rank
-//     m % splits), one cluster barrier later each owner adds its rows in split
-//     order and stores them.  No global scratch, atomics or fences;
+//     thread-block cluster and reduce through distributed shared memory.
+//     M <= 32: every CTA pushes its fp32 partial rows into the inbox of the
+//     CTA that owns them (row m belongs to rank m % splits), one cluster
+//     barrier later each owner adds its rows in split order.  M > 32: every
+//     CTA writes its partial tile to its own shared memory (over the idle
+//     operand stages) and sends each peer the block of rows that peer owns
+//     with ONE bulk copy (bytes counted on the owner's mbarrier); owners
+//     acknowledge to the senders and add 4 columns per thread.  No global
+//     scratch or atomics either way;
 //   * split-K, workspace variant: partial tiles go to a global fp32 workspace
 //     and the last-arriving warp per (tile, quadrant) reduces them.
 // Same contract as the large-M kernel: C = alpha*sa*sb * A.B^T + bias + beta*C.
 #include "tg_gemm_common.cuh"
+#include "tg_cluster_reduce.cuh"
 
 namespace tg {
 
@@ -50,7 +56,8 @@ struct SmCfg {
   static constexpr int kInboxBytes = kInboxRows * kBM * 4;
   static constexpr int kCtrlBytes = 128;
   static constexpr int kSmemBytes = kStages * kStageBytes + kInboxBytes + kCtrlBytes + 1024;
-  static_assert((2 * kStages + 1) * 8 + 12 <= kCtrlBytes, "control block");
+  static_assert((2 * kStages + 3) * 8 + 12 <= kCtrlBytes, "control block");
+  static_assert(MP * kBM * 4 <= kStages * kStageBytes, "the partial tile lies over the idle stages");
   static_assert(2 * kSmemBytes <= 227 * 1024, "two CTAs per SM");
 };
 
@@ -201,7 +208,9 @@ __global__ void __launch_bounds__(kThreads, 2)
   const uint32_t bar_full = smem_u32(ctrl);
   const uint32_t bar_empty = bar_full + 8 * S;
   const uint32_t bar_tfull = bar_empty + 8 * S;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + (2 * S + 1) * 8);
+  const uint32_t bar_inbox = bar_tfull + 8;  // bytes of the peers' partial rows (cluster reduction)
+  const uint32_t bar_done = bar_inbox + 8;   // acknowledgements of the owners this CTA sent rows to
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + (2 * S + 3) * 8);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -225,8 +234,21 @@ __global__ void __launch_bounds__(kThreads, 2)
       mbar_init(bar_empty + 8 * i, 1);
     }
     mbar_init(bar_tfull, 1);
+    mbar_init(bar_inbox, 1);
     init_abort_flag(abort_flag, p.wait_limit_us);
     fence_mbar_init();
+    if constexpr (CLUSTER) {
+      // cluster reduction: every peer sends this CTA the block of output rows it owns (rows_owned x 128 floats)
+      const int mv0 = p.M < MP ? p.M : MP;
+      const int rpr0 = (mv0 + p.splits - 1) / p.splits;
+      const int rows_owned = max(0, min(rpr0, mv0 - sp * rpr0));
+      if (p.splits > 1 && rows_owned > 0)
+        mbar_arrive_expect_tx(bar_inbox, static_cast<uint32_t>((p.splits - 1) * rows_owned * kBM * 4));
+      // owners are the ranks 0 .. ceil(mv / rpr) - 1; this CTA sends to all of them but itself
+      const int owners = (mv0 + rpr0 - 1) / rpr0;
+      mbar_init(bar_done, static_cast<uint32_t>(max(1, owners - (rows_owned > 0 ? 1 : 0))));
+      fence_mbar_init();
+    }
     // The ring is empty and only this thread touches the full barriers until the barrier below:
     // start the weight stream right away, TMEM allocation and the other warps catch up meanwhile.
     pol_w = policy_evict_first();  // weights are read once
@@ -252,7 +274,10 @@ __global__ void __launch_bounds__(kThreads, 2)
   }
   if constexpr (CLUSTER) {
     __syncwarp();
-    sm_cluster_arrive_relaxed();  // "this CTA runs" (nothing to publish): matched by the wait before the pushes
+    // "this CTA runs and its inbox / done barriers are initialised" (thread 0's fence.mbarrier_init above publishes
+    // them cluster-wide; a release here would add a device-scope fence, about a microsecond): matched by the wait
+    // before the copies
+    sm_cluster_arrive_relaxed();
   }
   tc_fence_before();
   __syncthreads();
@@ -387,50 +412,137 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
     if (!done && have_acc && n_ok) smallm_store_column<MP>(p, n, acc, mv, scale, bias);
   } else if constexpr (CLUSTER) {
-    // Output row m is finished by the CTA of rank m % splits; partial row m of split sp goes to slot
-    // [sp][m / splits] of that CTA's inbox.  rows_per_rank = ceil(mv / splits).
-    const int rpr = (mv + p.splits - 1) / p.splits;
-    __syncwarp();
-    sm_cluster_wait();  // every CTA of the cluster has started: its shared memory may be written
-    if (have_acc && n_local < p.tile_rows) {
-      const uint32_t inbox_addr = smem_u32(inbox) + static_cast<uint32_t>((sp * rpr) * kBM + n_local) * 4u;
-      uint32_t r = 0, row_addr = inbox_addr;  // m = j * splits + r; row_addr = slot [sp][j] in the owner's inbox
+    if constexpr (MP < 64) {
+      // Few rows: every CTA pushes its partial rows element by element into the owners' inboxes and one cluster
+      // barrier publishes them (measured: 0.4-0.9 us faster than the bulk-copy scheme below for M <= 16, slower
+      // by 0.4-1.1 us at M = 64, where 64 remote stores per thread queue up).
+      // Output row m is finished by the CTA of rank m % splits; partial row m of split sp goes to slot
+      // [sp][m / splits] of that CTA's inbox.  rows_per_rank = ceil(mv / splits).
+      const int rpr = (mv + p.splits - 1) / p.splits;
+      __syncwarp();
+      sm_cluster_wait();  // every CTA of the cluster has started: its shared memory may be written
+      if (have_acc && n_local < p.tile_rows) {
+        const uint32_t inbox_addr = smem_u32(inbox) + static_cast<uint32_t>((sp * rpr) * kBM + n_local) * 4u;
+        uint32_t r = 0, row_addr = inbox_addr;  // m = j * splits + r; row_addr = slot [sp][j] in the owner's inbox
 #pragma unroll
-      for (int m = 0; m < MP; ++m) {
-        if (m < mv) {
-          sm_st_cluster_f32(sm_map_to_cta(row_addr, r), acc[m]);
-          if (++r == static_cast<uint32_t>(p.splits)) {
-            r = 0;
-            row_addr += kBM * 4u;
+        for (int m = 0; m < MP; ++m) {
+          if (m < mv) {
+            sm_st_cluster_f32(sm_map_to_cta(row_addr, r), acc[m]);
+            if (++r == static_cast<uint32_t>(p.splits)) {
+              r = 0;
+              row_addr += kBM * 4u;
+            }
           }
         }
       }
-    }
-    if (threadIdx.x == 64) TG_STAMP(6);
-    __syncwarp();
-    sm_cluster_arrive();  // release: this CTA's pushes are done
-    sm_cluster_wait();    // acquire: every peer's pushes into this CTA's inbox are visible
-    if (threadIdx.x == 64) TG_STAMP(7);
-    if (n_ok) {
-      const int rank = static_cast<int>(sm_cluster_ctarank());
-      const float* col = inbox + n_local;
-      if (p.beta != 0.f) {
-        for (int j = 0; j * p.splits + rank < mv; ++j) {
-          const float* src = col + j * kBM;
-          float sum = src[0];
-          for (int s2 = 1; s2 < p.splits; ++s2) sum += src[s2 * rpr * kBM];  // split order: bit-stable
-          smallm_store(p, j * p.splits + rank, n, fmaf(sum, scale, bias));
+      if (threadIdx.x == 64) TG_STAMP(6);
+      __syncwarp();
+      sm_cluster_arrive();  // release: this CTA's pushes are done
+      sm_cluster_wait();    // acquire: every peer's pushes into this CTA's inbox are visible
+      if (threadIdx.x == 64) TG_STAMP(7);
+      if (n_ok) {
+        const int rank = static_cast<int>(sm_cluster_ctarank());
+        const float* col = inbox + n_local;
+        if (p.beta != 0.f) {
+          for (int j = 0; j * p.splits + rank < mv; ++j) {
+            const float* src = col + j * kBM;
+            float sum = src[0];
+            for (int s2 = 1; s2 < p.splits; ++s2) sum += src[s2 * rpr * kBM];  // split order: bit-stable
+            smallm_store(p, j * p.splits + rank, n, fmaf(sum, scale, bias));
+          }
+        } else if (p.out_dtype == TG_BF16) {
+          smallm_reduce_rows_as(reinterpret_cast<__nv_bfloat16*>(p.C) + n, p.ldc, col, rank, p.splits, rpr, mv, scale, bias);
+        } else if (p.out_dtype == TG_F16) {
+          smallm_reduce_rows_as(reinterpret_cast<__half*>(p.C) + n, p.ldc, col, rank, p.splits, rpr, mv, scale, bias);
+        } else {
+          smallm_reduce_rows_as(reinterpret_cast<float*>(p.C) + n, p.ldc, col, rank, p.splits, rpr, mv, scale, bias);
         }
-      } else if (p.out_dtype == TG_BF16) {
-        smallm_reduce_rows_as(reinterpret_cast<__nv_bfloat16*>(p.C) + n, p.ldc, col, rank, p.splits, rpr, mv, scale, bias);
-      } else if (p.out_dtype == TG_F16) {
-        smallm_reduce_rows_as(reinterpret_cast<__half*>(p.C) + n, p.ldc, col, rank, p.splits, rpr, mv, scale, bias);
-      } else {
-        smallm_reduce_rows_as(reinterpret_cast<float*>(p.C) + n, p.ldc, col, rank, p.splits, rpr, mv, scale, bias);
+      }
+      if (threadIdx.x == 64) TG_STAMP(8);
+      // no peer touches this CTA's shared memory after the barrier above: it may exit on its own
+    } else {
+      // Rank r of the cluster (= its K split) finishes the output rows [r * rpr, (r + 1) * rpr), rpr = ceil(mv / splits).
+      const int rpr = (mv + p.splits - 1) / p.splits;
+      const int my_r0 = sp * rpr;
+      const int my_rows = max(0, min(rpr, mv - my_r0));
+      float* tile = reinterpret_cast<float*>(smem);  // this CTA's partial tile [mv][128], over its idle stages
+      bool clean = true;  // warps 0 and 1 have nothing to wait for here
+      __syncwarp();
+      sm_cluster_wait();  // every CTA of the cluster has started and armed its inbox barrier
+      if (warp >= 2) {
+        if (have_acc) {  // all MMAs have completed: nothing reads or fills the stages any more
+#pragma unroll
+          for (int m = 0; m < MP; ++m)
+            if (m < mv) tile[m * kBM + n_local] = acc[m];
+        }
+        fence_proxy_async_smem();                       // the bulk copies below read what was just written
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps: the tile is complete
+        // bias and geometry of the owner's part, fetched while the copies fly
+        const int t = threadIdx.x - 64;
+        const int c4 = (t & 31) * 4;
+        const int left = static_cast<int>(p.N - row0);
+        const int n_valid = (left < p.tile_rows ? left : p.tile_rows) - c4;
+        float b4[4] = {0.f, 0.f, 0.f, 0.f};
+        if (p.bias != nullptr && my_rows > 0) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (i < n_valid) b4[i] = load_bias(p.bias, p.bias_dtype, static_cast<int64_t>(row0) + c4 + i);
+        }
+        if (warp == 2 && have_acc && lane >= 1 && lane < p.splits) {  // lane i serves the peer i ranks further on
+          const int r = (sp + lane) % p.splits;
+          const int rows = max(0, min(rpr, mv - r * rpr));
+          if (rows > 0)
+            cl_bulk_copy_to_peer(cl_map_to_cta(smem_u32(inbox + sp * rpr * kBM), static_cast<uint32_t>(r)),
+                                 smem_u32(tile + r * rpr * kBM), static_cast<uint32_t>(rows * kBM * 4),
+                                 cl_map_to_cta(bar_inbox, static_cast<uint32_t>(r)));
+        }
+        if (threadIdx.x == 64) TG_STAMP(6);
+        bool got = true;
+        if (my_rows > 0) {
+          got = mbar_wait(bar_inbox, 0u, abort_flag);  // the other splits' versions of this CTA's rows have landed
+          got = __all_sync(0xffffffffu, got);
+          if (!got) report_timeout(p.status, kRoleEpilogue * 1000 + 22);
+          // every sender's tile has been read: tell the senders right away, before this CTA's own adds and stores
+          if (got && warp == 2 && lane >= 1 && lane < p.splits)
+            cl_mbar_arrive_remote(cl_map_to_cta(bar_done, static_cast<uint32_t>((sp + lane) % p.splits)));
+        }
+        if (threadIdx.x == 64) TG_STAMP(7);
+        if (got && have_acc && n_valid > 0) {
+          // thread -> four columns of every fourth owned row: a warp writes one 256-byte (bf16) piece of a row
+          const int esz = (p.out_dtype == TG_F32) ? 4 : 2;
+          const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0) && (((p.ldc * esz) & 15) == 0);
+          for (int j = t >> 5; j < my_rows; j += 4) {
+            const float4 sum = cl_sum_splits(tile + (my_r0 + j) * kBM + c4, inbox + j * kBM + c4, rpr, p.splits, sp);
+            const float v[4] = {fmaf(sum.x, scale, b4[0]), fmaf(sum.y, scale, b4[1]), fmaf(sum.z, scale, b4[2]),
+                                fmaf(sum.w, scale, b4[3])};
+            if (p.beta != 0.f) {
+              for (int i = 0; i < 4 && i < n_valid; ++i) smallm_store(p, my_r0 + j, static_cast<int64_t>(row0) + c4 + i, v[i]);
+            } else {
+              cl_store4(p, my_r0 + j, static_cast<int64_t>(row0) + c4, v, n_valid, vec_ok);
+            }
+          }
+        }
+        if (threadIdx.x == 64) TG_STAMP(8);
+        // This CTA's tile must stay until every owner it sent rows to has them: wait for their acknowledgements.
+        const int owners = (mv + rpr - 1) / rpr;
+        if (have_acc && owners - (my_rows > 0 ? 1 : 0) > 0) {
+          bool acked = mbar_wait(bar_done, 0u, abort_flag);
+          acked = __all_sync(0xffffffffu, acked);
+          if (!acked) report_timeout(p.status, kRoleEpilogue * 1000 + 23);
+          got = got && acked;
+        }
+        clean = got && have_acc;
+      }
+      // Normal case: every copy into this CTA has landed and every copy out of it has been acknowledged, no peer
+      // touches its shared memory again, and it leaves on its own.  If a wait above gave up, peers may still be
+      // sending: such a CTA stays until all threads of the cluster have either left or arrived here as well
+      // (barrier.cluster.wait counts non-exited threads only).
+      clean = __syncthreads_and(clean ? 1 : 0) != 0;
+      if (!clean) {
+        sm_cluster_arrive();
+        sm_cluster_wait();
       }
     }
-    if (threadIdx.x == 64) TG_STAMP(8);
-    // no peer touches this CTA's shared memory after the barrier above: it may exit on its own
   } else {
     if (have_acc) {
       float* part = p.ws_partial + static_cast<int64_t>(u) * (MP * kBM) + n_local;
