@@ -67,11 +67,28 @@ def test_two_rank_gloo_gather_equals_unsharded(tmp_path):
 
 
 def test_model_entry_points_keep_reference_signature():
-    ref_params = ["rope", "rms_norm", "swiglu", "attn", "model", "use_cutile"]
-    for fn in monkey_patch.MODEL_TYPE_TO_APPLY_TILEGYM_FN.values():
+    # keyword lists of src/tilegym/transformers/monkey_patch.py:24-31, 64-72, 118-125, 158-166, 240-246, 293-300,
+    # 350-357, 393-400, 437-444, 495-502 and its registry at :555-566
+    base = ["rope", "rms_norm", "swiglu", "attn", "model", "use_cutile"]
+    ref_params = {
+        "llama": base, "mistral": base, "qwen2": base, "phi3": base, "olmo3": base,
+        "deepseek_v2": ["rope", "rms_norm", "swiglu", "attn", "moe", "model", "use_cutile"],
+        "qwen3_5": ["rope", "rms_norm", "swiglu", "attn", "gated_delta_rule", "model", "use_cutile"],
+        "gpt_oss": ["rope", "rms_norm", "swiglu", "attn", "use_cutile"],
+        "gemma3": ["rope", "rms_norm", "mlp", "attn", "model", "use_cutile"],
+        "olmoe": ["rope", "rms_norm", "attn", "moe", "model", "use_cutile"],
+    }
+    assert set(monkey_patch.MODEL_TYPE_TO_APPLY_TILEGYM_FN) == set(ref_params)
+    for name, fn in monkey_patch.MODEL_TYPE_TO_APPLY_TILEGYM_FN.items():
         params = inspect.signature(fn).parameters
-        assert list(params)[:6] == ref_params
+        assert list(params)[:len(ref_params[name])] == ref_params[name], name
+        assert list(params)[len(ref_params[name]):] == ["fp8_linear", "fp8_mode"]
         assert params["use_cutile"].default is False and params["fp8_linear"].default is False
+        fn()  # the defaults change nothing and need no GPU
+    assert inspect.signature(monkey_patch.apply_tilegym_kernel_to_gpt_oss).parameters["swiglu"].default is False
+    monkey_patch.apply_tilegym_kernel_to_deepseek_v2(True, True, True, True, False, None, False)  # positional use
+    with pytest.raises(TypeError):
+        monkey_patch.apply_tilegym_kernel_to_llama(no_such_flag=True)
     # defaults (fp8_linear=False) change nothing and need no GPU
     monkey_patch.apply_tilegym_kernel_to_llama()
     monkey_patch._apply_tilegym_kernel("llama", rope=True, not_a_kwarg=1)

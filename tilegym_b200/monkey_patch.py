@@ -77,16 +77,35 @@ def _apply(model_type: str, model, fp8_linear: bool, fp8_mode: Optional[str], fu
         PreTrainedModel._tilegym_b200_wrapped = True
 
 
-def _make(model_type: str):
-    def apply_fn(rope: bool = True, rms_norm: bool = True, swiglu: bool = True, attn: bool = True, model=None,
-                 use_cutile: bool = False, fp8_linear: bool = False, fp8_mode: Optional[str] = None) -> None:
-        for flag, on in (("rope", rope), ("rms_norm", rms_norm), ("swiglu", swiglu), ("attn", attn)):
-            if on and not (flag == "swiglu" and fp8_linear):
-                logger.debug("tilegym_b200: %s=True accepted; that kernel is not part of this library", flag)
-        # swiglu=True, the reference's switch for its fused SwiGLU MLP, selects the fused gate/up + SiLU*mul
-        # kernel here when the FP8 path is on
-        _apply(model_type, model, fp8_linear, fp8_mode, fuse_swiglu=swiglu)
+def _make(model_type: str, flags=("rope", "rms_norm", "swiglu", "attn"), defaults=None, takes_model: bool = True,
+          fuse_flag: Optional[str] = "swiglu"):
+    """Builds apply_tilegym_kernel_to_<model_type> with the reference's keyword list for that model (`flags`, then
+    `model` where the reference takes one, then `use_cutile`) plus `fp8_linear` / `fp8_mode`.  `fuse_flag` names the
+    reference switch of the fused gated MLP, which selects the fused gate/up + SiLU*mul kernel when the FP8 path is on."""
+    defaults = defaults or {}
+    names = list(flags) + (["model"] if takes_model else []) + ["use_cutile", "fp8_linear", "fp8_mode"]
+    params = []
+    for n in names:
+        if n == "model" or n == "fp8_mode":
+            default = None
+        elif n in ("use_cutile", "fp8_linear"):
+            default = False
+        else:
+            default = defaults.get(n, True)
+        params.append(inspect.Parameter(n, inspect.Parameter.POSITIONAL_OR_KEYWORD, default=default))
+    signature = inspect.Signature(params)
 
+    def apply_fn(*args, **kwargs) -> None:
+        bound = signature.bind(*args, **kwargs)
+        bound.apply_defaults()
+        a = bound.arguments
+        for flag in flags:
+            if a[flag] and not (flag == fuse_flag and a["fp8_linear"]):
+                logger.debug("tilegym_b200: %s=True accepted; that kernel is not part of this library", flag)
+        _apply(model_type, a.get("model"), a["fp8_linear"], a["fp8_mode"],
+               fuse_swiglu=bool(a[fuse_flag]) if fuse_flag else False)
+
+    apply_fn.__signature__ = signature
     apply_fn.__name__ = f"apply_tilegym_kernel_to_{model_type}"
     apply_fn.__doc__ = (
         f"Signature of the reference's apply_tilegym_kernel_to_{model_type} plus the opt-in `fp8_linear` / "
@@ -95,16 +114,31 @@ def _make(model_type: str):
     return apply_fn
 
 
+# keyword lists of src/tilegym/transformers/monkey_patch.py:24-31 (llama), :64-72 (deepseek_v2), :118-125 (qwen2),
+# :158-166 (qwen3_5), :240-246 (gpt_oss: no `model`, swiglu off by default), :293-300 (gemma3: `mlp`), :350-357
+# (mistral), :393-400 (phi3), :437-444 (olmoe), :495-502 (olmo3)
 apply_tilegym_kernel_to_llama = _make("llama")
-apply_tilegym_kernel_to_deepseek_v2 = _make("deepseek_v2")
+apply_tilegym_kernel_to_deepseek_v2 = _make("deepseek_v2", flags=("rope", "rms_norm", "swiglu", "attn", "moe"))
 apply_tilegym_kernel_to_mistral = _make("mistral")
 apply_tilegym_kernel_to_qwen2 = _make("qwen2")
+apply_tilegym_kernel_to_qwen3 = _make("qwen3_5", flags=("rope", "rms_norm", "swiglu", "attn", "gated_delta_rule"))
+apply_tilegym_kernel_to_gpt_oss = _make("gpt_oss", defaults={"swiglu": False}, takes_model=False)
+apply_tilegym_kernel_to_gemma3 = _make("gemma3", flags=("rope", "rms_norm", "mlp", "attn"), fuse_flag=None)
+apply_tilegym_kernel_to_phi3 = _make("phi3")
+apply_tilegym_kernel_to_olmo3 = _make("olmo3")
+apply_tilegym_kernel_to_olmoe = _make("olmoe", flags=("rope", "rms_norm", "attn", "moe"), fuse_flag=None)
 
 MODEL_TYPE_TO_APPLY_TILEGYM_FN = {
     "llama": apply_tilegym_kernel_to_llama,
     "deepseek_v2": apply_tilegym_kernel_to_deepseek_v2,
+    "gpt_oss": apply_tilegym_kernel_to_gpt_oss,
     "mistral": apply_tilegym_kernel_to_mistral,
     "qwen2": apply_tilegym_kernel_to_qwen2,
+    "qwen3_5": apply_tilegym_kernel_to_qwen3,
+    "gemma3": apply_tilegym_kernel_to_gemma3,
+    "phi3": apply_tilegym_kernel_to_phi3,
+    "olmo3": apply_tilegym_kernel_to_olmo3,
+    "olmoe": apply_tilegym_kernel_to_olmoe,
 }
 
 
