@@ -13,8 +13,9 @@
 //   * the K splits of a tile form a thread-block cluster and reduce through distributed shared memory: after its
 //     main loop every CTA writes its fp32 partial tile to its own shared memory and sends each peer the block
 //     of rows that peer owns with ONE bulk copy (cp.async.bulk shared::cta -> shared::cluster, completion counted
-//     in bytes on the owner's mbarrier); each owner then adds its rows in split order (bit-stable) and stores
-//     whole 256-byte row pieces.  No global scratch, no per-element remote stores;
+//     in bytes on the owner's mbarrier); each owner acknowledges to the senders (a remote mbarrier arrive, so a
+//     sender leaves as soon as its rows are taken), adds its rows in split order (bit-stable) and stores whole
+//     256-byte row pieces.  No global scratch, no per-element remote stores;
 //   * a tile that is not split is transposed through shared memory and stored as whole 16-byte pieces of rows.
 // Roles: warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, warps 2-5 promotion + store.
 // Replaces, for small M, the kernel at src/tilegym/suites/unsloth/cutile/fp8.py:243-334.
@@ -62,7 +63,7 @@ struct BsmCfg {
   static constexpr int kCtrlBytes = 256;
   static constexpr int kSmemBytes = kStages * kStageBytes + kScaleBytes + kCtrlBytes + 1024;
   static_assert(kInboxBytes <= kStages * kStageBytes, "tile and inbox lie over the stages");
-  static_assert((2 * kStages + 5) * 8 + 12 <= kCtrlBytes, "control block");
+  static_assert((2 * kStages + 6) * 8 + 12 <= kCtrlBytes, "control block");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory per CTA");
 };
 
@@ -134,7 +135,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t bar_tfull = bar_empty + 8 * S;   // 2
   const uint32_t bar_tempty = bar_tfull + 16;     // 2
   const uint32_t bar_inbox = bar_tempty + 16;     // 1: bytes of the peers' partial rows (cluster reduction)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + (2 * S + 5) * 8);
+  const uint32_t bar_done = bar_inbox + 8;        // 1: acknowledgements of the owners this CTA sent rows to
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + (2 * S + 6) * 8);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -170,6 +172,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int rows_owned = max(0, min(rpr0, mv0 - sp * rpr0));
       if (p.splits > 1 && rows_owned > 0)
         mbar_arrive_expect_tx(bar_inbox, static_cast<uint32_t>((p.splits - 1) * rows_owned * kBM * 4));
+      // owners are the ranks 0 .. ceil(mv / rpr) - 1; this CTA sends to all of them but itself
+      const int owners = (mv0 + rpr0 - 1) / rpr0;
+      mbar_init(bar_done, static_cast<uint32_t>(max(1, owners - (rows_owned > 0 ? 1 : 0))));
+      fence_mbar_init();
     }
     // The ring is empty and only this thread touches the full barriers until the barrier below: start the
     // weight stream right away, TMEM allocation and the other warps catch up meanwhile.
@@ -385,6 +391,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int my_rows = max(0, min(rpr, mv - my_r0));
     float* tile = inbox;              // this CTA's partial tile, [MP][128] fp32
     float* inb = inbox + MP * kBM;    // [split][rpr][128]: the rows this CTA owns, as the other splits computed them
+    bool clean = true;                // warps 0 and 1 have nothing to wait for here
     // Every CTA of the cluster has finished its main loop (its promotion warps have seen the last k-block's
     // MMAs complete, so nothing reads or fills its stages any more): tiles and inboxes, which lie over the
     // stages, may be written.
@@ -400,15 +407,24 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       fence_proxy_async_smem();                       // the bulk copies below read what was just written
       asm volatile("bar.sync 1, 128;" ::: "memory");  // the four promotion warps: the tile is complete
-      if (threadIdx.x == 64 && have_acc) {
-        for (int i = 1; i < p.splits; ++i) {  // peers in rotated order, so the ranks' copies fan out
-          const int r = (sp + i) % p.splits;
-          const int rows = max(0, min(rpr, mv - r * rpr));
-          if (rows > 0)
-            cl_bulk_copy_to_peer(cl_map_to_cta(smem_u32(inb + sp * rpr * kBM), static_cast<uint32_t>(r)),
-                                  smem_u32(tile + r * rpr * kBM), static_cast<uint32_t>(rows * kBM * 4),
-                                  cl_map_to_cta(bar_inbox, static_cast<uint32_t>(r)));
-        }
+      // geometry and bias of the owner's part, fetched while the copies fly
+      const int t = threadIdx.x - 64;
+      const int c4 = (t & 31) * 4;
+      const int left = static_cast<int>(p.N - row0);
+      const int n_valid = (left < kBM ? left : kBM) - c4;
+      float b4[4] = {0.f, 0.f, 0.f, 0.f};
+      if (p.bias != nullptr && my_rows > 0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (i < n_valid) b4[i] = load_bias(p.bias, p.bias_dtype, static_cast<int64_t>(row0) + c4 + i);
+      }
+      if (warp == 2 && have_acc && lane >= 1 && lane < p.splits) {  // lane i serves the peer i ranks further on
+        const int r = (sp + lane) % p.splits;
+        const int rows = max(0, min(rpr, mv - r * rpr));
+        if (rows > 0)
+          cl_bulk_copy_to_peer(cl_map_to_cta(smem_u32(inb + sp * rpr * kBM), static_cast<uint32_t>(r)),
+                               smem_u32(tile + r * rpr * kBM), static_cast<uint32_t>(rows * kBM * 4),
+                               cl_map_to_cta(bar_inbox, static_cast<uint32_t>(r)));
       }
       if (threadIdx.x == 64) TG_BSM_STAMP(42);
       bool got = true;
@@ -416,35 +432,40 @@ __global__ void __launch_bounds__(kThreads, 1)
         got = mbar_wait(bar_inbox, 0u, abort_flag);  // the other splits' versions of this CTA's rows have landed
         got = __all_sync(0xffffffffu, got);
         if (!got) report_timeout(p.status, kRoleEpilogue * 1000 + 72);
+        // every sender's tile has been read: tell the senders right away, before this CTA's own adds and stores
+        if (got && warp == 2 && lane >= 1 && lane < p.splits)
+          cl_mbar_arrive_remote(cl_map_to_cta(bar_done, static_cast<uint32_t>((sp + lane) % p.splits)));
       }
       if (threadIdx.x == 64) TG_BSM_STAMP(43);
-      if (got && have_acc) {
+      if (got && have_acc && n_valid > 0) {
         // thread -> four columns of every fourth owned row: a warp writes one 256-byte (bf16) piece of a row
-        const int t = threadIdx.x - 64;
-        const int c4 = (t & 31) * 4;
-        const int left = static_cast<int>(p.N - row0);
-        const int n_valid = (left < kBM ? left : kBM) - c4;
         const int esz = (p.out_dtype == TG_F32) ? 4 : 2;
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0) && (((p.ldc * esz) & 15) == 0);
-        float b4[4] = {0.f, 0.f, 0.f, 0.f};
-        if (p.bias != nullptr) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            if (i < n_valid) b4[i] = load_bias(p.bias, p.bias_dtype, static_cast<int64_t>(row0) + c4 + i);
-        }
-        if (n_valid > 0) {
-          for (int j = t >> 5; j < my_rows; j += 4) {
-            const float4 sum = cl_sum_splits(tile + (my_r0 + j) * kBM + c4, inb + j * kBM + c4, rpr, p.splits, sp);
-            const float v[4] = {sum.x + b4[0], sum.y + b4[1], sum.z + b4[2], sum.w + b4[3]};
-            cl_store4(p, my_r0 + j, static_cast<int64_t>(row0) + c4, v, n_valid, vec_ok);
-          }
+        for (int j = t >> 5; j < my_rows; j += 4) {
+          const float4 sum = cl_sum_splits(tile + (my_r0 + j) * kBM + c4, inb + j * kBM + c4, rpr, p.splits, sp);
+          const float v[4] = {sum.x + b4[0], sum.y + b4[1], sum.z + b4[2], sum.w + b4[3]};
+          cl_store4(p, my_r0 + j, static_cast<int64_t>(row0) + c4, v, n_valid, vec_ok);
         }
       }
+      // This CTA's tile must stay until every owner it sent rows to has them: wait for their acknowledgements.
+      const int owners = (mv + rpr - 1) / rpr;
+      if (have_acc && owners - (my_rows > 0 ? 1 : 0) > 0) {
+        bool acked = mbar_wait(bar_done, 0u, abort_flag);
+        acked = __all_sync(0xffffffffu, acked);
+        if (!acked) report_timeout(p.status, kRoleEpilogue * 1000 + 73);
+        got = got && acked;
+      }
+      clean = got && have_acc;
     }
-    // a CTA may only leave once no bulk copy still reads its tile: every owner has seen all its bytes arrive
-    __syncwarp();
-    cl_arrive();
-    cl_wait();
+    // Normal case: every copy into this CTA has landed and every copy out of it has been acknowledged, no peer
+    // touches its shared memory again, and it leaves on its own.  If a wait above gave up, peers may still be
+    // sending: such a CTA stays until all threads of the cluster have either left or arrived here as well
+    // (barrier.cluster.wait counts non-exited threads only).
+    clean = __syncthreads_and(clean ? 1 : 0) != 0;
+    if (!clean) {
+      cl_arrive();
+      cl_wait();
+    }
   }
 
   if (threadIdx.x == 64) TG_BSM_STAMP(44);

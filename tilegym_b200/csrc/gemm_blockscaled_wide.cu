@@ -14,6 +14,8 @@
 // Roles: warp 0 TMA producer, warp 1 MMA issuer and TMEM owner, warps 2-3 idle, warps 4-11 promotion + store.
 #include <cuda_fp8.h>
 
+#include <type_traits>
+
 #include "tg_gemm_common.cuh"
 #include "tg_quant_common.cuh"
 
@@ -47,8 +49,9 @@ constexpr int kTmemCols = kAccBufs * kBN;  // 512
 constexpr int kCtrlBytes = 256;
 constexpr int kOutBufBytes = 32 * 128;  // per promotion warp: 32 rows x 64 two-byte columns, 128-byte swizzle
 constexpr int kOutStageBytes = kEpiWarps * kOutBufBytes;
-constexpr int kSmemBytes = kStages * kStageBytes + kOutStageBytes + kCtrlBytes + 1024;
-static_assert((2 * kStages + 2 * kAccBufs + 8) * 8 + 12 <= kCtrlBytes, "control block");
+constexpr int kAmaxBytes = kEpiWarps * 32 * 4;  // one float per promotion thread (SiLU * mul epilogue)
+constexpr int kSmemBytes = kStages * kStageBytes + kOutStageBytes + kAmaxBytes + kCtrlBytes + 1024;
+static_assert((2 * kStages + 2 * kAccBufs + 16) * 8 + 12 <= kCtrlBytes, "control block");
 static_assert(kSmemBytes <= 227 * 1024, "shared memory per CTA");
 
 // 384 threads x 168 registers fill the register file; 128 threads give up 128 each, 256 threads take 64 each.
@@ -158,14 +161,17 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t a_base = base;
   const uint32_t b_base = base + S * kABytes;
   uint8_t* out_stage = smem + S * kStageBytes;  // 1024-byte aligned
-  uint8_t* ctrl = out_stage + kOutStageBytes;
+  float* xamax = reinterpret_cast<float*>(out_stage + kOutStageBytes);
+  uint8_t* ctrl = out_stage + kOutStageBytes + kAmaxBytes;
   const uint32_t bar_full = smem_u32(ctrl);
   const uint32_t bar_empty = bar_full + 8 * S;
   const uint32_t bar_tfull = bar_empty + 8 * S;
   const uint32_t bar_tempty = bar_tfull + 8 * kAccBufs;
-  const uint32_t bar_xfull = bar_tempty + 8 * kAccBufs;  // 4 + 4: gate / up exchange of the SiLU * mul epilogue,
-  const uint32_t bar_xfree = bar_xfull + 8 * 4;          // one pair of barriers per row quadrant
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + (2 * S + 2 * kAccBufs + 8) * 8);
+  // gate / up exchange of the SiLU * mul epilogue: per promotion warp one barrier "your partner's values are in
+  // its buffer" and one "your partner's row maxima are in place (and it has drained your buffer)"
+  const uint32_t bar_xdata = bar_tempty + 8 * kAccBufs;
+  const uint32_t bar_xamax = bar_xdata + 8 * kEpiWarps;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + (2 * S + 2 * kAccBufs + 16) * 8);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -181,9 +187,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(bar_tfull + 8 * i, 1);
       mbar_init(bar_tempty + 8 * i, kEpiWarps);
     }
-    for (int i = 0; i < 4; ++i) {
-      mbar_init(bar_xfull + 8 * i, 1);
-      mbar_init(bar_xfree + 8 * i, 1);
+    for (int i = 0; i < kEpiWarps; ++i) {
+      mbar_init(bar_xdata + 8 * i, 1);
+      mbar_init(bar_xamax + 8 * i, 1);
     }
     init_abort_flag(abort_flag, p.wait_limit_us);
     fence_mbar_init();
@@ -364,93 +370,95 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (!ok) break;
       if constexpr (kSwiglu) {
-        // The up warp (half 1) of a row quadrant hands its 128 values, rounded to 16 bits, to the gate warp (half 0)
-        // through its staging buffer, 64 columns at a time (two bounded barriers per round: filled / drained).
+        // The tile's two column halves are gate and up of the same 128 outputs, held by two warps (same rows).
+        // Each warp finishes 64 of them: the gate warp (half 0) outputs 0..63, the up warp (half 1) outputs 64..127.
+        // It hands the partner the 64 values that one needs (rounded to 16 bits, as the reference's intermediate
+        // tensor is) through its own staging buffer, forms silu(gate) * up for its columns, exchanges the row
+        // maximum (block quantisation) and stores its half of the row's 128-byte line.  Two bounded mbarriers per
+        // warp and tile: "partner's values are in" and "partner's maximum is in, and it has drained my buffer".
         const bool bf = p.out_dtype == TG_BF16;
-        uint8_t* xchg = out_stage + (q + 4) * kOutBufBytes;  // the up warp's buffer; 128-byte rows, swizzled
-        uint8_t* xrow = xchg + lane * 128;
+        uint8_t* my_row = out_stage + e * kOutBufBytes + lane * 128;  // 128-byte rows, 16-byte pieces swizzled
+        const uint8_t* peer_row = out_stage + (e ^ 4) * kOutBufBytes + lane * 128;
         float* acc = reinterpret_cast<float*>(acc2);
+        // (send0 / keep0 are compile-time so that the accumulators stay in registers)
+        auto finish = [&](auto kSend0, auto kKeep0) -> bool {
+          constexpr int send0 = decltype(kSend0)::value;  // first column of what the partner needs
+          constexpr int keep0 = decltype(kKeep0)::value;  // first column of what this warp finishes
+          constexpr bool is_gate = keep0 == 0;
 #pragma unroll
-        for (int r = 0; r < 2 && ok; ++r) {
-          if (half == 1) {
-            // the gate warp has read the previous round out of the buffer
-            if (!__all_sync(0xffffffffu, mbar_wait(bar_xfree + 8 * q, xph ^ 1u, abort_flag))) {
-              report_timeout(p.status, kRoleEpilogue * 1000 + 52);
-              ok = false;
-              break;
-            }
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              const float* v = acc + r * 64 + g * 8;
-              const uint4 o = bf ? make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
-                                              pack_bf16x2(v[6], v[7]))
-                                 : make_uint4(pack_f16x2(v[0], v[1]), pack_f16x2(v[2], v[3]), pack_f16x2(v[4], v[5]),
-                                              pack_f16x2(v[6], v[7]));
-              *reinterpret_cast<uint4*>(xrow + ((g ^ (lane & 7)) << 4)) = o;
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_xfull + 8 * q);  // release: the rows are in shared memory
-          } else {
-            if (!__all_sync(0xffffffffu, mbar_wait(bar_xfull + 8 * q, xph, abort_flag))) {
-              report_timeout(p.status, kRoleEpilogue * 1000 + 53);
-              ok = false;
-              break;
-            }
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              const uint4 u4 = *reinterpret_cast<const uint4*>(xrow + ((g ^ (lane & 7)) << 4));
-              const uint32_t uw[4] = {u4.x, u4.y, u4.z, u4.w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float* a = acc + r * 64 + g * 8 + 2 * j;
-                float u0, u1, g0, g1;
-                if (bf) {
-                  u0 = __uint_as_float(uw[j] << 16);
-                  u1 = __uint_as_float(uw[j] & 0xffff0000u);
-                  g0 = __bfloat162float(__float2bfloat16_rn(a[0]));
-                  g1 = __bfloat162float(__float2bfloat16_rn(a[1]));
-                } else {
-                  const float2 uf = __half22float2(*reinterpret_cast<const __half2*>(&uw[j]));
-                  u0 = uf.x;
-                  u1 = uf.y;
-                  g0 = __half2float(__float2half_rn(a[0]));
-                  g1 = __half2float(__float2half_rn(a[1]));
-                }
-                const float y0 = __fdividef(g0, 1.0f + __expf(-g0)) * u0;
-                const float y1 = __fdividef(g1, 1.0f + __expf(-g1)) * u1;
-                a[0] = bf ? __bfloat162float(__float2bfloat16_rn(y0)) : __half2float(__float2half_rn(y0));
-                a[1] = bf ? __bfloat162float(__float2bfloat16_rn(y1)) : __half2float(__float2half_rn(y1));
-              }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_xfree + 8 * q);  // the buffer may be refilled
-          }
-          xph ^= 1u;
+        for (int g = 0; g < 8; ++g) {
+          const float* v = acc + send0 + g * 8;
+          const uint4 o = bf ? make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                                          pack_bf16x2(v[6], v[7]))
+                             : make_uint4(pack_f16x2(v[0], v[1]), pack_f16x2(v[2], v[3]), pack_f16x2(v[4], v[5]),
+                                          pack_f16x2(v[6], v[7]));
+          *reinterpret_cast<uint4*>(my_row + ((g ^ (lane & 7)) << 4)) = o;
         }
-        if (!ok) break;
-        if (half == 0 && row < tile.row_end) {
-          // this thread now holds the 128 outputs of its row: quantise and store one 128-byte line
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_xdata + 8 * (e ^ 4));  // release: the rows are in shared memory
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_xdata + 8 * e, xph, abort_flag))) {
+          report_timeout(p.status, kRoleEpilogue * 1000 + 52);
+          return false;
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const uint4 u4 = *reinterpret_cast<const uint4*>(peer_row + ((g ^ (lane & 7)) << 4));
+          const uint32_t uw[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float* a = acc + keep0 + g * 8 + 2 * j;
+            float t0, t1, m0, m1;  // the partner's values and this warp's own, both rounded to 16 bits
+            if (bf) {
+              t0 = __uint_as_float(uw[j] << 16);
+              t1 = __uint_as_float(uw[j] & 0xffff0000u);
+              m0 = __bfloat162float(__float2bfloat16_rn(a[0]));
+              m1 = __bfloat162float(__float2bfloat16_rn(a[1]));
+            } else {
+              const float2 tf = __half22float2(*reinterpret_cast<const __half2*>(&uw[j]));
+              t0 = tf.x;
+              t1 = tf.y;
+              m0 = __half2float(__float2half_rn(a[0]));
+              m1 = __half2float(__float2half_rn(a[1]));
+            }
+            const float g0 = is_gate ? m0 : t0, g1 = is_gate ? m1 : t1;
+            const float u0 = is_gate ? t0 : m0, u1 = is_gate ? t1 : m1;
+            const float y0 = __fdividef(g0, 1.0f + __expf(-g0)) * u0;
+            const float y1 = __fdividef(g1, 1.0f + __expf(-g1)) * u1;
+            a[0] = bf ? __bfloat162float(__float2bfloat16_rn(y0)) : __half2float(__float2half_rn(y0));
+            a[1] = bf ? __bfloat162float(__float2bfloat16_rn(y1)) : __half2float(__float2half_rn(y1));
+            amax = fmaxf(amax, fmaxf(fabsf(a[0]), fabsf(a[1])));
+          }
+        }
+        xamax[e * 32 + lane] = amax;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_xamax + 8 * (e ^ 4));  // release: maximum stored, partner's buffer drained
+        if (!__all_sync(0xffffffffu, mbar_wait(bar_xamax + 8 * e, xph, abort_flag))) {
+          report_timeout(p.status, kRoleEpilogue * 1000 + 53);
+          return false;
+        }
+        xph ^= 1u;
+        if (row < tile.row_end) {
+          // quantise this warp's 64 outputs of the row and store its half of the 128-byte line
           float scale = 1.0f;
           if (p.quant_mode == 1) {
-            float amax = 0.f;
-#pragma unroll
-            for (int j = 0; j < 128; ++j) amax = fmaxf(amax, fabsf(acc[j]));
+            amax = fmaxf(amax, xamax[(e ^ 4) * 32 + lane]);
             scale = __fdiv_rn(amax, 448.0f);
             if (scale == 0.f) scale = 1.0f;
           }
           // the outputs are 16-bit values and the scale is RN(16-bit amax / 448): the test-free quotient applies
           const bool fast = p.quant_mode == 1 && q8_scale_is_tame(scale);
           const float rcp = __frcp_rn(scale);
-          const int out_col = tile.col0 >> 1;  // 128 outputs per 256-column tile
+          const int out_col = (tile.col0 >> 1) + keep0;  // 128 outputs per 256-column tile
           uint8_t* dst = reinterpret_cast<uint8_t*>(p.C) + row * p.ldc + out_col;
 #pragma unroll
-          for (int g = 0; g < 8; ++g) {
+          for (int g = 0; g < 4; ++g) {
             uint32_t w[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               float v[4];
 #pragma unroll
-              for (int i = 0; i < 4; ++i) v[i] = acc[g * 16 + j * 4 + i];
+              for (int i = 0; i < 4; ++i) v[i] = acc[keep0 + g * 16 + j * 4 + i];
               if (fast) {
                 const float2 q0 = q8_quot2(make_float2(v[0], v[1]), scale, rcp);
                 const float2 q1 = q8_quot2(make_float2(v[2], v[3]), scale, rcp);
@@ -465,8 +473,13 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             *reinterpret_cast<uint4*>(dst + g * 16) = make_uint4(w[0], w[1], w[2], w[3]);
           }
-          p.y_scale[row * (p.N >> 8) + (tile.col0 >> 8)] = scale;
+          if (is_gate) p.y_scale[row * (p.N >> 8) + (tile.col0 >> 8)] = scale;
         }
+          return true;
+        };
+        ok = half == 0 ? finish(std::integral_constant<int, 64>{}, std::integral_constant<int, 0>{})
+                       : finish(std::integral_constant<int, 0>{}, std::integral_constant<int, 64>{});
+        if (!ok) break;
         continue;
       }
       const int row0 = tile.row0 + q * 32;

@@ -12,6 +12,7 @@
 #include <cuda_fp8.h>
 
 #include <cstdio>
+#include <cstdlib>
 
 #include <type_traits>
 
@@ -180,10 +181,13 @@ __global__ void __launch_bounds__(256)
                  (q8_pair<KIND>(v[4 * k + 2], v[4 * k + 3], scale, r, tame, qmin, qmax) << 16);
     }
     if (live) {
-      if constexpr (EPT == 16)
-        __stcs(reinterpret_cast<uint4*>(y + c * EPT), make_uint4(out[0], out[1], out[2], out[3]));
-      else
+      if constexpr (EPT >= 16) {
+#pragma unroll
+        for (int i = 0; i < EPT / 16; ++i)
+          __stcs(reinterpret_cast<uint4*>(y + c * EPT) + i, make_uint4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]));
+      } else {
         __stcs(reinterpret_cast<uint2*>(y + c * EPT), make_uint2(out[0], out[1]));
+      }
       if ((lane & (tpg - 1)) == 0) {
         const int64_t g = c >> tpg_shift;
         s[dense_scales ? g : scale_index(g, groups_per_row, s_row_stride, s_group_stride)] = scale;
@@ -213,7 +217,7 @@ cudaError_t launch_kind(int kind, uint8_t* y, float* s, const T* x, int64_t n_ch
   return cudaGetLastError();
 }
 
-// group_size 8 runs 8 elements per thread, everything else 16.
+// group_size 8 runs 8 elements per thread, 16-bit inputs with groups >= 32 run 32, everything else 16.
 cudaError_t launch_any(int x_dtype, int kind, uint8_t* y, float* s, const void* x, int64_t numel, int group_size,
                        int64_t gpr, int64_t srs, int64_t sgs, float eps, float qmin, float qmax, int ue8m0,
                        int zero_to_one, int num_sms, cudaStream_t stream) {
@@ -225,6 +229,11 @@ cudaError_t launch_any(int x_dtype, int kind, uint8_t* y, float* s, const void* 
     if (x_dtype == TG_F16) return TG_GQ_LAUNCH(__half, 8);
     return TG_GQ_LAUNCH(float, 8);
   }
+  // 16-bit inputs with groups of 32 or more: 32 elements per thread halve the share of the per-thread work that
+  // does not scale with the elements (shuffles, scale, reciprocal, addresses)
+  const bool wide32 = getenv("TG_GQ16") == nullptr;  // TEMP A/B
+  if (wide32 && group_size >= 32 && x_dtype == TG_BF16) return TG_GQ_LAUNCH(__nv_bfloat16, 32);
+  if (wide32 && group_size >= 32 && x_dtype == TG_F16) return TG_GQ_LAUNCH(__half, 32);
   if (x_dtype == TG_BF16) return TG_GQ_LAUNCH(__nv_bfloat16, 16);
   if (x_dtype == TG_F16) return TG_GQ_LAUNCH(__half, 16);
   return TG_GQ_LAUNCH(float, 16);
