@@ -12,7 +12,6 @@
 #include <cuda_fp8.h>
 
 #include <cstdio>
-#include <cstdlib>
 
 #include <type_traits>
 
@@ -231,9 +230,8 @@ cudaError_t launch_any(int x_dtype, int kind, uint8_t* y, float* s, const void* 
   }
   // 16-bit inputs with groups of 32 or more: 32 elements per thread halve the share of the per-thread work that
   // does not scale with the elements (shuffles, scale, reciprocal, addresses)
-  const bool wide32 = getenv("TG_GQ16") == nullptr;  // TEMP A/B
-  if (wide32 && group_size >= 32 && x_dtype == TG_BF16) return TG_GQ_LAUNCH(__nv_bfloat16, 32);
-  if (wide32 && group_size >= 32 && x_dtype == TG_F16) return TG_GQ_LAUNCH(__half, 32);
+  if (group_size >= 32 && x_dtype == TG_BF16) return TG_GQ_LAUNCH(__nv_bfloat16, 32);
+  if (group_size >= 32 && x_dtype == TG_F16) return TG_GQ_LAUNCH(__half, 32);
   if (x_dtype == TG_BF16) return TG_GQ_LAUNCH(__nv_bfloat16, 16);
   if (x_dtype == TG_F16) return TG_GQ_LAUNCH(__half, 16);
   return TG_GQ_LAUNCH(float, 16);
