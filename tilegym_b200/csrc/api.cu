@@ -96,13 +96,13 @@ int32_t init_device(int dev) {
 enum Knob : int {
   kKnobSplits, kKnobTileRows, kKnobForcePath, kKnobPairMinTiles, kKnob2Cta, kKnobBn, kKnobSmallmWs, kKnobPdl,
   kKnobStaticWeights, kKnobGroupM, kKnobTailDiv, kKnobTmaStore, kKnobBsWideMin, kKnobBsWide,
-  kKnobBsSmallm, kKnobCount
+  kKnobBsSmallm, kKnobGroupOrder, kKnobCount
 };
 const char* const kKnobNames[kKnobCount] = {
     "TILEGYM_B200_SPLITS", "TILEGYM_B200_TILE_ROWS", "TILEGYM_B200_FORCE_PATH", "TILEGYM_B200_PAIR_MIN_TILES",
     "TILEGYM_B200_2CTA", "TILEGYM_B200_BN", "TILEGYM_B200_SMALLM_WS", "TILEGYM_B200_PDL",
     "TILEGYM_B200_STATIC_WEIGHTS", "TILEGYM_B200_GROUP_M", "TILEGYM_B200_TAIL_DIV", "TILEGYM_B200_TMA_STORE",
-    "TILEGYM_B200_BS_WIDE_MIN", "TILEGYM_B200_BS_WIDE", "TILEGYM_B200_BS_SMALLM"};
+    "TILEGYM_B200_BS_WIDE_MIN", "TILEGYM_B200_BS_WIDE", "TILEGYM_B200_BS_SMALLM", "TILEGYM_B200_GROUP_ORDER"};
 struct KnobTable {
   bool loaded = false;
   bool present[kKnobCount] = {};
@@ -772,6 +772,18 @@ int32_t tg_gemm_dense16(const TgTensorDesc* C, const TgTensorDesc* A, const TgTe
   return TG_OK;
 }
 
+// Tile order of the grouped kernel (GemmParams flags bit 6).  With few rows per group (a mixture-of-experts layer:
+// 3-4 row tiles per expert) the column tiles of one row tile run next to each other, so a group's activations and
+// weights are used within one short window and each is read from HBM once; with many rows per group the row tiles
+// vary fastest and the CTAs running together share a few weight panels.  TILEGYM_B200_GROUP_ORDER=1 / 2 forces
+// row-fastest / column-fastest.
+static int grouped_order_flag(int64_t M, int64_t G) {
+  const int forced = knob(kKnobGroupOrder, 0);
+  if (forced == 1) return 0;
+  if (forced == 2) return 64;
+  return (G > 0 && M / G < 512) ? 64 : 0;  // measured: 64 groups x 384 rows -8 % / -5 % (K = 2048 / 1536), 8 x 512 rows +1 %
+}
+
 int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDesc* A, const TgTensorDesc* B,
                                         const TgTensorDesc* As, const TgTensorDesc* Bs, uint64_t m_indptr,
                                         int32_t block_n, int32_t block_k, const TgTensorDesc* bias, float beta,
@@ -838,6 +850,7 @@ int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDes
   p.kb_per_split = p.num_kb;
   p.status = st.status;
   if (knob(kKnobPdl, 1) != 0) p.flags |= 2;  // programmatic dependent launch
+  p.flags |= grouped_order_flag(M, G);
   p.m_indptr = reinterpret_cast<const int32_t*>(m_indptr);
   p.row_scale = reinterpret_cast<const float*>(row_scale);
   p.num_groups = static_cast<int32_t>(G);
@@ -920,6 +933,7 @@ int32_t tg_fp8_gemm_blockscaled_grouped_swiglu(const TgTensorDesc* Y, const TgTe
   p.kb_per_split = p.num_kb;
   p.status = st.status;
   if (knob(kKnobPdl, 1) != 0) p.flags |= 2;
+  p.flags |= grouped_order_flag(M, G);
   p.m_indptr = reinterpret_cast<const int32_t*>(m_indptr);
   p.num_groups = static_cast<int32_t>(G);
   p.y_scale = reinterpret_cast<float*>(Ys->ptr);

@@ -103,9 +103,11 @@ __device__ __forceinline__ TileRef locate_tile(int t, int mtiles, const GemmPara
     r.valid = true;
     return r;
   } else {
-    // m-tiles vary fastest, so the CTAs running together share a few weight panels through L2
-    const int tn = t / mtiles;
-    const int j = t - tn * mtiles;
+    // flags bit 6 clear: m-tiles vary fastest, so the CTAs running together share a few weight panels through L2;
+    // set: the column tiles of one m-tile vary fastest, so a small group's rows and weights are used in one window
+    const bool n_fastest = (p.flags & 64) != 0;
+    const int tn = n_fastest ? t % p.tiles_n : t / mtiles;
+    const int j = n_fastest ? t / p.tiles_n : t - tn * mtiles;
     const int nb_per_group = (p.N + 127) >> 7;
     r.valid = false;
     r.row0 = r.row_end = r.b_row0 = r.bs_row0 = 0;

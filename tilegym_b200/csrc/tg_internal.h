@@ -53,7 +53,8 @@ struct GemmParams {
   // bit 0 (small-M kernel): the weight operand is not written by the kernel that precedes this one on the
   // stream, so its TMA loads may be issued before the programmatic-dependent-launch wait;
   // bit 1: launched with programmatic stream serialization; bit 2: SwiGLU epilogue; bits 3 / 4: bf16 / f16
-  // operands (dense kernel); bit 5: e5m2 instead of e4m3 operands (per-tensor kernels)
+  // operands (dense kernel); bit 5: e5m2 instead of e4m3 operands (per-tensor kernels); bit 6: grouped kernel,
+  // column tiles vary fastest in the tile order
   int32_t flags;
 };
 
