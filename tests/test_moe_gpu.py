@@ -40,11 +40,11 @@ def make_case(T, H, I, E, topk, seed, dtype=torch.float32):
             torch.stack([q for q, _ in q2]), torch.stack([s for _, s in q2]), wts, ids)
 
 
-def test_routing_tables(dev):
-    T, topk, E = 300, 6, 40
+@pytest.mark.parametrize("T,topk,E", [(300, 6, 40), (70000, 4, 100), (64, 2, 5000)])
+def test_routing_tables(dev, T, topk, E):
     g = torch.Generator().manual_seed(1)
     ids = torch.randint(0, E, (T, topk), generator=g, dtype=torch.int32)
-    ids[5, 2] = -3   # invalid ids take part in nothing
+    ids[5, topk - 1] = -3   # invalid ids take part in nothing
     ids[9, 0] = E
     wts = torch.rand(T, topk, generator=g)
     m_indptr, sorted_ids, pos, w_sorted = (t.cpu() for t in moe.moe_route(ids.to(dev), wts.to(dev), E))
