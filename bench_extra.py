@@ -223,6 +223,29 @@ def mlp_block_sweep(dev):
     return res
 
 
+def linear_decode_sweep(dev):
+    """FP8Linear forward on decode-sized bf16 activations (what a converted model's Linear costs per token step):
+    activation quantiser + GEMM, replayed from a CUDA graph over rotating layers so the weights come from HBM."""
+    from tilegym_b200.linear import FP8Linear
+
+    rows = []
+    for name, N, K in (("qkv", 6144, 4096), ("o_proj", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336)):
+        n_layers = max(2, int(4 * 126e6 / (N * K)) + 1)
+        g = torch.Generator(device=dev).manual_seed(N + K)
+        layers = []
+        for _ in range(n_layers):
+            lin = FP8Linear(K, N, bias=False, mode="per_tensor", device=dev)
+            lin.load_weight(torch.randn(N, K, generator=g, device=dev, dtype=torch.bfloat16).mul_(0.02))
+            layers.append(lin)
+        for M in (1, 16, 64):
+            x = torch.randn(M, K, generator=g, device=dev, dtype=torch.bfloat16)
+            us = graph_time_us(lambda i: layers[i](x), n_layers)
+            rows.append({"shape": name, "M": M, "N": N, "K": K, "us_quantise_plus_gemm": round(us, 2)})
+        del layers
+        torch.cuda.empty_cache()
+    return rows
+
+
 def cube_1024(dev, fp8_peak_tflops: float):
     """Benchmark configuration 1: one 1024 x 1024 x 1024 per-tensor GEMM (2.1 GFLOP, 4 MB: launch-bound)."""
     import tilegym_b200 as tg
@@ -327,4 +350,5 @@ def run(dev, peaks):
         "quantisers": quantiser_sweep(dev, hbm),
         "swiglu_gate_up": swiglu_sweep(dev),
         "llama8b_mlp_block": mlp_block_sweep(dev),
+        "fp8linear_decode": linear_decode_sweep(dev),
     }

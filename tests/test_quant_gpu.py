@@ -69,6 +69,21 @@ def test_quant_per_tensor(dev, shape, dtype):
     assert torch.equal(s.cpu(), sr) and same_bits(q, qr)
 
 
+@pytest.mark.parametrize("shape", [(1, 8), (1, 4096), (16, 4096), (9, 14336), (64, 4096), (31, 8200), (64, 4104)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_quant_per_tensor_decode_sizes(dev, shape, dtype):
+    """Up to 262144 16-bit elements the quantiser is one launch (a cluster of 1 .. 8 CTAs holding the tensor in
+    registers); the last shape is just past it and takes the two-pass form.  Same bytes and scale as the oracle."""
+    x = R.gen_activations(shape[0], shape[1], 7).to(dtype)
+    q, s = tg.quant_per_tensor(x.to(dev))
+    qr, sr = R.ref_quant_per_tensor(x)
+    assert torch.equal(s.cpu(), sr) and same_bits(q, qr)
+    z = torch.zeros(shape, dtype=dtype, device=dev)
+    z[-1, -1] = -0.0
+    q, s = tg.quant_per_tensor(z)
+    assert float(s) == 1.0 and float(q.float().abs().max()) == 0.0
+
+
 def test_quant_per_tensor_all_zero(dev):
     q, s = tg.quant_per_tensor(torch.zeros(8, 64, device=dev))
     assert float(s) == 1.0 and float(q.float().abs().max()) == 0.0

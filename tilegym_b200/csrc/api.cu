@@ -96,13 +96,13 @@ int32_t init_device(int dev) {
 enum Knob : int {
   kKnobSplits, kKnobTileRows, kKnobForcePath, kKnobPairMinTiles, kKnob2Cta, kKnobBn, kKnobSmallmWs, kKnobPdl,
   kKnobStaticWeights, kKnobGroupM, kKnobTailDiv, kKnobTmaStore, kKnobBsWideMin, kKnobBsWide,
-  kKnobBsSmallm, kKnobGroupOrder, kKnobCount
+  kKnobBsSmallm, kKnobGroupOrder, kKnobQuantFused, kKnobCount
 };
 const char* const kKnobNames[kKnobCount] = {
     "TILEGYM_B200_SPLITS", "TILEGYM_B200_TILE_ROWS", "TILEGYM_B200_FORCE_PATH", "TILEGYM_B200_PAIR_MIN_TILES",
     "TILEGYM_B200_2CTA", "TILEGYM_B200_BN", "TILEGYM_B200_SMALLM_WS", "TILEGYM_B200_PDL",
     "TILEGYM_B200_STATIC_WEIGHTS", "TILEGYM_B200_GROUP_M", "TILEGYM_B200_TAIL_DIV", "TILEGYM_B200_TMA_STORE",
-    "TILEGYM_B200_BS_WIDE_MIN", "TILEGYM_B200_BS_WIDE", "TILEGYM_B200_BS_SMALLM", "TILEGYM_B200_GROUP_ORDER"};
+    "TILEGYM_B200_BS_WIDE_MIN", "TILEGYM_B200_BS_WIDE", "TILEGYM_B200_BS_SMALLM", "TILEGYM_B200_GROUP_ORDER", "TILEGYM_B200_QUANT_FUSED"};
 struct KnobTable {
   bool loaded = false;
   bool present[kKnobCount] = {};
@@ -1169,6 +1169,7 @@ int32_t tg_quant_pertensor(const TgTensorDesc* Y, uint64_t scale_out, const TgTe
   cudaError_t e = launch_quant_pertensor(reinterpret_cast<uint8_t*>(Y->ptr), reinterpret_cast<float*>(scale_out),
                                          reinterpret_cast<const void*>(X->ptr), X->dtype, n,
                                          reinterpret_cast<uint32_t*>(amax_scratch), g_dev[device_id].num_sms,
+                                         knob(kKnobQuantFused, 1) != 0,  // TILEGYM_B200_QUANT_FUSED=0: always two passes
                                          reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(TG_ERR_LAUNCH, "quant_pertensor launch failed: %s", cudaGetErrorString(e));
   return TG_OK;

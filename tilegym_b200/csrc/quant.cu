@@ -210,6 +210,113 @@ __global__ void __launch_bounds__(256) tg_quant_pertensor16_kernel(uint8_t* __re
   }
 }
 
+// Small inputs (decode-sized activations) in ONE launch instead of clear + amax + quantise: a thread-block cluster
+// of up to 8 CTAs x 512 threads holds the whole tensor in registers (up to 64 elements per thread), reduces |x| to
+// the block maximum, exchanges the block maxima through distributed shared memory (one cluster barrier), and
+// quantises what it holds.  Same arithmetic as the two-pass form (amax / 448 by IEEE division, 1.0 for all zeros,
+// test-free exact quotient), so the bytes are the same.  16-bit inputs, 16-byte aligned, size a multiple of 8.
+constexpr int kFusedThreads = 512;
+constexpr int kFusedVecs = 8;  // 16-byte vectors (8 elements each) a thread may hold: 32 registers of data
+template <typename T>
+__global__ void __launch_bounds__(kFusedThreads, 1)
+    tg_quant_pertensor_fused_kernel(uint8_t* __restrict__ y, float* scale_out, const T* __restrict__ x, int64_t n_vecs) {
+  __shared__ float warp_max_s[32];
+  __shared__ float cta_max_s[8];  // one slot per CTA of the cluster, written by that CTA into every peer
+  uint32_t n_ctas, rank;
+  asm volatile("mov.u32 %0, %%cluster_nctaid.x;" : "=r"(n_ctas));
+  asm volatile("mov.u32 %0, %%cluster_ctaid.x;" : "=r"(rank));
+  // "this CTA runs": a peer's shared memory may only be written once that peer has started (waited for below)
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+  const int64_t stride = static_cast<int64_t>(n_ctas) * kFusedThreads;
+  const int64_t first = static_cast<int64_t>(rank) * kFusedThreads + threadIdx.x;
+  uint4 v[kFusedVecs];
+  float m = 0.f;
+#pragma unroll
+  for (int i = 0; i < kFusedVecs; ++i) {
+    const int64_t c = first + i * stride;
+    v[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (c < n_vecs) v[i] = __ldg(reinterpret_cast<const uint4*>(x) + c);
+    const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f;
+      if constexpr (std::is_same<T, __half>::value) f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+      else f = make_float2(__uint_as_float(w[j] << 16), __uint_as_float(w[j] & 0xffff0000u));
+      m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  }
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) warp_max_s[threadIdx.x >> 5] = m;
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");  // every CTA of the cluster has started
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = warp_max(threadIdx.x < kFusedThreads / 32 ? warp_max_s[threadIdx.x] : 0.f);
+    // lane r publishes this CTA's maximum in slot `rank` of CTA r's table
+    if (threadIdx.x < n_ctas) {
+      uint32_t local = static_cast<uint32_t>(__cvta_generic_to_shared(&cta_max_s[rank])), remote;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(threadIdx.x));
+      asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(t) : "memory");
+    }
+  }
+  // every CTA's maximum is in every table after this barrier (also orders the warp_max_s use inside the CTA)
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  float amax = 0.f;
+  for (uint32_t r = 0; r < n_ctas; ++r) amax = fmaxf(amax, cta_max_s[r]);
+  float scale = __fdiv_rn(amax, kE4M3Max);
+  if (scale == 0.f) scale = 1.0f;
+  if (rank == 0 && threadIdx.x == 0) *scale_out = scale;
+  const bool tame = q8_scale_is_tame(scale);
+  const float r = __frcp_rn(scale);
+#pragma unroll
+  for (int i = 0; i < kFusedVecs; ++i) {
+    const int64_t c = first + i * stride;
+    if (c >= n_vecs) break;
+    const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+    uint32_t out[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      float2 x0, x1;
+      if constexpr (std::is_same<T, __half>::value) {
+        x0 = __half22float2(*reinterpret_cast<const __half2*>(&w[2 * k]));
+        x1 = __half22float2(*reinterpret_cast<const __half2*>(&w[2 * k + 1]));
+      } else {
+        x0 = make_float2(__uint_as_float(w[2 * k] << 16), __uint_as_float(w[2 * k] & 0xffff0000u));
+        x1 = make_float2(__uint_as_float(w[2 * k + 1] << 16), __uint_as_float(w[2 * k + 1] & 0xffff0000u));
+      }
+      if (tame) {
+        const float2 q0 = q8_quot2(x0, scale, r), q1 = q8_quot2(x1, scale, r);
+        out[k] = q8_cast2<kQ8E4M3>(q0.x, q0.y, -kE4M3Max, kE4M3Max) | (q8_cast2<kQ8E4M3>(q1.x, q1.y, -kE4M3Max, kE4M3Max) << 16);
+      } else {
+        out[k] = q8_pair<kQ8E4M3>(x0.x, x0.y, scale, r, false, -kE4M3Max, kE4M3Max) |
+                 (q8_pair<kQ8E4M3>(x1.x, x1.y, scale, r, false, -kE4M3Max, kE4M3Max) << 16);
+      }
+    }
+    *(reinterpret_cast<uint2*>(y) + c) = make_uint2(out[0], out[1]);
+  }
+}
+
+template <typename T>
+cudaError_t launch_quant_pertensor_fused(uint8_t* y, float* scale_out, const T* x, int64_t numel, cudaStream_t stream) {
+  const int64_t n_vecs = numel / 8;
+  const int64_t per_cta = static_cast<int64_t>(kFusedThreads) * kFusedVecs;
+  int ctas = static_cast<int>((n_vecs + per_cta - 1) / per_cta);
+  if (ctas < 1) ctas = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(ctas), 1, 1);
+  cfg.blockDim = dim3(kFusedThreads, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(ctas);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, tg_quant_pertensor_fused_kernel<T>, y, scale_out, x, n_vecs);
+}
+
 // ------------------------------------------------------- 128x128 weight quant
 // One CTA per 128 x 128 block; thread t owns columns 4*(t%32) .. +3 of rows
 // t/32, t/32+8, ... (16 rows), keeps them in registers across the block-wide
@@ -300,7 +407,15 @@ cudaError_t launch_weight_dequant(void* y, int y_dtype, const uint8_t* x, const 
 }
 
 cudaError_t launch_quant_pertensor(uint8_t* y, float* scale_out, const void* x, int x_dtype, int64_t numel,
-                                   uint32_t* amax_scratch, int num_sms, cudaStream_t stream) {
+                                   uint32_t* amax_scratch, int num_sms, bool allow_single_launch, cudaStream_t stream) {
+  // up to 8 CTAs x 512 threads x 64 elements (262144 in all): the whole tensor fits one cluster's registers
+  const bool fused = allow_single_launch && x_dtype != TG_F32 && numel > 0 && numel % 8 == 0 && numel <= 8ll * kFusedThreads * kFusedVecs * 8 &&
+                     ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(y) & 7u) == 0);
+  if (fused) {
+    if (x_dtype == TG_BF16)
+      return launch_quant_pertensor_fused(y, scale_out, static_cast<const __nv_bfloat16*>(x), numel, stream);
+    return launch_quant_pertensor_fused(y, scale_out, static_cast<const __half*>(x), numel, stream);
+  }
   cudaError_t e = cudaMemsetAsync(amax_scratch, 0, sizeof(uint32_t), stream);
   if (e != cudaSuccess) return e;
   const int grid = grid_for((numel + 3) / 4, 256, num_sms * 8);

@@ -116,7 +116,7 @@ cudaError_t launch_act_quant(void* y, float* s, const void* x, int x_dtype, int6
 cudaError_t launch_weight_dequant(void* y, int y_dtype, const uint8_t* x, const float* s, int64_t M, int64_t N,
                                   int64_t lds, cudaStream_t stream);
 cudaError_t launch_quant_pertensor(uint8_t* y, float* scale_out, const void* x, int x_dtype, int64_t numel,
-                                   uint32_t* amax_scratch, int num_sms, cudaStream_t stream);
+                                   uint32_t* amax_scratch, int num_sms, bool allow_single_launch, cudaStream_t stream);
 cudaError_t launch_weight_quant_block(uint8_t* y, float* s, const void* x, int x_dtype, int64_t N, int64_t K,
                                       int64_t lds, cudaStream_t stream);
 
