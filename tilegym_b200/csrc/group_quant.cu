@@ -95,6 +95,7 @@ __global__ void __launch_bounds__(256)
                                     int64_t n_chunks, int tpg, int64_t groups_per_row, int64_t s_row_stride,
                                     int64_t s_group_stride, float eps, float qmin, float qmax, float qmax_rcp,
                                     int ue8m0, int zero_to_one, int dense_scales) {
+  q8_allow_dependents();
   const int lane = threadIdx.x & 31;
   const int tpg_shift = 31 - __clz(tpg);
   const int64_t span = static_cast<int64_t>(gridDim.x) * blockDim.x;

@@ -168,6 +168,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) tg_quant_pertensor16_kernel(uint8_t* __restrict__ y, float* scale_out,
                                                                    const T* __restrict__ x, int64_t n_chunks,
                                                                    const uint32_t* amax_bits) {
+  q8_allow_dependents();
   float scale = __fdiv_rn(__uint_as_float(*amax_bits), kE4M3Max);
   if (scale == 0.f) scale = 1.0f;
   if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
@@ -222,6 +223,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
     tg_quant_pertensor_fused_kernel(uint8_t* __restrict__ y, float* scale_out, const T* __restrict__ x, int64_t n_vecs) {
   __shared__ float warp_max_s[32];
   __shared__ float cta_max_s[8];  // one slot per CTA of the cluster, written by that CTA into every peer
+  q8_allow_dependents();
   uint32_t n_ctas, rank;
   asm volatile("mov.u32 %0, %%cluster_nctaid.x;" : "=r"(n_ctas));
   asm volatile("mov.u32 %0, %%cluster_ctaid.x;" : "=r"(rank));

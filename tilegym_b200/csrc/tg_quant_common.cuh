@@ -16,6 +16,12 @@ namespace tg {
 
 enum Q8Kind : int { kQ8E4M3 = 0, kQ8E5M2 = 1, kQ8Int8 = 2 };
 
+// Programmatic dependent launch, primary side: a kernel launched behind this one with programmatic stream
+// serialization (the GEMMs are) may be scheduled from now on and run the part in front of its griddepcontrol.wait -
+// barrier set-up, TMEM allocation, streaming weights declared static - while the quantiser still works; what it reads
+// of the quantiser's output it reads after that wait, which returns when this grid has completed.
+__device__ __forceinline__ void q8_allow_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // The reciprocal path needs a scale whose reciprocal and products stay in the normal range; the elements of a
 // group whose scale is outside it all take __fdiv_rn.
 __device__ __forceinline__ bool q8_scale_is_tame(float s) { return s > 1e-20f && s < 1e20f; }
