@@ -190,8 +190,10 @@ TG_API int32_t tg_fp8_gemm_blockscaled_grouped_swiglu(const TgTensorDesc* Y, con
 /* Between the two expert GEMMs: a = silu(X[:, :I]) * X[:, I:] in fp32, rounded to X's 16-bit type (the reference's
  * intermediate tensor, moe_interface.py:262-267), then quantised to e4m3 for the second GEMM.  mode 0: scale 1 and
  * a saturating cast, the reference's a2_scale of ones (moe_interface.py:269-279); mode 1: one scale amax / 448 per
- * 128 elements (1 for an all-zero group), IEEE division.  X: (R, 2 I) bf16 / f16, I % 128 == 0; Y: (R, I) e4m3;
- * S: (R, I / 128) f32; only the first m_indptr[E] rows are processed. */
+ * 128 elements (1 for an all-zero group), IEEE division.  Adding 2 to mode says that X's columns are interleaved in
+ * blocks of 128 (gate, up, gate, up, ...: what the first GEMM writes when its weight rows were rearranged for the fused
+ * epilogue).  X: (R, 2 I) bf16 / f16, I % 128 == 0; Y: (R, I) e4m3; S: (R, I / 128) f32; only the first m_indptr[E]
+ * rows are processed. */
 TG_API int32_t tg_moe_silu_mul_quant(const TgTensorDesc* Y, const TgTensorDesc* S, const TgTensorDesc* X, uint64_t m_indptr,
                                      int32_t num_experts, int32_t mode, int32_t device_id, uint64_t stream);
 

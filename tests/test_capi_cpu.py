@@ -146,7 +146,7 @@ def test_moe_argument_checks():
                                  _d(a_s), p, p, 4, 2, 0, 0) == -6                         # more rows than tokens x top_k
     x = torch.zeros(4, 512, dtype=torch.bfloat16)
     y = torch.zeros(4, 256, dtype=torch.float8_e4m3fn)
-    assert L.tg_moe_silu_mul_quant(_d(y), _d(torch.zeros(4, 2)), _d(x), p, 4, 2, 0, 0) == -6  # mode
+    assert L.tg_moe_silu_mul_quant(_d(y), _d(torch.zeros(4, 2)), _d(x), p, 4, 4, 0, 0) == -6  # mode
     assert L.tg_moe_silu_mul_quant(_d(y), _d(torch.zeros(4, 3)), _d(x), p, 4, 0, 0, 0) == -6
     assert L.tg_moe_silu_mul_quant(_d(y), _d(torch.zeros(4, 2)), _d(x.float()), p, 4, 0, 0, 0) == -2
     c = torch.zeros(16, 256, dtype=torch.bfloat16)

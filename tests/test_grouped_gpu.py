@@ -61,6 +61,55 @@ def test_ragged_unaligned_and_empty_groups(dev, out_dtype):
     _lib.device_status(dev.index)
 
 
+@pytest.mark.parametrize("tile", ["32", "64", None])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32, torch.float16])
+def test_small_groups_take_the_swap_ab_kernel(dev, tile, out_dtype):
+    """Groups of a few rows (a mixture-of-experts layer at decode sizes) run on the grouped form of the small-M
+    kernel: groups of 1 row, empty groups, groups longer than the 32- / 64-row tile (two or three tiles), N not a
+    multiple of 128, K not a multiple of 128, bias per group and a factor per row."""
+    sizes = [1, 0, 7, 33, 2, 0, 0, 70, 5, 1, 16, 3, 0, 9, 32, 4]
+    N, K = 328, 400
+    a8, b, As, bs, ind = make_case(sizes, N, K, seed=17)
+    g = torch.Generator().manual_seed(5)
+    bias = torch.randn(len(sizes), N, generator=g).to(torch.bfloat16)
+    rs = torch.rand(sum(sizes), generator=g) + 0.25
+    ref = R.ref_ragged_block_scaled_bmm(a8, b, As, bs, ind, out_dtype=torch.float32)
+    lo = 0
+    for q, sz in enumerate(sizes):
+        ref[lo:lo + sz] = ref[lo:lo + sz] * rs[lo:lo + sz, None] + bias[q].float()
+        lo += sz
+    ref = ref.to(out_dtype)
+    _lib.set_knob("TILEGYM_B200_GROUPED_SMALLM", tile)
+    try:
+        out = tg.ragged_block_scaled_bmm(a8.to(dev), b.to(dev), As.to(dev), bs.to(dev), ind.to(dev), max(sizes),
+                                         out_dtype=out_dtype, bias=bias.to(dev), row_scale=rs.to(dev))
+        torch.cuda.synchronize(dev)
+    finally:
+        _lib.set_knob("TILEGYM_B200_GROUPED_SMALLM", None)
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(out.cpu(), ref, rtol=1e-4, atol=1e-4 * float(ref.abs().max()))
+    else:
+        res = R.check_tolerance(out.float(), ref.float())
+        assert res["ok"], res
+    _lib.device_status(dev.index)
+
+
+def test_small_group_kernel_equals_the_tile_kernel_bit_for_bit(dev):
+    """Same k-block order and the same fused multiply-adds per element: the two grouped kernels agree exactly."""
+    sizes = [3, 20, 0, 31, 8, 1, 12, 5]
+    a8, b, As, bs, ind = make_case(sizes, 512, 1024, seed=23)
+    args = [t.to(dev) for t in (a8, b, As, bs, ind)]
+    outs = {}
+    for tile in ("0", "32", "64"):
+        _lib.set_knob("TILEGYM_B200_GROUPED_SMALLM", tile)
+        try:
+            outs[tile] = tg.ragged_block_scaled_bmm(*args, max(sizes)).clone()
+        finally:
+            _lib.set_knob("TILEGYM_B200_GROUPED_SMALLM", None)
+    assert torch.equal(outs["0"], outs["32"]) and torch.equal(outs["0"], outs["64"])
+    _lib.device_status(dev.index)
+
+
 def test_each_group_equals_the_dense_kernel(dev):
     """Per group the grouped kernel runs the same k-block order and the same fused multiply-adds as the dense
     block-scaled kernel: identical bits."""

@@ -96,13 +96,14 @@ int32_t init_device(int dev) {
 enum Knob : int {
   kKnobSplits, kKnobTileRows, kKnobForcePath, kKnobPairMinTiles, kKnob2Cta, kKnobBn, kKnobSmallmWs, kKnobPdl,
   kKnobStaticWeights, kKnobGroupM, kKnobTailDiv, kKnobTmaStore, kKnobBsWideMin, kKnobBsWide,
-  kKnobBsSmallm, kKnobGroupOrder, kKnobQuantFused, kKnobCount
+  kKnobBsSmallm, kKnobGroupOrder, kKnobQuantFused, kKnobGroupedSmallm, kKnobCount
 };
 const char* const kKnobNames[kKnobCount] = {
     "TILEGYM_B200_SPLITS", "TILEGYM_B200_TILE_ROWS", "TILEGYM_B200_FORCE_PATH", "TILEGYM_B200_PAIR_MIN_TILES",
     "TILEGYM_B200_2CTA", "TILEGYM_B200_BN", "TILEGYM_B200_SMALLM_WS", "TILEGYM_B200_PDL",
     "TILEGYM_B200_STATIC_WEIGHTS", "TILEGYM_B200_GROUP_M", "TILEGYM_B200_TAIL_DIV", "TILEGYM_B200_TMA_STORE",
-    "TILEGYM_B200_BS_WIDE_MIN", "TILEGYM_B200_BS_WIDE", "TILEGYM_B200_BS_SMALLM", "TILEGYM_B200_GROUP_ORDER", "TILEGYM_B200_QUANT_FUSED"};
+    "TILEGYM_B200_BS_WIDE_MIN", "TILEGYM_B200_BS_WIDE", "TILEGYM_B200_BS_SMALLM", "TILEGYM_B200_GROUP_ORDER", "TILEGYM_B200_QUANT_FUSED",
+    "TILEGYM_B200_GROUPED_SMALLM"};
 struct KnobTable {
   bool loaded = false;
   bool present[kKnobCount] = {};
@@ -854,6 +855,30 @@ int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDes
   p.m_indptr = reinterpret_cast<const int32_t*>(m_indptr);
   p.row_scale = reinterpret_cast<const float*>(row_scale);
   p.num_groups = static_cast<int32_t>(G);
+  // Few rows per group (a mixture-of-experts layer at decode sizes): the swap-AB small-M kernel in its grouped form
+  // streams each group's weights once for a 32- or 64-row tile instead of a 128-row one, of which most would be
+  // other groups' rows.  TILEGYM_B200_GROUPED_SMALLM=0 switches it off, 32 / 64 force the tile height.
+  {
+    const int forced = knob(kKnobGroupedSmallm, -1);
+    int mp = 0;
+    if (forced == 32 || forced == 64) mp = forced;
+    else if (forced != 0) mp = M <= 24 * G ? 32 : (M <= 64 * G ? 64 : 0);  // measured cross-overs (64 groups, K = 2048 / 1536)
+    if (mp != 0 && beta == 0.0f && KB <= blockscaled_smallm_max_kb_per_cta()) {
+      const int64_t mbound = (M + mp - 1) / mp + G;
+      if (mbound * NB <= 0x3fffffff) {
+        p.tiles_m = 1;
+        p.tiles_n = static_cast<int32_t>(NB);
+        p.mtile_bound = static_cast<int32_t>(mbound);
+        CUtensorMap tmW, tmX;
+        if ((rc = make_map(&tmW, B->ptr, G * N, K, K, 128)) != TG_OK) return rc;  // B viewed as [G * N, K]
+        if ((rc = make_map(&tmX, A->ptr, M, K, A->strides[0], mp)) != TG_OK) return rc;
+        cudaError_t e0 = launch_gemm_blockscaled_smallm_grouped(tmW, tmX, p, mp, cs);
+        if (e0 != cudaSuccess)
+          return fail(TG_ERR_LAUNCH, "grouped block-scaled GEMM (small groups) launch failed: %s", cudaGetErrorString(e0));
+        return TG_OK;
+      }
+    }
+  }
   // every group adds at most one partly filled 128-row tile to the ceil(M / 128) a dense problem would have
   const int64_t bound = (M + 127) / 128 + G;
   if (bound * p.tiles_n > 0x3fffffff) return fail(TG_ERR_ARGS, "problem has too many tiles");

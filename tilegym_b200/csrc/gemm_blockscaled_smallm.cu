@@ -45,12 +45,14 @@ namespace {
 constexpr int kThreads = 192;
 constexpr int kMaxKbPerCta = 32;  // k-blocks one CTA may own (rows of the staged scale table)
 
-template <int MP>
+// TWO: sized for two CTAs per SM (the grouped form: one short work unit per CTA, so one CTA's start-up runs beside
+// the other's weight stream; half the stages each keep the bytes in flight per SM the same).
+template <int MP, bool TWO = false>
 struct BsmCfg {
   static constexpr int kWBytes = kBM * kBK;  // 128 weight rows x 128 B per stage
   static constexpr int kXBytes = MP * kBK;
   static constexpr int kStageBytes = kWBytes + kXBytes;
-  static constexpr int kStages = (MP == 128) ? 6 : 8;
+  static constexpr int kStages = TWO ? 4 : ((MP == 128) ? 6 : 8);
   static constexpr int kTmemCols = 2 * MP;  // two partial-product buffers
   // After the main loop the operand stages are idle and hold (a) this CTA's fp32 partial tile [MP][128] (the
   // unsplit path: the transposition tile of the output) and (b) the cluster reduction inbox: the partial rows
@@ -64,7 +66,8 @@ struct BsmCfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + kScaleBytes + kCtrlBytes + 1024;
   static_assert(kInboxBytes <= kStages * kStageBytes, "tile and inbox lie over the stages");
   static_assert((2 * kStages + 6) * 8 + 12 <= kCtrlBytes, "control block");
-  static_assert(kSmemBytes <= 227 * 1024, "shared memory per CTA");
+  static_assert(kSmemBytes * (TWO ? 2 : 1) <= 227 * 1024, "shared memory per SM");
+  static_assert(kTmemCols * (TWO ? 2 : 1) <= 512, "TMEM columns per SM");
 };
 
 template <typename T>
@@ -115,11 +118,58 @@ __device__ __forceinline__ void bsm_store_column(T* c, int64_t ldc, const float 
     if (m < mv) c[m * ldc] = bsm_cast<T>(acc[m] + bias);
 }
 
-template <int MP, bool CLUSTER>
-__global__ void __launch_bounds__(kThreads, 1)
+// Grouped form (GROUPED, never split): the mixture-of-experts GEMM when every expert has few rows.  Rows
+// [m_indptr[g], m_indptr[g + 1]) of X use weight g (W viewed as [groups * N, K]); the MP-row tiles of all groups are
+// numbered densely, one CTA per (row tile, 128 weight rows), the grid sized by the host's bound on the tile count;
+// a CTA beyond the real count leaves at once.  Rows of the X tile past the end of its group belong to other groups:
+// their scales are staged as 0 and they are never stored.
+struct BsmGroupTile {
+  int group;
+  int row0;   // first row of X, As and C
+  int rows;   // valid rows of the tile (<= MP)
+  int valid;
+};
+
+template <int MP>
+__device__ __forceinline__ BsmGroupTile bsm_locate_group_tile(int j, const GemmParams& p, int lane) {
+  BsmGroupTile r = {0, 0, 0, 0};
+  int before = 0;  // tiles of the groups already scanned
+  for (int g0 = 0; g0 < p.num_groups; g0 += 32) {
+    const int g = g0 + lane;
+    // clamped to [0, M]: whatever the offsets hold, no row outside X / C is ever touched
+    const int beg = g < p.num_groups ? min(max(__ldg(p.m_indptr + g), 0), p.M) : 0;
+    const int end = g < p.num_groups ? min(max(__ldg(p.m_indptr + g + 1), 0), p.M) : 0;
+    const int tiles = end > beg ? (end - beg + MP - 1) / MP : 0;
+    int incl = tiles;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    const int excl = before + incl - tiles;
+    const bool mine = tiles > 0 && j >= excl && j < excl + tiles;
+    const unsigned hit = __ballot_sync(0xffffffffu, mine);
+    if (hit != 0u) {
+      const int src = __ffs(hit) - 1;
+      const int gbeg = __shfl_sync(0xffffffffu, beg, src), gend = __shfl_sync(0xffffffffu, end, src);
+      const int gexcl = __shfl_sync(0xffffffffu, excl, src);
+      r.group = g0 + src;
+      r.row0 = gbeg + (j - gexcl) * MP;
+      r.rows = min(MP, gend - r.row0);
+      r.valid = 1;
+      return r;
+    }
+    before += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  return r;
+}
+
+template <int MP, bool CLUSTER, bool GROUPED = false>
+__global__ void __launch_bounds__(kThreads, GROUPED ? 2 : 1)
     tg_fp8_gemm_blockscaled_smallm_kernel(const __grid_constant__ CUtensorMap tmW,
                                           const __grid_constant__ CUtensorMap tmX, const GemmParams p) {
-  using Cfg = BsmCfg<MP>;
+  static_assert(!(GROUPED && CLUSTER), "the grouped form is never split");
+  using Cfg = BsmCfg<MP, GROUPED>;
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -146,10 +196,39 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   // one work unit per CTA: weight-row tile tn (128 rows = one row of Bs), K split sp
   const int u = blockIdx.x;
-  const int tn = u / p.splits, sp = u - tn * p.splits;
+  int tn, sp;
+  int x_row0 = 0;              // first activation row of the tile (grouped form)
+  int mv_tile = p.M < MP ? p.M : MP;  // valid activation rows
+  int64_t w_row0;              // first weight row in the [groups * N, K] view
+  int64_t bs_row;              // row of Bs
+  int64_t bias_off = 0;        // grouped form: offset of the group's bias row
+  if constexpr (GROUPED) {
+    // m_indptr comes from the kernel in front (the routing): nothing of this CTA may run ahead of it
+    griddep_wait();
+    __shared__ BsmGroupTile gt_s;
+    tn = u % p.tiles_n;
+    sp = 0;
+    if (warp == 0) {
+      const BsmGroupTile gt = bsm_locate_group_tile<MP>(u / p.tiles_n, p, lane);
+      if (lane == 0) gt_s = gt;
+    }
+    __syncthreads();
+    const BsmGroupTile gt = gt_s;
+    if (!gt.valid) return;  // beyond the last tile: the whole CTA leaves before it owns anything
+    x_row0 = gt.row0;
+    mv_tile = gt.rows;
+    w_row0 = static_cast<int64_t>(gt.group) * p.N + static_cast<int64_t>(tn) * kBM;
+    bs_row = static_cast<int64_t>(gt.group) * p.tiles_n + tn;
+    bias_off = static_cast<int64_t>(gt.group) * p.N;
+  } else {
+    tn = u / p.splits;
+    sp = u - tn * p.splits;
+    w_row0 = static_cast<int64_t>(tn) * kBM;
+    bs_row = tn;
+  }
   const int kb0 = sp * p.kb_per_split;
   const int kb1 = min(kb0 + p.kb_per_split, p.num_kb);
-  const int row0 = tn * kBM;
+  const int row0 = tn * kBM;  // first output column of the tile (within the group)
   uint64_t pol_w = 0, pol_x = 0;
   int pre = 0;  // k-blocks whose loads were issued before the set-up barrier
 
@@ -188,11 +267,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (!early_w) griddep_wait();
     for (int i = 0; i < pre; ++i) {
       mbar_arrive_expect_tx(bar_full + 8 * i, Cfg::kStageBytes);
-      tma_load_2d_hint(w_base + i * Cfg::kWBytes, &tmW, bar_full + 8 * i, (kb0 + i) * kBK, row0, pol_w);
+      tma_load_2d_hint(w_base + i * Cfg::kWBytes, &tmW, bar_full + 8 * i, (kb0 + i) * kBK, static_cast<int>(w_row0), pol_w);
     }
     if (early_w) griddep_wait();
     for (int i = 0; i < pre; ++i)
-      tma_load_2d_hint(x_base + i * Cfg::kXBytes, &tmX, bar_full + 8 * i, (kb0 + i) * kBK, 0, pol_x);
+      tma_load_2d_hint(x_base + i * Cfg::kXBytes, &tmX, bar_full + 8 * i, (kb0 + i) * kBK, x_row0, pol_x);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
@@ -205,7 +284,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   griddep_wait();  // every thread: no global read or write below may overtake the previous kernel
   if (threadIdx.x == 0) TG_BSM_STAMP(1);
 
-  const int mv = p.M < MP ? p.M : MP;
+  const int mv = mv_tile;
   const int q = warp & 3;
   const int n_local = q * 32 + lane;
   const int64_t n = static_cast<int64_t>(row0) + n_local;
@@ -227,8 +306,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (elected) {
         mbar_arrive_expect_tx(bar_full + 8 * s, Cfg::kStageBytes);
-        tma_load_2d_hint(w_base + s * Cfg::kWBytes, &tmW, bar_full + 8 * s, kb * kBK, row0, pol_w);
-        tma_load_2d_hint(x_base + s * Cfg::kXBytes, &tmX, bar_full + 8 * s, kb * kBK, 0, pol_x);
+        tma_load_2d_hint(w_base + s * Cfg::kWBytes, &tmW, bar_full + 8 * s, kb * kBK, static_cast<int>(w_row0), pol_w);
+        tma_load_2d_hint(x_base + s * Cfg::kXBytes, &tmX, bar_full + 8 * s, kb * kBK, x_row0, pol_x);
       }
       __syncwarp();
       if (++s == S) {
@@ -278,12 +357,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     {
       const int t = threadIdx.x - 64;
       const int nkb = kb1 - kb0;
-      const float* bs_row = p.Bs + static_cast<int64_t>(tn) * p.ldbs + kb0;
+      const float* bs_ptr = p.Bs + bs_row * p.ldbs + kb0;
       for (int m = t; m < MP; m += 128) {
-        const float* as_row = p.As + static_cast<int64_t>(m < p.M ? m : 0) * p.ldas + kb0;
+        const float* as_row = p.As + static_cast<int64_t>(m < mv ? x_row0 + m : 0) * p.ldas + kb0;
 #pragma unroll 8
         for (int j = 0; j < nkb; ++j)  // independent loads: several are in flight at once
-          sc_tab[j * MP + m] = (m < p.M) ? __ldg(as_row + j) * __ldg(bs_row + j) : 0.f;
+          sc_tab[j * MP + m] = (m < mv) ? __ldg(as_row + j) * __ldg(bs_ptr + j) : 0.f;
       }
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");  // the four promotion warps: the table is complete
@@ -360,28 +439,36 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   // ---------------------------------------------------------------- reduction and store
   float bias = 0.f;
-  if (n_ok && p.bias != nullptr) bias = load_bias(p.bias, p.bias_dtype, n);
+  if (n_ok && p.bias != nullptr) bias = load_bias(p.bias, p.bias_dtype, bias_off + n);
   if (p.splits == 1) {
     if (warp >= 2) {
+      if constexpr (GROUPED) {
+        if (have_acc && p.row_scale != nullptr) {  // e.g. the routing weight of a mixture-of-experts row
+#pragma unroll
+          for (int m = 0; m < MP; ++m) acc[m] *= (m < mv) ? __ldg(p.row_scale + x_row0 + m) : 0.f;  // broadcast loads
+        }
+      }
       const int vec = (p.out_dtype == TG_F32) ? 4 : 8;
       const int left = static_cast<int>(p.N - row0);
       const int cols = left < kBM ? left : kBM;
+      const int64_t c_off = static_cast<int64_t>(x_row0) * p.ldc;  // first row of the tile's rows in C (0 unless grouped)
       if (c_rows_aligned(p) && p.N % vec == 0) {  // the same answer in every thread
         if (p.out_dtype == TG_BF16)
-          bsm_store_tile<MP>(reinterpret_cast<__nv_bfloat16*>(p.C) + row0, p.ldc, reinterpret_cast<__nv_bfloat16*>(inbox),
-                             acc, have_acc, n_local, mv, cols, bias);
+          bsm_store_tile<MP>(reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + row0, p.ldc,
+                             reinterpret_cast<__nv_bfloat16*>(inbox), acc, have_acc, n_local, mv, cols, bias);
         else if (p.out_dtype == TG_F16)
-          bsm_store_tile<MP>(reinterpret_cast<__half*>(p.C) + row0, p.ldc, reinterpret_cast<__half*>(inbox), acc,
+          bsm_store_tile<MP>(reinterpret_cast<__half*>(p.C) + c_off + row0, p.ldc, reinterpret_cast<__half*>(inbox), acc,
                              have_acc, n_local, mv, cols, bias);
         else
-          bsm_store_tile<MP>(reinterpret_cast<float*>(p.C) + row0, p.ldc, inbox, acc, have_acc, n_local, mv, cols, bias);
+          bsm_store_tile<MP>(reinterpret_cast<float*>(p.C) + c_off + row0, p.ldc, inbox, acc, have_acc, n_local, mv, cols,
+                             bias);
       } else if (have_acc && n_ok) {
         if (p.out_dtype == TG_BF16)
-          bsm_store_column<MP>(reinterpret_cast<__nv_bfloat16*>(p.C) + n, p.ldc, acc, mv, bias);
+          bsm_store_column<MP>(reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + n, p.ldc, acc, mv, bias);
         else if (p.out_dtype == TG_F16)
-          bsm_store_column<MP>(reinterpret_cast<__half*>(p.C) + n, p.ldc, acc, mv, bias);
+          bsm_store_column<MP>(reinterpret_cast<__half*>(p.C) + c_off + n, p.ldc, acc, mv, bias);
         else
-          bsm_store_column<MP>(reinterpret_cast<float*>(p.C) + n, p.ldc, acc, mv, bias);
+          bsm_store_column<MP>(reinterpret_cast<float*>(p.C) + c_off + n, p.ldc, acc, mv, bias);
       }
     }
   } else if constexpr (CLUSTER) {
@@ -562,6 +649,43 @@ int blockscaled_smallm_resident_clusters(int mp, int splits, int num_sms) {
     c = n > 0 ? n : -1;
   }
   return c > 0 ? c : 0;
+}
+
+template <int MP>
+cudaError_t launch_bsm_grouped(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int units,
+                               cudaStream_t stream) {
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(tg_fp8_gemm_blockscaled_smallm_kernel<MP, false, true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, BsmCfg<MP, true>::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(units), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = BsmCfg<MP, true>::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (p.flags & 2) ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, tg_fp8_gemm_blockscaled_smallm_kernel<MP, false, true>, tmW, tmX, p);
+}
+
+// Grouped form: p.tiles_n = ceil(N / 128) per group, p.mtile_bound >= the number of mp-row tiles of all groups,
+// p.splits == 1, p.num_kb <= the k-blocks one CTA may own; tmW maps the weights as [groups * N, K].
+cudaError_t launch_gemm_blockscaled_smallm_grouped(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p,
+                                                   int mp, cudaStream_t stream) {
+  if (p.splits != 1 || p.num_kb > kMaxKbPerCta || p.kb_per_split != p.num_kb) return cudaErrorInvalidValue;
+  const int64_t units = static_cast<int64_t>(p.mtile_bound) * p.tiles_n;
+  if (units < 1 || units > 0x7fffffff) return cudaErrorInvalidValue;
+  if (mp == 32) return launch_bsm_grouped<32>(tmW, tmX, p, static_cast<int>(units), stream);
+  if (mp == 64) return launch_bsm_grouped<64>(tmW, tmX, p, static_cast<int>(units), stream);
+  return cudaErrorInvalidValue;
 }
 
 cudaError_t launch_gemm_blockscaled_smallm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int mp,

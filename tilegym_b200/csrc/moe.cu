@@ -157,8 +157,11 @@ __global__ void __launch_bounds__(256) moe_silu_mul_quant_kernel(uint8_t* __rest
   const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
   for (int64_t g = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; g < n_groups; g += warps) {
     const int64_t r = g / groups_per_row, gc = g - r * groups_per_row;
-    const T* gate = x + r * (2 * inter) + gc * 128 + lane * 4;
-    const T* up = gate + inter;
+    // plain layout: row = [gate (I) | up (I)]; interleaved (mode bit 1): 128 gate values, the 128 up values of the
+    // same outputs, the next 128 gate values, ... (what the first GEMM writes when its weight rows were interleaved)
+    const bool inter_l = (mode & 2) != 0;
+    const T* gate = x + r * (2 * inter) + (inter_l ? gc * 256 : gc * 128) + lane * 4;
+    const T* up = gate + (inter_l ? 128 : inter);
     const uint2 gv = *reinterpret_cast<const uint2*>(gate);
     const uint2 uv = *reinterpret_cast<const uint2*>(up);
     const T* gp = reinterpret_cast<const T*>(&gv);
@@ -174,7 +177,7 @@ __global__ void __launch_bounds__(256) moe_silu_mul_quant_kernel(uint8_t* __rest
       amax = fmaxf(amax, fabsf(a[i]));
     }
     float scale = 1.0f;
-    if (mode == 1) {
+    if (mode & 1) {
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
       scale = __fdiv_rn(amax, 448.0f);
@@ -378,7 +381,8 @@ TG_API int32_t tg_moe_silu_mul_quant(const TgTensorDesc* Y, const TgTensorDesc* 
   if (X->shape[1] != 2 * I || I % 128 != 0 || I == 0) return api_fail(TG_ERR_ARGS, "X must be [rows, 2 * I] with I a multiple of 128");
   if (Y->shape[0] != R || Y->shape[1] != I || S->shape[0] != R || S->shape[1] != I / 128)
     return api_fail(TG_ERR_ARGS, "Y must be [rows, I] and S [rows, I / 128]");
-  if (mode != 0 && mode != 1) return api_fail(TG_ERR_ARGS, "mode must be 0 (scale 1) or 1 (amax / 448 per 128 elements)");
+  if (mode < 0 || mode > 3)
+    return api_fail(TG_ERR_ARGS, "mode must be 0 (scale 1) or 1 (amax / 448 per 128 elements), plus 2 for interleaved gate / up blocks");
   if (m_indptr == 0) return api_fail(TG_ERR_NULL, "m_indptr is null");
   if (num_experts < 1) return api_fail(TG_ERR_ARGS, "num_experts must be positive");
   if (R == 0) return TG_OK;

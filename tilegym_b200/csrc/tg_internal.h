@@ -95,6 +95,9 @@ int blockscaled_smallm_max_kb_per_cta();
 int blockscaled_smallm_resident_clusters(int mp, int splits, int num_sms);
 cudaError_t launch_gemm_blockscaled_smallm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int mp,
                                            cudaStream_t stream);
+// Grouped (mixture-of-experts, few rows per group) form of the same kernel; mp 32 or 64.
+cudaError_t launch_gemm_blockscaled_smallm_grouped(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p,
+                                                   int mp, cudaStream_t stream);
 // Swap-AB split-K kernel for M <= 64: tmW boxes 128 weight rows, tmX boxes `mp` activation rows.
 cudaError_t launch_gemm_smallm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int mp,
                                cudaStream_t stream);

@@ -158,7 +158,10 @@ def fused_experts_impl(
     y8 = torch.empty((R, inter), dtype=_FP8, device=dev)
     y_s = torch.empty((R, inter // 128), dtype=torch.float32, device=dev)
     mode = 1 if a2_quant == "block" else 0
-    if w1_interleaved:
+    # With few rows per expert (decode sizes) the first GEMM runs on the small-group kernel, which has no fused
+    # epilogue: the separate silu * mul pass reads whichever column order the weights produce.
+    small_groups = R <= 64 * E and H <= 4096
+    if w1_interleaved and not small_groups:
         # fc1 with silu * mul and the quantisation in its epilogue
         _lib.check_rc(L.tg_fp8_gemm_blockscaled_grouped_swiglu(
             _lib.desc(y8), _lib.desc(y_s), _lib.desc(a_sorted), _lib.desc(w1), _lib.desc(as_sorted), _lib.desc(w1_scale),
@@ -167,7 +170,7 @@ def fused_experts_impl(
         # fc1 on contiguous expert segments: [rows, 2 I] in the 16-bit type, then silu * mul + quantise
         c1 = ops.ragged_block_scaled_bmm(a_sorted, w1, as_sorted, w1_scale, m_indptr, R, out_dtype=out_dtype)
         _lib.check_rc(L.tg_moe_silu_mul_quant(_lib.desc(y8), _lib.desc(y_s), _lib.desc(c1), m_indptr.data_ptr(), E,
-                                              mode, dev.index, stream))
+                                              mode | (2 if w1_interleaved else 0), dev.index, stream))
     # fc2, routing weight applied to the fp32 sums before the rounding
     c3 = ops.ragged_block_scaled_bmm(y8, w2, y_s, w2_scale, m_indptr, R, out_dtype=out_dtype, row_scale=w_sorted)
     out = hidden_states if (inplace and hidden_states.dtype == out_dtype) else torch.empty((T, H), dtype=out_dtype, device=dev)
