@@ -321,6 +321,32 @@ def moe_layer_sweep(dev, fp8_peak_tflops: float):
     return res
 
 
+def moe_decode_sweep(dev, hbm_peak_gbs: float):
+    """The same mixture-of-experts layer at decode sizes: few rows per expert, so both expert GEMMs run on the grouped
+    small-M kernel and the layer is a weight-streaming problem (the weights of every expert that got a token)."""
+    from tilegym_b200 import moe
+
+    H, I, E, topk = 2048, 1536, 64, 6
+    g = torch.Generator(device=dev).manual_seed(0)
+    w1 = torch.randn(E, 2 * I, H, generator=g, device=dev, dtype=torch.bfloat16).mul_(0.05).to(torch.float8_e4m3fn)
+    w2 = torch.randn(E, H, I, generator=g, device=dev, dtype=torch.bfloat16).mul_(0.05).to(torch.float8_e4m3fn)
+    w1s = torch.rand(E, 2 * I // 128, H // 128, generator=g, device=dev) + 0.5
+    w2s = torch.rand(E, H // 128, I // 128, generator=g, device=dev) + 0.5
+    rows = []
+    for T in (1, 16, 64, 256):
+        x = torch.randn(T, H, generator=g, device=dev, dtype=torch.bfloat16)
+        ids = torch.randint(0, E, (T, topk), generator=g, device=dev)
+        wts = torch.softmax(torch.randn(T, topk, generator=g, device=dev), dim=-1)
+        touched = int(torch.unique(ids).numel())
+        weight_bytes = touched * (2 * I * H + H * I)
+        us = graph_time_us(lambda i: moe.fused_experts_impl(x, w1, w2, wts, ids, use_fp8_w8a8=True, w1_scale=w1s,
+                                                            w2_scale=w2s, a2_quant="block"), 2, replays=10)
+        rows.append({"tokens": T, "experts_touched": touched, "us": round(us, 1),
+                     "weight_gbs": round(weight_bytes / us / 1e3, 1),
+                     "frac_of_measured_hbm": round(weight_bytes / us / 1e3 / hbm_peak_gbs, 3)})
+    return {"shape": f"hidden={H} intermediate={I} experts={E} top_k={topk}", "rows": rows}
+
+
 def run_configs(dev, peaks):
     """Bounded sweeps of the benchmark configurations the headline number does not cover."""
     hbm = float(peaks["hbm_gbs"])
@@ -347,6 +373,7 @@ def run(dev, peaks):
                   "measured HBM copy bandwidth / of 2 x measured bf16 burst",
         "grouped_block_scaled": grouped_sweep(dev, fp8),
         "moe_layer": moe_layer_sweep(dev, fp8),
+        "moe_layer_decode": moe_decode_sweep(dev, hbm),
         "quantisers": quantiser_sweep(dev, hbm),
         "swiglu_gate_up": swiglu_sweep(dev),
         "llama8b_mlp_block": mlp_block_sweep(dev),
