@@ -310,14 +310,15 @@ def moe_layer_sweep(dev, fp8_peak_tflops: float):
     flops = 2.0 * T * topk * (2 * I * H + H * I)
     res = {"shape": f"tokens={T} hidden={H} intermediate={I} experts={E} top_k={topk}", "gflop": round(flops / 1e9, 1)}
     fused = lambda i: moe.fused_experts_impl(x, w1i, w2, wts, ids, use_fp8_w8a8=True, w1_scale=w1si, w2_scale=w2s,  # noqa: E731
-                                             a2_quant="block", w1_interleaved=True)
+                                             a2_quant="block", w1_interleaved=True, fuse_silu_epilogue=True)
     separate = lambda i: moe.fused_experts_impl(x, w1, w2, wts, ids, use_fp8_w8a8=True, w1_scale=w1s, w2_scale=w2s,  # noqa: E731
                                                 a2_quant="block")
     # the layer is a dozen short launches: replayed from a CUDA graph (its routing tables never leave the device)
     res["fused_epilogue_us"] = round(graph_time_us(fused, 2, replays=10), 1)
     res["separate_silu_mul_us"] = round(graph_time_us(separate, 2, replays=10), 1)
-    res["fused_tflops"] = round(flops / res["fused_epilogue_us"] / 1e6, 1)
-    res["fused_frac_of_burst_peak"] = round(res["fused_tflops"] / fp8_peak_tflops, 3)
+    best = min(res["fused_epilogue_us"], res["separate_silu_mul_us"])  # the separate pass is the default path
+    res["tflops"] = round(flops / best / 1e6, 1)
+    res["frac_of_burst_peak"] = round(res["tflops"] / fp8_peak_tflops, 3)
     return res
 
 

@@ -114,13 +114,15 @@ def test_fused_experts_reference_test_shapes(dev, T, H, I, E, topk):
     _lib.device_status(dev.index)
 
 
+@pytest.mark.parametrize("fuse", [True, False])
 @pytest.mark.parametrize("a2_quant", ["ones", "block"])
 @pytest.mark.parametrize("dtype", [torch.float8_e4m3fn, torch.bfloat16])
-@pytest.mark.parametrize("T,H,I,E,topk", [(64, 1024, 512, 20, 8), (700, 512, 384, 6, 3), (5, 256, 128, 3, 1)])
-def test_first_gemm_with_silu_mul_in_its_epilogue(dev, T, H, I, E, topk, dtype, a2_quant):
-    """With the gate / up rows of w1 interleaved in blocks of 128 the first GEMM applies silu * mul and the e4m3
-    quantisation itself: same oracle, same tolerance, and close to the unfused path (not bit-identical: the fused
-    epilogue uses the fast exponential)."""
+@pytest.mark.parametrize("T,H,I,E,topk", [(64, 1024, 512, 20, 8), (700, 512, 384, 6, 3), (300, 256, 256, 2, 2),
+                                          (5, 256, 128, 3, 1)])
+def test_interleaved_gate_up_weights(dev, T, H, I, E, topk, dtype, a2_quant, fuse):
+    """With the gate / up rows of w1 interleaved in blocks of 128 the first GEMM can apply silu * mul and the e4m3
+    quantisation itself (fuse, taken where an expert has more than 64 rows on average: the second and third shape);
+    without it, and for small groups, the separate pass reads the interleaved columns.  Same oracle, same tolerance."""
     x, w1, w1s, w2, w2s, wts, ids = make_case(T, H, I, E, topk, seed=3 * T + E)
     a8, a_s = R.ref_act_quant(x.to(torch.bfloat16) if dtype == torch.bfloat16 else x, 128)
     out_dtype = torch.bfloat16 if dtype == torch.bfloat16 else torch.float16
@@ -129,7 +131,7 @@ def test_first_gemm_with_silu_mul_in_its_epilogue(dev, T, H, I, E, topk, dtype, 
     hidden = x.to(torch.bfloat16).to(dev) if dtype == torch.bfloat16 else a8.to(dev)
     out = moe.fused_experts_impl(hidden, w1i, w2.to(dev), wts.to(dev), ids.to(dev), use_fp8_w8a8=True, w1_scale=w1si,
                                  w2_scale=w2s.to(dev), a1_scale=None if dtype == torch.bfloat16 else a_s.to(dev),
-                                 a2_quant=a2_quant, w1_interleaved=True)
+                                 a2_quant=a2_quant, w1_interleaved=True, fuse_silu_epilogue=fuse)
     assert out.dtype == out_dtype
     close_enough(out, ref)
     _lib.device_status(dev.index)

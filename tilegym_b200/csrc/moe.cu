@@ -213,33 +213,43 @@ __device__ __forceinline__ float round16<__half>(float v) {
   return __half2float(__float2half_rn(v));
 }
 
-// One warp per group of 128 output elements (lane = 4 consecutive ones).  X row = [gate (I) | up (I)].
-// mode 0: scale 1, y = e4m3(a) (saturating); mode 1: scale = amax / 448 (1 for an all-zero group), y = e4m3(a / scale).
+// Eight lanes per group of 128 output elements, 16 consecutive ones per lane (two 16-byte loads of gate values, two of
+// up values, one 16-byte store): a warp covers four groups.  X row = [gate (I) | up (I)], or with mode bit 1 set
+// 128 gate values, the 128 up values of the same outputs, the next 128 gate values, ... (what the first GEMM writes
+// when its weight rows were interleaved).  mode bit 0 clear: scale 1, y = e4m3(a) (saturating); set: scale = amax / 448
+// (1 for an all-zero group), y = e4m3(a / scale).
 template <typename T>
 __global__ void __launch_bounds__(256) moe_silu_mul_quant_kernel(uint8_t* __restrict__ y, float* __restrict__ s,
                                                                  const T* __restrict__ x,
                                                                  const int32_t* __restrict__ m_indptr, int num_experts,
                                                                  int64_t inter, int mode) {
-  const int lane = threadIdx.x & 31;
+  q8_allow_dependents();
+  const int sub = threadIdx.x & 7;  // which 16 of the group's 128 outputs
   const int64_t groups_per_row = inter / 128;
   const int64_t rows = m_indptr != nullptr ? static_cast<int64_t>(__ldg(m_indptr + num_experts)) : 0;
   const int64_t n_groups = rows * groups_per_row;
-  const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  for (int64_t g = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; g < n_groups; g += warps) {
-    const int64_t r = g / groups_per_row, gc = g - r * groups_per_row;
-    // plain layout: row = [gate (I) | up (I)]; interleaved (mode bit 1): 128 gate values, the 128 up values of the
-    // same outputs, the next 128 gate values, ... (what the first GEMM writes when its weight rows were interleaved)
-    const bool inter_l = (mode & 2) != 0;
-    const T* gate = x + r * (2 * inter) + (inter_l ? gc * 256 : gc * 128) + lane * 4;
+  const int64_t span = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 3;
+  const bool inter_l = (mode & 2) != 0;
+  // all lanes of a warp run the same number of iterations (the shuffles need them): the warp's first group decides
+  for (int64_t g0 = ((static_cast<int64_t>(blockIdx.x) * blockDim.x + (threadIdx.x & ~31)) >> 3); g0 < n_groups; g0 += span) {
+    const int64_t g = g0 + ((threadIdx.x & 31) >> 3);
+    const bool live = g < n_groups;
+    const int64_t r = live ? g / groups_per_row : 0, gc = live ? g - r * groups_per_row : 0;
+    const T* gate = x + r * (2 * inter) + (inter_l ? gc * 256 : gc * 128) + sub * 16;
     const T* up = gate + (inter_l ? 128 : inter);
-    const uint2 gv = *reinterpret_cast<const uint2*>(gate);
-    const uint2 uv = *reinterpret_cast<const uint2*>(up);
-    const T* gp = reinterpret_cast<const T*>(&gv);
-    const T* upv = reinterpret_cast<const T*>(&uv);
-    float a[4];
+    uint4 gv[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)}, uv[2] = {gv[0], gv[0]};
+    if (live) {
+      gv[0] = __ldcs(reinterpret_cast<const uint4*>(gate));
+      gv[1] = __ldcs(reinterpret_cast<const uint4*>(gate) + 1);
+      uv[0] = __ldcs(reinterpret_cast<const uint4*>(up));
+      uv[1] = __ldcs(reinterpret_cast<const uint4*>(up) + 1);
+    }
+    const T* gp = reinterpret_cast<const T*>(gv);
+    const T* upv = reinterpret_cast<const T*>(uv);
+    float a[16];
     float amax = 0.f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 16; ++i) {
       const float gf = to_f32<T>(gp[i]), uf = to_f32<T>(upv[i]);
       // silu(g) * u in fp32 (fast exponential and division: the result is rounded to 16 bits right away),
       // rounded once to the 16-bit type of the reference's intermediate tensor
@@ -249,22 +259,31 @@ __global__ void __launch_bounds__(256) moe_silu_mul_quant_kernel(uint8_t* __rest
     float scale = 1.0f;
     if (mode & 1) {
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));  // the group's 8 lanes
       scale = __fdiv_rn(amax, 448.0f);
       if (scale == 0.f) scale = 1.0f;
       if (q8_scale_is_tame(scale)) {  // 16-bit values over RN(16-bit amax / 448): the test-free quotient applies
         const float rcp = __frcp_rn(scale);
-        const float2 q0 = q8_quot2(make_float2(a[0], a[1]), scale, rcp), q1 = q8_quot2(make_float2(a[2], a[3]), scale, rcp);
-        a[0] = q0.x; a[1] = q0.y; a[2] = q1.x; a[3] = q1.y;
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+          const float2 q = q8_quot2(make_float2(a[i], a[i + 1]), scale, rcp);
+          a[i] = q.x;
+          a[i + 1] = q.y;
+        }
       } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) a[i] = __fdiv_rn(a[i], scale);
+        for (int i = 0; i < 16; ++i) a[i] = __fdiv_rn(a[i], scale);
       }
     }
-    const uint32_t lo = q8_cast2<kQ8E4M3>(a[0], a[1], -448.f, 448.f);
-    const uint32_t hi = q8_cast2<kQ8E4M3>(a[2], a[3], -448.f, 448.f);
-    *reinterpret_cast<uint32_t*>(y + r * inter + gc * 128 + lane * 4) = lo | (hi << 16);
-    if (lane == 0) s[r * groups_per_row + gc] = scale;
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      w[k] = q8_cast2<kQ8E4M3>(a[4 * k], a[4 * k + 1], -448.f, 448.f) |
+             (q8_cast2<kQ8E4M3>(a[4 * k + 2], a[4 * k + 3], -448.f, 448.f) << 16);
+    if (live) {
+      __stcs(reinterpret_cast<uint4*>(y + r * inter + gc * 128 + sub * 16), make_uint4(w[0], w[1], w[2], w[3]));
+      if (sub == 0) s[r * groups_per_row + gc] = scale;
+    }
   }
 }
 
@@ -480,7 +499,7 @@ TG_API int32_t tg_moe_silu_mul_quant(const TgTensorDesc* Y, const TgTensorDesc* 
   if (num_experts < 1) return api_fail(TG_ERR_ARGS, "num_experts must be positive");
   if (R == 0) return TG_OK;
   if (X->ptr == 0 || Y->ptr == 0 || S->ptr == 0) return api_fail(TG_ERR_NULL, "data pointer is null");
-  if ((X->ptr & 7u) || (Y->ptr & 3u)) return api_fail(TG_ERR_ALIGN, "X must be 8-byte and Y 4-byte aligned");
+  if ((X->ptr & 15u) || (Y->ptr & 15u)) return api_fail(TG_ERR_ALIGN, "X and Y must be 16-byte aligned");
   Guard guard(device_id);
   if (guard.err != cudaSuccess) {
     cudaGetLastError();
@@ -490,7 +509,7 @@ TG_API int32_t tg_moe_silu_mul_quant(const TgTensorDesc* Y, const TgTensorDesc* 
   int32_t* status = nullptr;
   int32_t rc = api_init_device(device_id, &num_sms, &status);
   if (rc != TG_OK) return rc;
-  const int grid = grid_for(R * (I / 128), 8, num_sms, 8);
+  const int grid = grid_for(R * (I / 128), 32, num_sms, 8);  // 32 groups of 128 outputs per 256-thread block
   cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
   if (X->dtype == TG_BF16)
     moe_silu_mul_quant_kernel<__nv_bfloat16><<<grid, 256, 0, cs>>>(

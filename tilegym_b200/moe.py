@@ -104,6 +104,7 @@ def fused_experts_impl(
     a1_scale: Optional[torch.Tensor] = None,
     a2_quant: str = "ones",
     w1_interleaved: bool = False,
+    fuse_silu_epilogue: bool = False,
 ) -> torch.Tensor:
     """out[t] = sum_j topk_weights[t, j] * w2[e] . (silu(gate) * up),  [gate | up] = w1[e] . x[t],  e = topk_ids[t, j].
 
@@ -115,8 +116,10 @@ def fused_experts_impl(
     type, and the intermediate is cast to e4m3 with scale 1 (`a2_quant="ones"`, moe_interface.py:269-279);
     `a2_quant="block"` quantises it per 1 x 128 with amax / 448 instead, which keeps more of its range.
     `w1_interleaved=True` says that w1 / w1_scale were rearranged by `interleave_gate_up_blocks` (128 gate rows,
-    128 up rows, alternating): the first GEMM then applies silu * mul and the quantisation in its epilogue and
-    the [rows, 2 I] intermediate is never written."""
+    128 up rows, alternating).  With `fuse_silu_epilogue=True` (which needs that layout) the first GEMM applies
+    silu * mul and the quantisation in its epilogue and the [rows, 2 I] intermediate is never written: it saves
+    that tensor (151 MB at 4096 tokens of the DeepSeek-V2-Lite shape) and costs about 7 % of the layer's time,
+    because the epilogue's exponentials cannot overlap the next tile; the default runs the separate pass."""
     if use_int8_w8a16:
         raise NotImplementedError("tilegym_b200.fused_experts_impl implements the FP8 W8A8 path only (no int8 weights)")
     if not use_fp8_w8a8 or w1_scale is None or w2_scale is None:
@@ -161,7 +164,8 @@ def fused_experts_impl(
     # With few rows per expert (decode sizes) the first GEMM runs on the small-group kernel, which has no fused
     # epilogue: the separate silu * mul pass reads whichever column order the weights produce.
     small_groups = R <= 64 * E and H <= 4096
-    if w1_interleaved and not small_groups:
+    assert not fuse_silu_epilogue or w1_interleaved, "the fused epilogue needs interleave_gate_up_blocks weights"
+    if fuse_silu_epilogue and not small_groups:
         # fc1 with silu * mul and the quantisation in its epilogue
         _lib.check_rc(L.tg_fp8_gemm_blockscaled_grouped_swiglu(
             _lib.desc(y8), _lib.desc(y_s), _lib.desc(a_sorted), _lib.desc(w1), _lib.desc(as_sorted), _lib.desc(w1_scale),
@@ -213,9 +217,11 @@ class FP8MoE(torch.nn.Module):
     """Expert weights quantised once (128 x 128 blocks, amax / 448) and kept in e4m3; forward takes 16-bit
     hidden states and the router's top-k weights and ids."""
 
-    def __init__(self, w1_fp8, w1_scale, w2_fp8, w2_scale, a2_quant: str = "block"):
+    def __init__(self, w1_fp8, w1_scale, w2_fp8, w2_scale, a2_quant: str = "block", fuse_silu_epilogue: bool = False):
         super().__init__()
-        w1_fp8, w1_scale = interleave_gate_up_blocks(w1_fp8, w1_scale)  # silu * mul runs in the first GEMM's epilogue
+        # gate / up rows in alternating blocks of 128: the order the fused epilogue needs; the separate pass reads it too
+        w1_fp8, w1_scale = interleave_gate_up_blocks(w1_fp8, w1_scale)
+        self.fuse_silu_epilogue = fuse_silu_epilogue  # True: no [rows, 2 I] intermediate, about 7 % slower
         self.register_buffer("w1", w1_fp8)
         self.register_buffer("w1_scale", w1_scale)
         self.register_buffer("w2", w2_fp8)
@@ -235,5 +241,6 @@ class FP8MoE(torch.nn.Module):
         x = hidden_states.reshape(-1, shape[-1]).contiguous()
         out = fused_experts_impl(x, self.w1, self.w2, topk_weights.reshape(x.shape[0], -1),
                                  topk_ids.reshape(x.shape[0], -1), use_fp8_w8a8=True, w1_scale=self.w1_scale,
-                                 w2_scale=self.w2_scale, a2_quant=self.a2_quant, w1_interleaved=True)
+                                 w2_scale=self.w2_scale, a2_quant=self.a2_quant, w1_interleaved=True,
+                                 fuse_silu_epilogue=self.fuse_silu_epilogue)
         return out.reshape(shape)
