@@ -187,6 +187,14 @@ TG_API int32_t tg_fp8_gemm_blockscaled_grouped_swiglu(const TgTensorDesc* Y, con
                                                       uint64_t m_indptr, int32_t round_dtype, int32_t quant_mode,
                                                       int32_t device_id, uint64_t stream);
 
+/* tg_act_quant and tg_moe_permute_rows in one pass, for 16-bit activations: every row of X (T, H) bf16 / f16 is
+ * quantised per 1 x 128 block (amax / 448, 1.0 for an all-zero block; the bytes and scales tg_act_quant produces) and
+ * written, with its scales, to each of its top_k rows pos[t * top_k + j] of A_sorted (R, H) e4m3 / As_sorted
+ * (R, H / 128) f32 (entries of -1 are skipped).  pos as tg_moe_route produces it.  No reference counterpart (the
+ * reference gathers rows inside its GEMM tiles). */
+TG_API int32_t tg_moe_quant_permute_rows(const TgTensorDesc* A_sorted, const TgTensorDesc* As_sorted, const TgTensorDesc* X,
+                                         uint64_t pos, int32_t topk, int32_t device_id, uint64_t stream);
+
 /* Between the two expert GEMMs: a = silu(X[:, :I]) * X[:, I:] in fp32, rounded to X's 16-bit type (the reference's
  * intermediate tensor, moe_interface.py:262-267), then quantised to e4m3 for the second GEMM.  mode 0: scale 1 and
  * a saturating cast, the reference's a2_scale of ones (moe_interface.py:269-279); mode 1: one scale amax / 448 per

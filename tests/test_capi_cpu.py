@@ -149,6 +149,12 @@ def test_moe_argument_checks():
     assert L.tg_moe_silu_mul_quant(_d(y), _d(torch.zeros(4, 2)), _d(x), p, 4, 4, 0, 0) == -6  # mode
     assert L.tg_moe_silu_mul_quant(_d(y), _d(torch.zeros(4, 3)), _d(x), p, 4, 0, 0, 0) == -6
     assert L.tg_moe_silu_mul_quant(_d(y), _d(torch.zeros(4, 2)), _d(x.float()), p, 4, 0, 0, 0) == -2
+    xq = torch.zeros(4, 256, dtype=torch.bfloat16)
+    aq, sq = torch.zeros(8, 256, dtype=torch.float8_e4m3fn), torch.zeros(8, 2)
+    assert L.tg_moe_quant_permute_rows(_d(aq), _d(sq), _d(xq.float()), p, 2, 0, 0) == -2          # 16-bit inputs only
+    assert L.tg_moe_quant_permute_rows(_d(aq), _d(torch.zeros(8, 3)), _d(xq), p, 2, 0, 0) == -6    # scale shape
+    assert L.tg_moe_quant_permute_rows(_d(aq), _d(sq), _d(xq), p, 1, 0, 0) == -6                   # more rows than pairs
+    assert L.tg_moe_quant_permute_rows(_d(aq), _d(sq), _d(xq), 0, 2, 0, 0) == -5
     c = torch.zeros(16, 256, dtype=torch.bfloat16)
     assert L.tg_moe_unpermute_sum(_d(torch.zeros(8, 256, dtype=torch.float16)), _d(c), p, 2, 0, 0) == -2
     assert L.tg_moe_unpermute_sum(_d(torch.zeros(4, 256, dtype=torch.bfloat16)), _d(c), p, 2, 0, 0) == -6

@@ -63,6 +63,38 @@ def test_routing_tables(dev, T, topk, E):
     assert torch.equal(w_sorted[:n_valid], wts.reshape(-1)[srt])
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("T,H,topk,E", [(37, 512, 4, 9), (1, 128, 1, 3), (300, 2048, 6, 64)])
+def test_quantise_and_scatter_equals_act_quant_then_gather(dev, T, H, topk, E, dtype):
+    """16-bit activations go into expert order in one pass: the bytes and scales of act_quant followed by the row
+    gather, including tokens with an invalid expert id (skipped) and an all-zero block (scale 1)."""
+    g = torch.Generator().manual_seed(T + H)
+    x = (torch.randn(T, H, generator=g) * 3).to(dtype)
+    x[0, :128] = 0
+    ids = torch.randint(0, E, (T, topk), generator=g, dtype=torch.int32)
+    ids[T // 2, 0] = -1
+    xd, idd = x.to(dev), ids.to(dev)
+    m_indptr, sorted_ids, pos, _ = moe.moe_route(idd, None, E)
+    n_rows = T * topk
+    a8, a_s = tg.act_quant(xd, 128)
+    L = _lib.lib()
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    ref_a = torch.zeros((n_rows, H), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+    ref_s = torch.zeros((n_rows, H // 128), dtype=torch.float32, device=dev)
+    _lib.check_rc(L.tg_moe_permute_rows(_lib.desc(ref_a), _lib.desc(ref_s), _lib.desc(a8), _lib.desc(a_s),
+                                        sorted_ids.data_ptr(), m_indptr.data_ptr(), E, topk, dev.index, stream))
+    out_a = torch.zeros((n_rows, H), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+    out_s = torch.zeros((n_rows, H // 128), dtype=torch.float32, device=dev)
+    _lib.check_rc(L.tg_moe_quant_permute_rows(_lib.desc(out_a), _lib.desc(out_s), _lib.desc(xd), pos.data_ptr(), topk,
+                                              dev.index, stream))
+    torch.cuda.synchronize(dev)
+    assert torch.equal(out_a.view(torch.uint8), ref_a.view(torch.uint8)) and torch.equal(out_s, ref_s)
+    yr, sr = R.ref_act_quant(x, 128)
+    rows = int(m_indptr[-1])
+    src = (sorted_ids[:rows].cpu().long() // topk)
+    assert torch.equal(out_a[:rows].cpu().view(torch.uint8), yr.view(torch.uint8)[src]) and torch.equal(out_s[:rows].cpu(), sr[src])
+
+
 def test_moe_align_block_size_tables(dev):
     """Semantics of src/tilegym/ops/moe_interface.py:30-81: each expert's pairs padded to a multiple of the block
     with the value tokens * top_k, one expert id per block."""

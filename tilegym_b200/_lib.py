@@ -126,6 +126,9 @@ SIGNATURES = {
         ctypes.c_int32,
         [_P, _P, _P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64],
     ),
+    "tg_moe_quant_permute_rows": (
+        ctypes.c_int32, [_P, _P, _P, ctypes.c_uint64, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64],
+    ),
     "tg_moe_silu_mul_quant": (
         ctypes.c_int32,
         [_P, _P, _P, ctypes.c_uint64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint64],

@@ -64,25 +64,6 @@ __device__ __forceinline__ int64_t scale_index(int64_t g, int64_t groups_per_row
   return row * row_stride + (g - row * groups_per_row) * group_stride;
 }
 
-// |x| maximum of two packed 16-bit pairs, element-wise (NaN operands are ignored, like fmaxf).
-template <typename T>
-__device__ __forceinline__ uint32_t absmax_pairs(uint32_t a, uint32_t b) {
-  if constexpr (std::is_same<T, __half>::value) {
-    const __half2 m = __hmax2(__habs2(*reinterpret_cast<const __half2*>(&a)), __habs2(*reinterpret_cast<const __half2*>(&b)));
-    return *reinterpret_cast<const uint32_t*>(&m);
-  } else {
-    const __nv_bfloat162 m = __hmax2(__habs2(*reinterpret_cast<const __nv_bfloat162*>(&a)),
-                                     __habs2(*reinterpret_cast<const __nv_bfloat162*>(&b)));
-    return *reinterpret_cast<const uint32_t*>(&m);
-  }
-}
-
-template <typename T>
-__device__ __forceinline__ float2 unpack_pair(uint32_t w) {
-  if constexpr (std::is_same<T, __half>::value) return __half22float2(*reinterpret_cast<const __half2*>(&w));
-  else return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));  // bf16 -> fp32 is a shift
-}
-
 // A thread owns a chunk of EPT consecutive elements; the `tpg` = group_size / EPT lanes (a power of two, at
 // most 32) that share a group sit next to each other in a warp.  `zero_to_one` selects the 1 x 128 activation
 // quantiser's rule (scale 1.0 for an all-zero group, no eps).  16-bit inputs stay packed for the |x| maximum and

@@ -181,6 +181,70 @@ __global__ void __launch_bounds__(128) moe_permute_rows_kernel(uint8_t* __restri
   }
 }
 
+// ------------------------------------------------------------------------------------------ quantise + row scatter
+// 16-bit activations straight into expert order: every token row is quantised once (1 x 128 blocks, amax / 448, 1.0
+// for an all-zero block - the arithmetic of act_quant) and written to each of its top_k places pos[t * top_k + j]
+// (skipped where that is -1), together with its scales.  One pass instead of act_quant + row gather.
+// A thread owns 16 consecutive elements, the 8 lanes of a block sit next to each other.
+template <typename T>
+__global__ void __launch_bounds__(256) moe_quant_permute_kernel(uint8_t* __restrict__ y, float* __restrict__ ys,
+                                                                const T* __restrict__ x,
+                                                                const int32_t* __restrict__ pos, int64_t tokens, int topk,
+                                                                int64_t hidden) {
+  q8_allow_dependents();
+  const int lane = threadIdx.x & 31;
+  const int64_t cpr = hidden / 16;  // chunks per row
+  const int64_t n_chunks = tokens * cpr;
+  const int64_t span = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  // all lanes of a warp run the same number of iterations (the shuffles need them)
+  for (int64_t base = static_cast<int64_t>(blockIdx.x) * blockDim.x + (threadIdx.x & ~31); base < n_chunks; base += span) {
+    const int64_t c = base + lane;
+    const bool live = c < n_chunks;
+    uint32_t w[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) w[j] = 0u;
+    if (live) {
+      const uint4 t0 = __ldcs(reinterpret_cast<const uint4*>(x + c * 16));
+      const uint4 t1 = __ldcs(reinterpret_cast<const uint4*>(x + c * 16) + 1);
+      w[0] = t0.x; w[1] = t0.y; w[2] = t0.z; w[3] = t0.w;
+      w[4] = t1.x; w[5] = t1.y; w[6] = t1.z; w[7] = t1.w;
+    }
+    uint32_t m2 = absmax_pairs<T>(w[0], w[1]);
+#pragma unroll
+    for (int j = 2; j < 8; j += 2) m2 = absmax_pairs<T>(m2, absmax_pairs<T>(w[j], w[j + 1]));
+    const float2 mm = unpack_pair<T>(m2);
+    float amax = fmaxf(mm.x, mm.y);
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    float scale = q8_scale_from_amax(amax, 448.f, 1.0f / 448.f);
+    if (scale == 0.f) scale = 1.0f;
+    const float r = __frcp_rn(scale);
+    const bool fast = q8_scale_is_tame(scale);
+    uint32_t out[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 x0 = unpack_pair<T>(w[2 * k]), x1 = unpack_pair<T>(w[2 * k + 1]);
+      if (fast) {
+        const float2 q0 = q8_quot2(x0, scale, r), q1 = q8_quot2(x1, scale, r);
+        out[k] = q8_cast2<kQ8E4M3>(q0.x, q0.y, -448.f, 448.f) | (q8_cast2<kQ8E4M3>(q1.x, q1.y, -448.f, 448.f) << 16);
+      } else {
+        out[k] = q8_pair<kQ8E4M3>(x0.x, x0.y, scale, r, false, -448.f, 448.f) |
+                 (q8_pair<kQ8E4M3>(x1.x, x1.y, scale, r, false, -448.f, 448.f) << 16);
+      }
+    }
+    if (live) {
+      const int64_t t = c / cpr, col = (c - t * cpr) * 16;
+      const uint4 o4 = make_uint4(out[0], out[1], out[2], out[3]);
+      for (int j = 0; j < topk; ++j) {
+        const int32_t dst = __ldg(pos + t * topk + j);
+        if (dst < 0) continue;
+        *reinterpret_cast<uint4*>(y + static_cast<int64_t>(dst) * hidden + col) = o4;
+        if ((lane & 7) == 0) ys[static_cast<int64_t>(dst) * (hidden / 128) + (col >> 7)] = scale;
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------ silu * mul + quantise
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);
@@ -480,6 +544,47 @@ TG_API int32_t tg_moe_permute_rows(const TgTensorDesc* A_sorted, const TgTensorD
       reinterpret_cast<const int32_t*>(sorted_ids), reinterpret_cast<const int32_t*>(m_indptr), num_experts, topk, K,
       A->strides[0], static_cast<int>(KB), As->strides[0]);
   return launch_status("moe permute rows");
+}
+
+TG_API int32_t tg_moe_quant_permute_rows(const TgTensorDesc* A_sorted, const TgTensorDesc* As_sorted, const TgTensorDesc* X,
+                                         uint64_t pos, int32_t topk, int32_t device_id, uint64_t stream) {
+  if (A_sorted == nullptr || As_sorted == nullptr || X == nullptr) return api_fail(TG_ERR_NULL, "a descriptor is null");
+  if (X->dtype != TG_BF16 && X->dtype != TG_F16) return api_fail(TG_ERR_DTYPE, "X must be bf16 or f16");
+  if (A_sorted->dtype != TG_F8E4M3) return api_fail(TG_ERR_DTYPE, "A_sorted must be float8_e4m3fn");
+  if (As_sorted->dtype != TG_F32) return api_fail(TG_ERR_DTYPE, "As_sorted must be f32");
+  if (!contiguous_2d(A_sorted) || !contiguous_2d(As_sorted) || !contiguous_2d(X))
+    return api_fail(TG_ERR_ARGS, "A_sorted, As_sorted and X must be contiguous 2-D");
+  const int64_t T = X->shape[0], H = X->shape[1], R = A_sorted->shape[0];
+  if (H <= 0 || H % 128 != 0) return api_fail(TG_ERR_ARGS, "the hidden size must be a positive multiple of 128");
+  if (A_sorted->shape[1] != H || As_sorted->shape[0] != R || As_sorted->shape[1] != H / 128)
+    return api_fail(TG_ERR_ARGS, "A_sorted must be [rows, hidden] and As_sorted [rows, hidden / 128]");
+  if (topk < 1 || R > T * topk) return api_fail(TG_ERR_ARGS, "A_sorted has more rows than tokens x top_k");
+  if (pos == 0) return api_fail(TG_ERR_NULL, "pos is null");
+  if (pos & 3u) return api_fail(TG_ERR_ALIGN, "pos must be 4-byte aligned");
+  if (T == 0 || R == 0) return TG_OK;
+  if (X->ptr == 0 || A_sorted->ptr == 0 || As_sorted->ptr == 0) return api_fail(TG_ERR_NULL, "data pointer is null");
+  if ((X->ptr | A_sorted->ptr) & 15u) return api_fail(TG_ERR_ALIGN, "X and A_sorted must be 16-byte aligned");
+  if (As_sorted->ptr & 3u) return api_fail(TG_ERR_ALIGN, "As_sorted must be 4-byte aligned");
+  Guard guard(device_id);
+  if (guard.err != cudaSuccess) {
+    cudaGetLastError();
+    return api_fail(TG_ERR_DEVICE, "cannot select the CUDA device");
+  }
+  int num_sms = 0;
+  int32_t* status = nullptr;
+  int32_t rc = api_init_device(device_id, &num_sms, &status);
+  if (rc != TG_OK) return rc;
+  const int grid = grid_for(T * (H / 16), 256, num_sms, 8);
+  cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+  if (X->dtype == TG_BF16)
+    moe_quant_permute_kernel<__nv_bfloat16><<<grid, 256, 0, cs>>>(
+        reinterpret_cast<uint8_t*>(A_sorted->ptr), reinterpret_cast<float*>(As_sorted->ptr),
+        reinterpret_cast<const __nv_bfloat16*>(X->ptr), reinterpret_cast<const int32_t*>(pos), T, topk, H);
+  else
+    moe_quant_permute_kernel<__half><<<grid, 256, 0, cs>>>(
+        reinterpret_cast<uint8_t*>(A_sorted->ptr), reinterpret_cast<float*>(As_sorted->ptr),
+        reinterpret_cast<const __half*>(X->ptr), reinterpret_cast<const int32_t*>(pos), T, topk, H);
+  return launch_status("moe quant_permute_rows");
 }
 
 TG_API int32_t tg_moe_silu_mul_quant(const TgTensorDesc* Y, const TgTensorDesc* S, const TgTensorDesc* X, uint64_t m_indptr,

@@ -9,8 +9,12 @@
 // rounding boundaries - a test on the bits of a, no conversion needed.  Only those elements (about one in
 // 10^5, plus the target's subnormal range, where the boundaries sit elsewhere) are redone with __fdiv_rn.
 #pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_fp8.h>
 #include <stdint.h>
+
+#include <type_traits>
 
 namespace tg {
 
@@ -89,6 +93,25 @@ __device__ __forceinline__ float q8_scale_from_amax(float amax, float qmax, floa
   if (amax < 1e-30f) return __fdiv_rn(amax, qmax);
   const float q = amax * c;
   return __fmaf_rn(__fmaf_rn(-q, qmax, amax), c, q);
+}
+
+// |x| maximum of two packed 16-bit pairs, element-wise (NaN operands are ignored, like fmaxf).
+template <typename T>
+__device__ __forceinline__ uint32_t absmax_pairs(uint32_t a, uint32_t b) {
+  if constexpr (std::is_same<T, __half>::value) {
+    const __half2 m = __hmax2(__habs2(*reinterpret_cast<const __half2*>(&a)), __habs2(*reinterpret_cast<const __half2*>(&b)));
+    return *reinterpret_cast<const uint32_t*>(&m);
+  } else {
+    const __nv_bfloat162 m = __hmax2(__habs2(*reinterpret_cast<const __nv_bfloat162*>(&a)),
+                                     __habs2(*reinterpret_cast<const __nv_bfloat162*>(&b)));
+    return *reinterpret_cast<const uint32_t*>(&m);
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ float2 unpack_pair(uint32_t w) {
+  if constexpr (std::is_same<T, __half>::value) return __half22float2(*reinterpret_cast<const __half2*>(&w));
+  else return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));  // bf16 -> fp32 is a shift
 }
 
 // Two neighbouring elements -> two bytes (x0 in the low byte).

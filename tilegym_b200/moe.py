@@ -145,19 +145,24 @@ def fused_experts_impl(
     assert tuple(w2_scale.shape) == (E, H // 128, inter // 128), "w2_scale must hold one scale per 128 x 128 block"
     topk = topk_ids.shape[1]
     out_dtype = torch.bfloat16 if hidden_states.dtype == torch.bfloat16 else torch.float16
-    if hidden_states.dtype == _FP8:
-        assert a1_scale is not None and tuple(a1_scale.shape) == (T, H // 128), "a1_scale must be [tokens, hidden / 128]"
-        a8, a_s = hidden_states, a1_scale.to(torch.float32)
-    else:
-        a8, a_s = ops.act_quant(hidden_states, 128)
-
     L, stream = _lib.lib(), ops._stream(dev)
     m_indptr, sorted_ids, pos, w_sorted = moe_route(topk_ids, topk_weights, E)
     R = T * topk
     a_sorted = torch.empty((R, H), dtype=_FP8, device=dev)
     as_sorted = torch.empty((R, H // 128), dtype=torch.float32, device=dev)
-    _lib.check_rc(L.tg_moe_permute_rows(_lib.desc(a_sorted), _lib.desc(as_sorted), _lib.desc(a8), _lib.desc(a_s),
-                                        sorted_ids.data_ptr(), m_indptr.data_ptr(), E, topk, dev.index, stream))
+    if hidden_states.dtype == _FP8:
+        assert a1_scale is not None and tuple(a1_scale.shape) == (T, H // 128), "a1_scale must be [tokens, hidden / 128]"
+        a8, a_s = hidden_states, a1_scale.to(torch.float32)
+        _lib.check_rc(L.tg_moe_permute_rows(_lib.desc(a_sorted), _lib.desc(as_sorted), _lib.desc(a8), _lib.desc(a_s),
+                                            sorted_ids.data_ptr(), m_indptr.data_ptr(), E, topk, dev.index, stream))
+    elif hidden_states.dtype in (torch.bfloat16, torch.float16):
+        # 16-bit activations: quantised (the arithmetic of act_quant) and scattered into expert order in one pass
+        _lib.check_rc(L.tg_moe_quant_permute_rows(_lib.desc(a_sorted), _lib.desc(as_sorted), _lib.desc(hidden_states),
+                                                  pos.data_ptr(), topk, dev.index, stream))
+    else:
+        a8, a_s = ops.act_quant(hidden_states, 128)
+        _lib.check_rc(L.tg_moe_permute_rows(_lib.desc(a_sorted), _lib.desc(as_sorted), _lib.desc(a8), _lib.desc(a_s),
+                                            sorted_ids.data_ptr(), m_indptr.data_ptr(), E, topk, dev.index, stream))
     y8 = torch.empty((R, inter), dtype=_FP8, device=dev)
     y_s = torch.empty((R, inter // 128), dtype=torch.float32, device=dev)
     mode = 1 if a2_quant == "block" else 0
