@@ -110,6 +110,37 @@ def test_small_group_kernel_equals_the_tile_kernel_bit_for_bit(dev):
     _lib.device_status(dev.index)
 
 
+@pytest.mark.parametrize("seed", list(range(8)))
+def test_random_small_groups_agree_with_the_tile_kernel_and_the_oracle(dev, seed):
+    """Seeded random problems: group count, group sizes (many empty), N and K vary; the small-group kernel (tile
+    height chosen by the library), the forced other height and the 128-row tile kernel must agree bit for bit, and
+    all must meet the oracle."""
+    g = torch.Generator().manual_seed(1000 + seed)
+    G = int(torch.randint(1, 40, (1,), generator=g))
+    hi = int(torch.randint(2, 70, (1,), generator=g))
+    sizes = [int(v) for v in torch.randint(0, hi, (G,), generator=g)]
+    if sum(sizes) == 0:
+        sizes[0] = 1
+    N = int(torch.randint(1, 5, (1,), generator=g)) * 128 + int(torch.randint(0, 2, (1,), generator=g)) * 72
+    K = int(torch.randint(1, 9, (1,), generator=g)) * 128 + int(torch.randint(0, 2, (1,), generator=g)) * 48
+    a8, b, As, bs, ind = make_case(sizes, N, K, seed=2000 + seed)
+    ref = R.ref_ragged_block_scaled_bmm(a8, b, As, bs, ind)
+    args = [t.to(dev) for t in (a8, b, As, bs, ind)]
+    outs = []
+    for tile in (None, "0", "32", "64"):
+        _lib.set_knob("TILEGYM_B200_GROUPED_SMALLM", tile)
+        try:
+            outs.append(tg.ragged_block_scaled_bmm(*args, max(sizes)).clone())
+        finally:
+            _lib.set_knob("TILEGYM_B200_GROUPED_SMALLM", None)
+    torch.cuda.synchronize(dev)
+    _lib.device_status(dev.index)
+    for o in outs[1:]:
+        assert torch.equal(outs[0], o), (G, sizes, N, K)
+    res = R.check_tolerance(outs[0], ref)
+    assert res["ok"], (res, G, N, K)
+
+
 def test_each_group_equals_the_dense_kernel(dev):
     """Per group the grouped kernel runs the same k-block order and the same fused multiply-adds as the dense
     block-scaled kernel: identical bits."""
