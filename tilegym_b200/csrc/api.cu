@@ -5,6 +5,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <algorithm>
 #include <cstring>
 
 #include <dlfcn.h>
@@ -864,7 +865,8 @@ int32_t tg_fp8_gemm_blockscaled_grouped(const TgTensorDesc* C, const TgTensorDes
     if (forced == 32 || forced == 64) mp = forced;
     else if (forced != 0) mp = M <= 24 * G ? 32 : (M <= 64 * G ? 64 : 0);  // measured cross-overs (64 groups, K = 2048 / 1536)
     if (mp != 0 && beta == 0.0f && KB <= blockscaled_smallm_max_kb_per_cta()) {
-      const int64_t mbound = (M + mp - 1) / mp + G;
+      // every group adds at most one partly filled tile, and there are never more tiles than rows
+      const int64_t mbound = std::min<int64_t>((M + mp - 1) / mp + G, M);
       if (mbound * NB <= 0x3fffffff) {
         p.tiles_m = 1;
         p.tiles_n = static_cast<int32_t>(NB);
