@@ -25,12 +25,27 @@ namespace tg {
 namespace {
 
 // ------------------------------------------------------------------------------------------ routing
+// With up to kRouteSmemExperts experts a block first counts its pairs in shared memory and then adds one number per
+// expert to the global counts (a few thousand global atomics instead of one per pair, all on a handful of addresses).
+constexpr int kRouteSmemExperts = 2048;
 template <typename IdT>
-__global__ void moe_count_kernel(const IdT* __restrict__ ids, int64_t n, int num_experts, int32_t* __restrict__ counts) {
+__global__ void __launch_bounds__(256) moe_count_kernel(const IdT* __restrict__ ids, int64_t n, int num_experts,
+                                                        int32_t* __restrict__ counts) {
+  __shared__ int32_t local[kRouteSmemExperts];
+  const bool use_smem = num_experts <= kRouteSmemExperts;
+  if (use_smem) {
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) local[e] = 0;
+    __syncthreads();
+  }
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t e = static_cast<int64_t>(ids[i]);
-    if (e >= 0 && e < num_experts) atomicAdd(counts + e, 1);
+    if (e >= 0 && e < num_experts) atomicAdd(use_smem ? local + e : counts + e, 1);
+  }
+  if (use_smem) {
+    __syncthreads();
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x)
+      if (local[e] != 0) atomicAdd(counts + e, local[e]);
   }
 }
 
@@ -74,10 +89,43 @@ __global__ void moe_scan_kernel(int32_t* __restrict__ counts, int num_experts, i
   if (threadIdx.x == 0) m_indptr[num_experts] = carry;
 }
 
+// Placement: with few enough experts a block counts the pairs of its slice per expert in shared memory, reserves one
+// range per expert with a single global atomic, and hands out the places inside the range from shared memory.  A
+// block's slice is contiguous (the same pairs in both passes).
 template <typename IdT, typename WT>
-__global__ void moe_place_kernel(const IdT* __restrict__ ids, const WT* __restrict__ weights, int64_t n, int num_experts,
-                                 int32_t* __restrict__ cursors, int32_t* __restrict__ sorted_ids,
-                                 int32_t* __restrict__ pos, float* __restrict__ w_sorted) {
+__global__ void __launch_bounds__(256) moe_place_kernel(const IdT* __restrict__ ids, const WT* __restrict__ weights,
+                                                        int64_t n, int num_experts, int32_t* __restrict__ cursors,
+                                                        int32_t* __restrict__ sorted_ids, int32_t* __restrict__ pos,
+                                                        float* __restrict__ w_sorted) {
+  __shared__ int32_t local[kRouteSmemExperts];  // per expert: count of the slice, then the next place in the block's range
+  if (num_experts <= kRouteSmemExperts) {
+    const int64_t per = (n + gridDim.x - 1) / gridDim.x;
+    const int64_t lo = static_cast<int64_t>(blockIdx.x) * per, hi = lo + per < n ? lo + per : n;
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) local[e] = 0;
+    __syncthreads();
+    for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      const int64_t e = static_cast<int64_t>(ids[i]);
+      if (e >= 0 && e < num_experts) atomicAdd(local + e, 1);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+      const int32_t c = local[e];
+      local[e] = c != 0 ? atomicAdd(cursors + e, c) : 0;  // first place of this block's range for expert e
+    }
+    __syncthreads();
+    for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      const int64_t e = static_cast<int64_t>(ids[i]);
+      if (e >= 0 && e < num_experts) {
+        const int32_t r = atomicAdd(local + e, 1);
+        sorted_ids[r] = static_cast<int32_t>(i);
+        pos[i] = r;
+        if (w_sorted != nullptr) w_sorted[r] = weights != nullptr ? static_cast<float>(weights[i]) : 1.0f;
+      } else {
+        pos[i] = -1;
+      }
+    }
+    return;
+  }
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t e = static_cast<int64_t>(ids[i]);
