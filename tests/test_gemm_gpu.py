@@ -386,6 +386,35 @@ def test_block_scaled_small_m_output_dtypes_and_unaligned_n(dev, M, out_dtype, N
             assert R.check_tolerance(out, ref)["ok"]
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M", [1, 16, 33, 64])
+def test_block_scaled_small_m_with_many_weight_tiles(dev, M, out_dtype):
+    """M <= 64, a short K and at least as many weight tiles as SMs (DeepSeek's N = 24576, K = 1536 in small): one
+    short CTA per (row tile, weight tile), two per SM.  Against the oracle, with bias and a ragged N, and bit for bit
+    against the 128 x 128 tile kernel."""
+    N, K = 150 * 128 + 40, 640
+    g = torch.Generator().manual_seed(M + 3)
+    A = (torch.randn(M, K, generator=g) * 0.5).to(torch.float8_e4m3fn)
+    B = (torch.randn(N, K, generator=g) * 0.1).to(torch.float8_e4m3fn)
+    As = torch.rand(M, K // 128, generator=g) + 0.1
+    Bs = torch.rand(-(-N // 128), K // 128, generator=g) + 0.1
+    bias = torch.randn(N, generator=g).to(torch.bfloat16)
+    ref = R.ref_fp8_block_scaled_mm(A, B, As, Bs, bias=bias, out_dtype=out_dtype)
+    args = [t.to(dev) for t in (A, B, As, Bs)]
+    out = tg.fp8_block_scaled_mm(*args, bias=bias.to(dev), out_dtype=out_dtype)
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(out.cpu(), ref, rtol=1e-4, atol=1e-4 * float(ref.abs().max()))
+    else:
+        assert R.check_tolerance(out, ref)["ok"]
+    _lib.set_knob("TILEGYM_B200_BS_SMALLM", "0")
+    try:
+        tile = tg.fp8_block_scaled_mm(*args, bias=bias.to(dev), out_dtype=out_dtype)
+    finally:
+        _lib.set_knob("TILEGYM_B200_BS_SMALLM", None)
+    assert torch.equal(out, tile)
+    _lib.device_status(dev.index)
+
+
 def test_block_scaled_small_m_is_bit_stable_and_back_to_back(dev):
     a8, b8, As, Bs = (t.to(dev) for t in R.gen_block_scaled_case(128, 3072, 5120, seed=12))
     first = tg.w8a8_block_fp8_matmul(a8, b8, As, Bs, [128, 128], torch.bfloat16).clone()

@@ -1038,6 +1038,26 @@ int32_t tg_fp8_gemm_blockscaled(const TgTensorDesc* C, const TgTensorDesc* A, co
   if (tiles > 0x3fffffff) return fail(TG_ERR_ARGS, "problem has too many tiles");
   // Small M (M <= 128, no beta): the swap-AB kernel (weights on the MMA M axis, K splits reduced inside a
   // cluster); TILEGYM_B200_BS_SMALLM=0 switches it off.
+  // M <= 64, a short K and at least as many weight tiles as SMs (e.g. N = 24576, K = 1536): one short CTA per
+  // (row tile, weight tile), two per SM, no K split - the launch shape of the grouped small-M kernel with one group.
+  if (M <= 64 && beta == 0.0f && knob(kKnobBsSmallm, 1) != 0 && p.num_kb <= blockscaled_smallm_max_kb_per_cta() &&
+      NB >= st.num_sms && knob(kKnobGroupedSmallm, -1) != 0) {
+    const int mp = M <= 32 ? 32 : 64;
+    p.tiles_m = 1;
+    p.tiles_n = static_cast<int32_t>(NB);
+    p.splits = 1;
+    p.kb_per_split = p.num_kb;
+    p.num_groups = 1;
+    p.m_indptr = nullptr;
+    p.mtile_bound = static_cast<int32_t>((M + mp - 1) / mp);
+    if (knob(kKnobPdl, 1) != 0) p.flags |= 2;
+    CUtensorMap tmW, tmX;
+    if ((rc = make_map(&tmW, B->ptr, N, K, B->strides[0], 128)) != TG_OK) return rc;
+    if ((rc = make_map(&tmX, A->ptr, M, K, A->strides[0], mp)) != TG_OK) return rc;
+    cudaError_t e0 = launch_gemm_blockscaled_smallm_grouped(tmW, tmX, p, mp, cs);
+    if (e0 != cudaSuccess) return fail(TG_ERR_LAUNCH, "block-scaled GEMM (small M, many tiles) launch failed: %s", cudaGetErrorString(e0));
+    return TG_OK;
+  }
   if (M <= 128 && beta == 0.0f && knob(kKnobBsSmallm, 1) != 0) {
     int s = 0, per = 0;
     const int mp = M <= 32 ? 32 : (M <= 64 ? 64 : 128);

@@ -133,6 +133,14 @@ struct BsmGroupTile {
 template <int MP>
 __device__ __forceinline__ BsmGroupTile bsm_locate_group_tile(int j, const GemmParams& p, int lane) {
   BsmGroupTile r = {0, 0, 0, 0};
+  if (p.m_indptr == nullptr) {  // one group holding all M rows: the dense problem on this kernel's launch shape
+    if (j * MP < p.M) {
+      r.row0 = j * MP;
+      r.rows = min(MP, p.M - r.row0);
+      r.valid = 1;
+    }
+    return r;
+  }
   int before = 0;  // tiles of the groups already scanned
   for (int g0 = 0; g0 < p.num_groups; g0 += 32) {
     const int g = g0 + lane;
@@ -677,7 +685,9 @@ cudaError_t launch_bsm_grouped(const CUtensorMap& tmW, const CUtensorMap& tmX, c
 }
 
 // Grouped form: p.tiles_n = ceil(N / 128) per group, p.mtile_bound >= the number of mp-row tiles of all groups,
-// p.splits == 1, p.num_kb <= the k-blocks one CTA may own; tmW maps the weights as [groups * N, K].
+// p.splits == 1, p.num_kb <= the k-blocks one CTA may own; tmW maps the weights as [groups * N, K].  With
+// p.m_indptr == nullptr all M rows form one group: the dense problem as many short CTAs, two per SM, for shapes with
+// at least as many weight tiles as SMs and a short K, where the cluster split-K form cannot keep all CTAs resident.
 cudaError_t launch_gemm_blockscaled_smallm_grouped(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p,
                                                    int mp, cudaStream_t stream) {
   if (p.splits != 1 || p.num_kb > kMaxKbPerCta || p.kb_per_split != p.num_kb) return cudaErrorInvalidValue;
