@@ -45,8 +45,8 @@ namespace {
 constexpr int kThreads = 192;
 constexpr int kMaxKbPerCta = 32;  // k-blocks one CTA may own (rows of the staged scale table)
 
-// TWO: sized for two CTAs per SM (the grouped form: one short work unit per CTA, so one CTA's start-up runs beside
-// the other's weight stream; half the stages each keep the bytes in flight per SM the same).
+// TWO: sized for two CTAs per SM (MP <= 64: one short work unit per CTA, so one CTA's start-up and reduction run
+// beside the other's weight stream; half the stages each keep the bytes in flight per SM the same).
 template <int MP, bool TWO = false>
 struct BsmCfg {
   static constexpr int kWBytes = kBM * kBK;  // 128 weight rows x 128 B per stage
@@ -172,12 +172,16 @@ __device__ __forceinline__ BsmGroupTile bsm_locate_group_tile(int j, const GemmP
   return r;
 }
 
+// Up to 64 activation rows the kernel is sized for two CTAs per SM (see BsmCfg): twice as many K splits stay
+// resident, and one CTA's start-up and reduction run beside the other's weight stream.
+__host__ __device__ constexpr bool bsm_two_per_sm(int mp) { return mp <= 64; }
+
 template <int MP, bool CLUSTER, bool GROUPED = false>
-__global__ void __launch_bounds__(kThreads, GROUPED ? 2 : 1)
+__global__ void __launch_bounds__(kThreads, bsm_two_per_sm(MP) ? 2 : 1)
     tg_fp8_gemm_blockscaled_smallm_kernel(const __grid_constant__ CUtensorMap tmW,
                                           const __grid_constant__ CUtensorMap tmX, const GemmParams p) {
   static_assert(!(GROUPED && CLUSTER), "the grouped form is never split");
-  using Cfg = BsmCfg<MP, GROUPED>;
+  using Cfg = BsmCfg<MP, bsm_two_per_sm(MP)>;
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -581,16 +585,16 @@ cudaError_t launch_bsm(const CUtensorMap& tmW, const CUtensorMap& tmX, const Gem
   const bool cluster = p.splits > 1;
   if (dev >= 0 && dev < 64 && !configured[dev][cluster ? 1 : 0]) {
     cudaError_t e = cluster ? cudaFuncSetAttribute(tg_fp8_gemm_blockscaled_smallm_kernel<MP, true>,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, BsmCfg<MP>::kSmemBytes)
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, BsmCfg<MP, bsm_two_per_sm(MP)>::kSmemBytes)
                             : cudaFuncSetAttribute(tg_fp8_gemm_blockscaled_smallm_kernel<MP, false>,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, BsmCfg<MP>::kSmemBytes);
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, BsmCfg<MP, bsm_two_per_sm(MP)>::kSmemBytes);
     if (e != cudaSuccess) return e;
     configured[dev][cluster ? 1 : 0] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(p.tiles_n * p.splits), 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = BsmCfg<MP>::kSmemBytes;
+  cfg.dynamicSmemBytes = BsmCfg<MP, bsm_two_per_sm(MP)>::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   int na = 0;
@@ -620,11 +624,11 @@ namespace {
 template <int MP>
 int max_clusters(int splits) {
   cudaFuncSetAttribute(tg_fp8_gemm_blockscaled_smallm_kernel<MP, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                       BsmCfg<MP>::kSmemBytes);
+                       BsmCfg<MP, bsm_two_per_sm(MP)>::kSmemBytes);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(splits * 64), 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = BsmCfg<MP>::kSmemBytes;
+  cfg.dynamicSmemBytes = BsmCfg<MP, bsm_two_per_sm(MP)>::kSmemBytes;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = static_cast<unsigned>(splits);
@@ -644,7 +648,7 @@ int max_clusters(int splits) {
 // How many clusters of `splits` CTAs of the small-M kernel (activation rows padded to mp) the current device
 // holds at once (cluster placement is per GPC, so this is not num_sms / splits); cached per device.
 int blockscaled_smallm_resident_clusters(int mp, int splits, int num_sms) {
-  if (splits <= 1) return num_sms;
+  if (splits <= 1) return bsm_two_per_sm(mp) ? 2 * num_sms : num_sms;
   if (splits > 8) return 0;
   static int cache[64][3][9] = {};  // 0 = not asked yet, -1 = none
   int dev = 0;
@@ -653,7 +657,12 @@ int blockscaled_smallm_resident_clusters(int mp, int splits, int num_sms) {
   if (dev < 0 || dev >= 64) return 0;
   int& c = cache[dev][mi][splits];
   if (c == 0) {
-    const int n = mp == 32 ? max_clusters<32>(splits) : (mp == 64 ? max_clusters<64>(splits) : max_clusters<128>(splits));
+    int n = mp == 32 ? max_clusters<32>(splits) : (mp == 64 ? max_clusters<64>(splits) : max_clusters<128>(splits));
+    // The occupancy query reports the same counts for the two-per-SM instantiations as for the one-per-SM one (74 /
+    // 45 / 33 / 26 / 22 / 15 / 15 clusters of 2 ... 8 on a B200), but two of their CTAs do share an SM: 40 clusters of
+    // 6 (240 CTAs) run as one wave - 15.1 us on N = 5120, K = 12288 against 18.0 us for 40 clusters of 3 - while 40
+    // clusters of 7 do not.  Residency only decides speed (clusters are independent), so the count is doubled.
+    if (bsm_two_per_sm(mp)) n *= 2;
     c = n > 0 ? n : -1;
   }
   return c > 0 ? c : 0;
@@ -667,14 +676,14 @@ cudaError_t launch_bsm_grouped(const CUtensorMap& tmW, const CUtensorMap& tmX, c
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(tg_fp8_gemm_blockscaled_smallm_kernel<MP, false, true>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, BsmCfg<MP, true>::kSmemBytes);
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, BsmCfg<MP, bsm_two_per_sm(MP)>::kSmemBytes);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(units), 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = BsmCfg<MP, true>::kSmemBytes;
+  cfg.dynamicSmemBytes = BsmCfg<MP, bsm_two_per_sm(MP)>::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
